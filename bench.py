@@ -1,0 +1,437 @@
+"""Benchmark of the sparse-attention decode path (one layer, one decode step per "step").
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3] [--impl reference]
+
+A step = append+hash one new token, soft-hash the query, score every cached key, select the
+top-k plus sink/window, sparse attention over the selected rows — the body of the reference's
+`Attention.sparse_forward` between the QKV projection and the output projection.  Inputs are
+seeded synthetic tensors with the benchmark configuration's shapes and distributions.
+
+Printed JSON (one line, rank 0):
+  value / ms_per_step   whole-job tokens/s per layer, inputs resident in HBM, each step one CUDA
+                        graph launch timed with CUDA events; L2 is flushed between steps
+  e2e                   the same step through the public API (`SocketAttention.sparse_decode`)
+                        with q/k/v in pinned HOST buffers and the output read back to the host
+  roofline              the dominant kernel: algorithmic bytes / measured launch time
+  stages                every kernel's time and achieved GB/s, and the whole step's
+  cpu_baseline          the CPU restatement of the reference path on this box's host cores
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from socket_b200.config import PRESETS  # noqa: E402
+
+METRIC = "sparse_attn_decode_tokens_per_s"
+UNIT = "tokens/s/layer"
+FALLBACK_HBM_GBS = 6650.0
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/; None where no capture of that kernel/workload exists yet.
+NCU_TRAFFIC = {}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--workload", default="c2", choices=sorted(PRESETS))
+    ap.add_argument("--impl", default="socket_b200", choices=["socket_b200", "reference"])
+    ap.add_argument("--shard", default="weak", choices=["weak", "strong"],
+                    help="N>1: weak = every GPU owns a full set of KV-head groups of the workload; "
+                         "strong = the workload's KV heads are split over the GPUs")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--seed", type=int, default=1234)
+    return ap.parse_args()
+
+
+def peak_hbm():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+                for n, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+def cpu_reference_steps(cfg, state, n_steps_cap=50, budget_s=12.0):
+    """Times the CPU restatement of the reference path (oracle/c) on the host cores: per step
+    hash the new key, soft-hash the query, score, select + list, sparse attention."""
+    from oracle import c_oracle
+    k, v, codes, vnorm, planes, protos, q_all, k_all, v_all = state
+    B, Hkv, Tcap, D = k.shape
+    T0 = cfg.context
+    cores = c_oracle.num_threads()
+    times = []
+    t_begin = time.perf_counter()
+    for i in range(n_steps_cap):
+        t0 = time.perf_counter()
+        pos = T0 + i
+        kn = k_all[i][:, 0]                    # [B,Hkv,D]
+        vn_ = v_all[i][:, 0]
+        k[:, :, pos] = kn
+        v[:, :, pos] = vn_
+        codes[:, :, pos] = c_oracle.hash_keys(kn.contiguous(), planes, exact=False).to(torch.uint8)
+        vnorm[:, :, pos] = c_oracle.value_norm(vn_.contiguous())
+        T = pos + 1
+        qp = c_oracle.soft_hash(q_all[i], planes, protos)
+        sc = c_oracle.score(qp, codes, vnorm, T)
+        lst, ln = c_oracle.select_list(sc, cfg.sink, cfg.window, cfg.topk, sorted_by_score=True)
+        c_oracle.sparse_attention(q_all[i], k, v, lst, ln)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_begin > budget_s and len(times) >= 3:
+            break
+    use = times[1:] if len(times) > 1 else times
+    per_step = sum(use) / len(use)
+    return per_step, cores, len(times)
+
+
+def host_state(cfg, seed, steps):
+    """Host copies of the benchmark state for the CPU leg (same generator as the GPU leg's,
+    drawn on the CPU)."""
+    from oracle import c_oracle
+    from socket_b200.synth import make_decode_inputs, make_step_inputs
+    dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[cfg.kv_dtype]
+    B, H, Hkv, T, D = cfg.batch, cfg.n_head, cfg.n_local_heads, cfg.context, cfg.head_dim
+    dev = "cuda" if torch.cuda.is_available() else None
+    inp = make_decode_inputs(B, H, Hkv, T, D=D, L=cfg.L, P=cfg.P, seed=seed, dtype=dt, device=dev)
+    Tcap = T + steps + 8
+    k = torch.zeros(B, Hkv, Tcap, D, dtype=dt)
+    v = torch.zeros(B, Hkv, Tcap, D, dtype=dt)
+    k[:, :, :T] = inp.k.cpu()
+    v[:, :, :T] = inp.v.cpu()
+    planes = inp.planes.cpu()
+    codes = torch.zeros(B, Hkv, Tcap, cfg.L, dtype=torch.uint8)
+    codes[:, :, :T] = c_oracle.hash_keys(k[:, :, :T].contiguous(), planes, exact=False).to(torch.uint8)
+    vnorm = torch.zeros(B, Hkv, Tcap, dtype=torch.float16)
+    vnorm[:, :, :T] = c_oracle.value_norm(v[:, :, :T].contiguous())
+    q_all, k_all, v_all = make_step_inputs(B, H, Hkv, D, steps, seed + 1, dt)
+    return (k, v, codes, vnorm, planes, inp.protos_T.cpu(), q_all, k_all, v_all)
+
+
+def run_reference(args, cfg):
+    """`--impl reference`: the reference path's CPU implementation on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n = max(1, min(args.steps, 50))
+    state = host_state(cfg, args.seed, n + args.warmup)
+    from oracle import c_oracle
+    per_step, cores, done = cpu_reference_steps(cfg, state, n_steps_cap=n + min(args.warmup, 3))
+    val = cfg.batch / per_step
+    sample = (f"{done} decode steps of workload {args.workload} (full context, all heads) with the C "
+              f"restatement of the reference path, OpenMP over {cores} threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": done, "warmup": 1, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": cfg.kv_dtype, "data": "synthetic",
+        "config": workload_config(args, cfg, 1),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(args, cfg, world):
+    return {
+        "workload": f"{args.workload}: one layer, batch {cfg.batch}, {cfg.n_head} query / "
+                    f"{cfg.n_local_heads} KV heads, head_dim {cfg.head_dim}, context {cfg.context}, "
+                    f"{cfg.kv_dtype} KV, L={cfg.L} P={cfg.P}, top-k {cfg.topk} + sink {cfg.sink} + "
+                    f"window {cfg.window}",
+        "parallelism": ("single GPU" if world == 1 else
+                        (f"{world} GPUs, each owning the workload's {cfg.n_local_heads} KV-head groups "
+                         f"(no collective on the path)" if args.shard == "weak" else
+                         f"{world} GPUs, the {cfg.n_local_heads} KV heads split {cfg.n_local_heads // world} per GPU")),
+        "l2": "flushed between timed steps (256 MiB write)" if not args.no_flush else "not flushed",
+        "timing": "per-step CUDA events around one CUDA-graph launch, summed over the steps",
+    }
+
+
+# ------------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    cfg_full = PRESETS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, cfg_full)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+
+    from socket_b200 import ops
+    from socket_b200.attention import SocketAttention
+    from socket_b200.synth import make_decode_inputs, make_step_inputs
+    from socket_b200 import tp
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        tp.maybe_init_dist("nccl")
+    cfg = cfg_full.shard_kv_heads(world) if (world > 1 and args.shard == "strong") else cfg_full
+
+    dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[cfg.kv_dtype]
+    B, H, Hkv, T0, D = cfg.batch, cfg.n_head, cfg.n_local_heads, cfg.context, cfg.head_dim
+    K, W = args.steps, args.warmup
+    total_steps = K + W
+    Tcap = T0 + 2 * total_steps + 64
+    inp = make_decode_inputs(B, H, Hkv, T0, D=D, L=cfg.L, P=cfg.P, seed=args.seed + rank, dtype=dt, device=dev)
+    attn = SocketAttention(H, Hkv, D, L=cfg.L, P=cfg.P, heavy_const=cfg.topk, sink_size=cfg.sink,
+                           window_size=cfg.window, planes=inp.planes, protos_T=inp.protos_T, dtype=dt,
+                           device=dev)
+    cache = attn.setup_cache(B, Tcap, dtype=dt)
+    k_bshd = inp.k.permute(0, 2, 1, 3)
+    v_bshd = inp.v.permute(0, 2, 1, 3)
+    for s0 in range(0, T0, 8192):
+        s1 = min(T0, s0 + 8192)
+        cache.append(torch.arange(s0, s1, device=dev), k_bshd[:, s0:s1].contiguous(),
+                     v_bshd[:, s0:s1].contiguous(), attn.planes)
+    del inp, k_bshd, v_bshd
+    q_all, k_all, v_all = make_step_inputs(B, H, Hkv, D, total_steps, args.seed + 1000 + rank, dt, device=dev)
+
+    # staging buffers the captured step reads from
+    q_s = torch.empty(B, H, D, dtype=dt, device=dev)
+    k_s = torch.empty(B, 1, Hkv, D, dtype=dt, device=dev)
+    v_s = torch.empty(B, 1, Hkv, D, dtype=dt, device=dev)
+    pos_s = torch.zeros(1, dtype=torch.int64, device=dev)
+    out = torch.empty(B, H, D, dtype=dt, device=dev)
+    step = ops.DecodeStep(cache, q_s, k_s, v_s, pos_s, attn.planes, attn.protos_T, out, topk=cfg.topk,
+                          sink=cfg.sink, window=cfg.window, T_max=Tcap)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def stage(i, pos):
+        q_s.copy_(q_all[i])
+        k_s.copy_(k_all[i])
+        v_s.copy_(v_all[i])
+        pos_s.fill_(pos)
+
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.stream(side):
+        stage(0, T0)
+        step.run()                       # also sets the kernels' shared-memory attributes
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step.run()
+    torch.cuda.synchronize()
+
+    def timed_loop(n, first, launch):
+        evs = []
+        for i in range(n):
+            stage(first + i, T0 + first + i)
+            if not args.no_flush:
+                flush.fill_(i & 0xff)
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            launch()
+            e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in evs]
+
+    timed_loop(W, 0, graph.replay)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    per_step_ms = timed_loop(K, W, graph.replay)
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    total_ms = sum(per_step_ms)
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    total_ms = float(t.item())
+    assert int(step.status) == 0, f"device status {int(step.status)}"
+    tokens = B * K * (world if args.shard == "weak" else 1)
+    value = tokens / (total_ms * 1e-3)
+    ms_per_step = total_ms / K
+
+    # ---- per-kernel timing (same stream, same flush discipline) --------------------------
+    T_now = T0 + total_steps
+    peak, peak_src = peak_hbm()
+    stages = {}
+    lutbuf = torch.empty(B * H * cfg.L * cfg.R, dtype=torch.float32, device=dev)
+    a_codes = B * Hkv * T_now * cfg.L
+    a_kv = B * H * cfg.ktot * 2 * D * cfg.kv_bytes()
+
+    def time_kernel(fn, n=50):
+        ts = []
+        for i in range(n + 3):
+            if not args.no_flush:
+                flush.fill_(i & 0xff)
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            ts.append((e0, e1))
+        torch.cuda.synchronize()
+        v = sorted(a.elapsed_time(b) for a, b in ts[3:])
+        return sum(v) / len(v) * 1e3    # us
+
+    probs, lut = ops.soft_hash(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv, want_probs=False,
+                               want_lut=True)
+    scores = ops.score(lut, cache.k_hard, cache.v_norm, H, T_now)
+    lst, ln = ops.select_list(scores, T_now, cfg.topk, cfg.sink, cfg.window)
+    us = {}
+    us["kv_append"] = time_kernel(lambda: cache.append(pos_s, k_s, v_s, attn.planes))
+    us["soft_hash"] = time_kernel(lambda: ops.soft_hash(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv,
+                                                        want_probs=False, want_lut=True))
+    us["score"] = time_kernel(lambda: ops.score(lut, cache.k_hard, cache.v_norm, H, T_now, out=scores))
+    us["select_list"] = time_kernel(lambda: ops.select_list(scores, T_now, cfg.topk, cfg.sink, cfg.window))
+    us["sparse_decode"] = time_kernel(lambda: ops.sparse_decode(q_s, cache.k_cache, cache.v_cache, lst, ln, T=T_now))
+    alg = {"kv_append": 0, "soft_hash": 0, "score": a_codes, "select_list": 0, "sparse_decode": a_kv}
+    for name, t_us in us.items():
+        gbs = alg[name] / (t_us * 1e-6) / 1e9 if alg[name] else None
+        stages[name] = {"us": round(t_us, 2), "algorithmic_bytes": alg[name],
+                        "achieved_gbs": None if gbs is None else round(gbs, 1)}
+    A = a_codes + a_kv
+    step_gbs = A / (ms_per_step * 1e-3) / 1e9
+    stages["whole_step"] = {"us": round(ms_per_step * 1e3, 2), "algorithmic_bytes": A,
+                            "achieved_gbs": round(step_gbs, 1), "frac_of_hbm_peak": round(step_gbs / peak, 4),
+                            "frac_of_8tbs": round(step_gbs / 8000.0, 4)}
+    dominant = max(("score", "sparse_decode", "select_list"), key=lambda n: us[n])
+    dom_alg = alg[dominant] if alg[dominant] else A
+    dom_gbs = dom_alg / (us[dominant] * 1e-6) / 1e9
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": round(dom_gbs, 1), "peak": peak,
+                "unit": "GB/s", "frac": round(dom_gbs / peak, 4), "peak_source": peak_src,
+                "traffic": NCU_TRAFFIC.get((dominant, args.workload))}
+
+    # ---- end to end through the public API with host buffers -----------------------------
+    n_e2e = min(K, 200)
+    hq = q_all[:n_e2e + 3].cpu().pin_memory()
+    hk = k_all[:n_e2e + 3].cpu().pin_memory()
+    hv = v_all[:n_e2e + 3].cpu().pin_memory()
+    hout = torch.empty(B, H, D, dtype=dt).pin_memory()
+    dq = torch.empty(B, H, D, dtype=dt, device=dev)
+    dk = torch.empty(B, 1, Hkv, D, dtype=dt, device=dev)
+    dv = torch.empty(B, 1, Hkv, D, dtype=dt, device=dev)
+    dpos = torch.zeros(1, dtype=torch.int64, device=dev)
+    hpos = torch.zeros(1, dtype=torch.int64).pin_memory()
+    dout = torch.empty(B, H, D, dtype=dt, device=dev)
+    e2e_ms = []
+    for i in range(n_e2e + 3):
+        if not args.no_flush:
+            flush.fill_(i & 0xff)
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        hpos[0] = T_now + i
+        e0.record()
+        dq.copy_(hq[i], non_blocking=True)
+        dk.copy_(hk[i], non_blocking=True)
+        dv.copy_(hv[i], non_blocking=True)
+        dpos.copy_(hpos, non_blocking=True)
+        attn.sparse_decode(dq, dk, dv, dpos, out=dout)
+        hout.copy_(dout, non_blocking=True)
+        e1.record()
+        e1.synchronize()
+        if i >= 3:
+            e2e_ms.append(e0.elapsed_time(e1))
+    e2e_t = torch.tensor([sum(e2e_ms) / len(e2e_ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(e2e_t, op=torch.distributed.ReduceOp.MAX)
+    e2e_ms_step = float(e2e_t.item())
+    h2d = (dq.numel() + dk.numel() + dv.numel()) * dq.element_size() + 8
+    d2h = dout.numel() * dout.element_size()
+    e2e = {"value": B * (world if args.shard == "weak" else 1) / (e2e_ms_step * 1e-3), "unit": UNIT,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms_step,
+           "steps": len(e2e_ms)}
+    clocks = sampler.stop() if sampler is not None else None
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            state = host_state(cfg_full, args.seed, 64)
+            per_step, cores, done = cpu_reference_steps(cfg_full, state)
+            cpu_baseline = {"value": cfg_full.batch / per_step, "unit": UNIT, "cores": cores, "kind": "port",
+                            "ms_per_step": per_step * 1e3,
+                            "sample": f"{done} decode steps of workload {args.workload} (full context, all "
+                                      f"heads) with the C restatement of the reference path"}
+        except Exception as e:  # the baseline is a reported figure, never a reason to lose the line
+            cpu_baseline = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                            "sample": f"failed: {e!r}"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "higher_is_better": True,
+            "scaling": args.shard, "vs_baseline": None, "dtype": cfg.kv_dtype, "data": "synthetic",
+            "config": workload_config(args, cfg, world), "roofline": roofline, "stages": stages,
+            "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": clocks,
+            "gpu_launches": K * step.n_launches,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

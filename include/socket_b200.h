@@ -1,0 +1,223 @@
+/* socket_b200 — C ABI of the B200-native SOCKET sparse-attention decode path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as an
+ * opaque pointer, i.e. a cudaStream_t), enqueues its kernels on that stream and returns
+ * without synchronising.  Nothing here allocates device memory: outputs and scratch are
+ * provided by the caller (sizes from the *_workspace_bytes queries).
+ *
+ * Return value: 0 on success, a negative sk_status on an argument / launch error detected
+ * on the host (nothing was enqueued for argument errors).  sk_last_error() returns a
+ * thread-local description of the most recent failure.  Conditions that only the device
+ * can see (a cache position out of range, a list index out of range, a wait that ran out)
+ * are reported through the optional `status` word: a device int32 the kernels OR flags
+ * into (SK_DEV_*); the offending access is skipped, the context stays usable.
+ *
+ * File:line citations name the reference interface (amarka8/SOCKET, paths relative to the
+ * reference root) each entry point replaces.
+ */
+#ifndef SOCKET_B200_H_
+#define SOCKET_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SK_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define SK_API __attribute__((visibility("default")))
+#else
+#define SK_API
+#endif
+
+/* element types of q / K / V / planes */
+enum { SK_F32 = 0, SK_BF16 = 1, SK_F16 = 2 };
+
+enum sk_status {
+    SK_OK = 0,
+    SK_ERR_INVALID_ARGUMENT = -1, /* null pointer, non-positive size, inconsistent shapes   */
+    SK_ERR_UNSUPPORTED = -2,      /* a shape / dtype this build has no kernel for            */
+    SK_ERR_MISALIGNED = -3,       /* pointer or stride not aligned as the kernel requires    */
+    SK_ERR_WORKSPACE = -4,        /* workspace too small                                     */
+    SK_ERR_CUDA = -5              /* the CUDA runtime reported a launch / configuration error */
+};
+
+/* flags OR-ed into the device status word */
+#define SK_DEV_POS_OUT_OF_RANGE 1   /* sk_kv_append: input_pos outside [0, Tcap)           */
+#define SK_DEV_INDEX_OUT_OF_RANGE 2 /* sk_sparse_decode: list entry >= T (entry skipped)   */
+#define SK_DEV_WAIT_TIMEOUT 4       /* a bounded wait on an asynchronous copy gave up      */
+
+SK_API int sk_abi_version(void);
+SK_API const char* sk_status_string(int status);
+SK_API const char* sk_last_error(void);
+
+/* ------------------------------------------------------------------------------------
+ * Key hashing.  Replaces Attention.hard_hash_keys + pack_bits (GPT-FAST/model.py:403-413):
+ * code[n,l] = sum_p [<keys[n,:], planes[l,p,:]> >= 0] << (P-1-p).  The sign is decided on
+ * the exact dot product (fp64 accumulation), so it does not depend on summation order.
+ *   keys    [N, D] rows, `key_row_stride` elements apart
+ *   planes  [L, P, D] contiguous
+ *   codes   [N, L], `code_row_stride` elements apart; uint8 when code_bytes == 1 (P <= 8),
+ *           int16 when code_bytes == 2 (P <= 15, the reference's dtype)
+ * ---------------------------------------------------------------------------------- */
+SK_API int sk_hash_keys(const void* keys, int key_dtype, int64_t key_row_stride, const void* planes,
+                 int plane_dtype, int64_t N, int D, int L, int P, void* codes, int code_bytes,
+                 int64_t code_row_stride, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * KV-cache append with hashing.  Replaces, in one launch, hard_hash_keys + the v-norm +
+ * KVCache.update (GPT-FAST/model.py:449-451, 187-229) for S new tokens:
+ *   k_new, v_new [B, S, Hkv, D] contiguous (kv_dtype)
+ *   input_pos    [S] int64, device: cache position of each new token
+ *   k_cache, v_cache [B, Hkv, Tcap, D]; codes [B, Hkv, Tcap, L] uint8;
+ *   v_norm [B, Hkv, Tcap] fp16 (||v||_2, model.py:450)
+ *   prefill_len  device int32, updated to max(prefill_len, max(input_pos)+1) (model.py:228)
+ *   status       device int32 or NULL; a position outside [0,Tcap) sets
+ *                SK_DEV_POS_OUT_OF_RANGE and that token is not written (the reference
+ *                raises from a host-side check, model.py:211-217)
+ * ---------------------------------------------------------------------------------- */
+SK_API int sk_kv_append(const void* k_new, const void* v_new, int kv_dtype, const int64_t* input_pos,
+                 const void* planes, int plane_dtype, void* k_cache, void* v_cache,
+                 uint8_t* codes, uint16_t* v_norm, int32_t* prefill_len, int32_t* status, int B,
+                 int S, int Hkv, int D, int64_t Tcap, int L, int P, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Query soft hash.  Replaces Attention.soft_hash (GPT-FAST/model.py:392-401):
+ * q_probs[b,h,l,:] = softmax_r( (tanh(<q, planes[l,p]>) / sqrt(D)) . protos_T[p,r] / temperature )
+ * (temperature 1.0 = the GPT-FAST formula; the HuggingFace variant divides by 0.3,
+ * pipeline/train_quest/modeling/modeling_llama.py:638).
+ *   q [B,H,D]; planes [L,P,D]; protos_T [P,R] fp32
+ *   q_probs  [B,H,L,R] fp32 or NULL
+ *   lut      scorer table or NULL: [B*Hkv*tiles][R][L][ht] fp32 with ht = sk_lut_head_tile(H/Hkv),
+ *            tiles = (H/Hkv)/ht — the same numbers, grouped so that the ht query heads of a
+ *            KV head that are scored together sit in one 4*ht-byte word.  B*H*L*R*4 bytes.
+ * ---------------------------------------------------------------------------------- */
+SK_API int sk_lut_head_tile(int rep);
+SK_API int sk_soft_hash(const void* q, int q_dtype, const void* planes, int plane_dtype,
+                 const float* protos_T, float temperature, int B, int H, int Hkv, int D, int L,
+                 int P, int R, float* q_probs, float* lut, void* stream);
+
+/* Scorer table from a q_probs tensor the caller already has ([B,H,L,R], any SK_* dtype);
+ * used by the drop-in build_sparse_list_decode, whose first argument is q_probs
+ * (GPT-FAST/kernels/sparse.py:16-17). */
+SK_API int sk_lut_from_probs(const void* q_probs, int dtype, int B, int H, int Hkv, int L, int R,
+                      float* lut, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Soft-collision scorer on the cache-native layout.  Computes what
+ * soft_hash_collision_kernel_3 computes (GPT-FAST/kernels/soft_hash_collision.cu:25-54)
+ * without the relayout that feeds it (GPT-FAST/model.py:494-506):
+ * scores[b,h,t] = allowed ? (sum_l q_probs[b,h,l,codes[b,h/rep,t,l]]) * v_norm[b,h/rep,t] : -inf
+ *   lut      from sk_soft_hash / sk_lut_from_probs
+ *   codes    [B,Hkv,Tcap,L] uint8 (16-byte aligned rows: L % 16 == 0)
+ *   v_norm   [B,Hkv,Tcap] fp16
+ *   allowed  [B,H,T] bytes (0 = masked) or NULL (every position allowed, the decode case,
+ *            model.py:490-492)
+ *   T        number of live positions; when T_dev != NULL the kernels use min(*T_dev, T)
+ *            (device-side length, e.g. KVCache.prefill_len) and T only bounds the grid
+ *   scores   [B,H,score_row_stride] fp32
+ * ---------------------------------------------------------------------------------- */
+SK_API int sk_score(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
+             const uint8_t* allowed, int B, int H, int Hkv, int L, int R, int64_t T,
+             const int32_t* T_dev, int64_t Tcap, float* scores, int64_t score_row_stride,
+             int32_t* status, void* stream);
+
+/* Exact surface of the reference's scorer extension, soft_hash_collision(q_probs,
+ * key_buckets, allowed_ext, v_hist) (GPT-FAST/kernels/soft_hash_collision_loader.py:16-72):
+ *   q_probs [B,H,1,L,R] fp32, key_buckets [B,H,L,T] int16, allowed [B,H,1,T] bool bytes,
+ *   v_hist [B,H,1,T] fp32, out [B,H,1,T] fp32.  Tables are added in ascending order, so
+ *   the result is bit-identical to the reference kernel's. */
+SK_API int sk_score_compat(const float* q_probs, const int16_t* key_buckets, const uint8_t* allowed,
+                    const float* v_hist, float* out, int B, int H, int L, int R, int64_t T,
+                    void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Top-k select + list assembly.  Replaces torch.topk and the list code of
+ * build_sparse_list_decode (GPT-FAST/kernels/sparse.py:57-95).  Per row r = (b,h):
+ *   list[r] = [0..sink) ++ [max(T-window,sink)..T) ++ topM(scores[r]),  list_len[r] = its length
+ * (a single entry T-1 replaces an empty sink+window part; duplicates between the parts are
+ * kept; entries whose position is not allowed become -1, as in the reference).  Among equal
+ * scores the smallest index wins.  Order of the top-M part: ascending index (sorted == 0)
+ * or descending score like torch.topk (sorted != 0).
+ *   scores [rows, score_row_stride] fp32, allowed [rows, T] bytes or NULL
+ *   list   [rows, list_row_stride] int32, list_row_stride >= sk_list_len(T, sink, window, M)
+ * ---------------------------------------------------------------------------------- */
+SK_API int64_t sk_list_len(int64_t T, int sink, int window, int64_t M);
+SK_API int sk_select_list(const float* scores, int64_t score_row_stride, const uint8_t* allowed,
+                   int64_t rows, int64_t T, const int32_t* T_dev, int64_t M, int sink,
+                   int window, int sorted, int32_t* list, int64_t list_row_stride,
+                   int32_t* list_len, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * GQA sparse flash-decode.  Replaces sparse_attention_fwd and its two Triton kernels
+ * (GPT-FAST/kernels/sparse.py:309-329, 102-235):
+ *   out[b,h,:] = sum_j softmax_j(<q[b,h], K[b,h/rep,idx_j]>/sqrt(D)) V[b,h/rep,idx_j],
+ *   j < list_len[b,h]; repeated indices count as often as they appear; negative entries
+ *   are skipped.  K/V rows are read in place from the cache (strides in elements), no
+ *   contiguous copy of the prefix is needed (compare GPT-FAST/model.py:541-542).
+ *   q, out [B,H,D] (q_dtype); k_cache, v_cache (kv_dtype) with batch/head/row strides
+ *   T: positions >= T are rejected (SK_DEV_INDEX_OUT_OF_RANGE), T_dev as in sk_score
+ *   workspace: sk_sparse_decode_workspace_bytes(B,H,D,max_list_len) bytes, 256-byte aligned.
+ *              Its first B*H int32 must be zero before the first call; every call leaves
+ *              them zero again.
+ * ---------------------------------------------------------------------------------- */
+SK_API size_t sk_sparse_decode_workspace_bytes(int B, int H, int D, int64_t max_list_len);
+SK_API int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, const void* v_cache,
+                     int kv_dtype, int64_t kv_batch_stride, int64_t kv_head_stride,
+                     int64_t kv_row_stride, const int32_t* list, int64_t list_row_stride,
+                     const int32_t* list_len, int64_t max_list_len, void* out, int B, int H,
+                     int Hkv, int D, int64_t T, const int32_t* T_dev, void* workspace,
+                     size_t workspace_bytes, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * One decode step of one layer, fused on one stream with no host synchronisation: the
+ * body of Attention.sparse_forward between the QKV projection and the output projection
+ * (GPT-FAST/model.py:449-552): append+hash the new token, soft-hash the query, score,
+ * select, attend.  Graph-capturable: the live length is read from `prefill_len` on the
+ * device, grids are sized from `T_max`.
+ * ---------------------------------------------------------------------------------- */
+typedef struct sk_decode_params {
+    /* new token */
+    const void* q;         /* [B,H,D]      q_dtype                                   */
+    const void* k_new;     /* [B,1,Hkv,D]  kv_dtype, NULL = cache already holds it   */
+    const void* v_new;     /* [B,1,Hkv,D]                                             */
+    const int64_t* input_pos; /* [1] device                                           */
+    /* hash parameters */
+    const void* planes;    /* [L,P,D] plane_dtype */
+    const float* protos_T; /* [P,R] */
+    float temperature;
+    /* cache */
+    void* k_cache;         /* [B,Hkv,Tcap,D] */
+    void* v_cache;
+    uint8_t* codes;        /* [B,Hkv,Tcap,L] */
+    uint16_t* v_norm;      /* [B,Hkv,Tcap] fp16 */
+    int32_t* prefill_len;  /* device int32 */
+    /* outputs */
+    void* out;             /* [B,H,D] q_dtype */
+    int32_t* list;         /* [B,H,list_row_stride] or NULL (then taken from workspace) */
+    int32_t* list_len;     /* [B,H] or NULL */
+    int64_t list_row_stride;
+    /* scratch */
+    void* workspace;
+    size_t workspace_bytes;
+    int32_t* status;       /* device int32 or NULL */
+    /* shapes */
+    int q_dtype, kv_dtype, plane_dtype;
+    int B, H, Hkv, D, L, P, R;
+    int64_t Tcap;
+    int64_t T_max;         /* upper bound of the live length during this call */
+    int64_t M;
+    int sink, window;
+} sk_decode_params;
+
+SK_API size_t sk_decode_step_workspace_bytes(int B, int H, int Hkv, int D, int L, int R, int64_t T_max,
+                                      int64_t M, int sink, int window);
+SK_API int sk_decode_step(const sk_decode_params* p, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SOCKET_B200_H_ */

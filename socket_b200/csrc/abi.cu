@@ -1,0 +1,286 @@
+// extern "C" entry points: argument validation, workspace carving, kernel launches.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace sk {
+
+static thread_local char g_err[512] = "";
+
+int fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return SK_OK;
+}
+
+static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+static inline bool valid_dtype(int d) { return d == SK_F32 || d == SK_BF16 || d == SK_F16; }
+static inline size_t esize(int d) { return d == SK_F32 ? 4 : 2; }
+static inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+static int64_t list_len_host(int64_t T, int sink, int window, int64_t M) {
+    if (T <= 0) return 0;
+    int64_t s = sink < 0 ? 0 : (sink > T ? T : sink);
+    int64_t w = window < 0 ? 0 : (window > T ? T : window);
+    int64_t nb = s;
+    if (w > 0) {
+        int64_t st = T - w > s ? T - w : s;
+        if (st < T) nb += T - st;
+    }
+    if (nb == 0) nb = 1;
+    return nb + (M < T ? (M < 0 ? 0 : M) : T);
+}
+
+}  // namespace sk
+
+using namespace sk;
+
+#define SK_REQUIRE(cond, ...)                                          \
+    do {                                                               \
+        if (!(cond)) return fail(SK_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+    } while (0)
+#define SK_ALIGNED(ptr, a, name)                                                         \
+    do {                                                                                 \
+        if (!aligned(ptr, a)) return fail(SK_ERR_MISALIGNED, name " must be %d-byte aligned", (int)(a)); \
+    } while (0)
+
+extern "C" {
+
+int sk_abi_version(void) { return SK_ABI_VERSION; }
+
+const char* sk_status_string(int status) {
+    switch (status) {
+        case SK_OK: return "ok";
+        case SK_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case SK_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+        case SK_ERR_MISALIGNED: return "misaligned pointer or stride";
+        case SK_ERR_WORKSPACE: return "workspace too small";
+        case SK_ERR_CUDA: return "CUDA runtime error";
+        default: return "unknown status";
+    }
+}
+
+const char* sk_last_error(void) { return g_err; }
+
+int sk_hash_keys(const void* keys, int key_dtype, int64_t key_row_stride, const void* planes,
+                 int plane_dtype, int64_t N, int D, int L, int P, void* codes, int code_bytes,
+                 int64_t code_row_stride, void* stream) {
+    SK_REQUIRE(N >= 0 && D > 0 && L > 0 && P > 0, "sk_hash_keys: sizes must be positive");
+    if (N == 0) return SK_OK;
+    SK_REQUIRE(keys && planes && codes, "sk_hash_keys: null pointer");
+    SK_REQUIRE(valid_dtype(key_dtype) && valid_dtype(plane_dtype), "sk_hash_keys: bad dtype");
+    SK_REQUIRE(code_bytes == 1 || code_bytes == 2, "sk_hash_keys: code_bytes must be 1 or 2");
+    SK_REQUIRE(P <= (code_bytes == 1 ? 8 : 15), "sk_hash_keys: P=%d does not fit %d-byte codes", P, code_bytes);
+    SK_REQUIRE(key_row_stride >= D && code_row_stride >= L, "sk_hash_keys: row stride smaller than row");
+    return launch_hash_keys(keys, key_dtype, key_row_stride, planes, plane_dtype, N, D, L, P, codes,
+                            code_bytes, code_row_stride, (cudaStream_t)stream);
+}
+
+int sk_kv_append(const void* k_new, const void* v_new, int kv_dtype, const int64_t* input_pos,
+                 const void* planes, int plane_dtype, void* k_cache, void* v_cache,
+                 uint8_t* codes, uint16_t* v_norm, int32_t* prefill_len, int32_t* status, int B,
+                 int S, int Hkv, int D, int64_t Tcap, int L, int P, void* stream) {
+    SK_REQUIRE(B >= 0 && S >= 0 && Hkv > 0 && D > 0 && Tcap > 0 && L > 0 && P > 0,
+               "sk_kv_append: sizes must be positive");
+    if (B == 0 || S == 0) return SK_OK;
+    SK_REQUIRE(k_new && v_new && input_pos && planes && k_cache && v_cache && codes && v_norm && prefill_len,
+               "sk_kv_append: null pointer");
+    SK_REQUIRE(valid_dtype(kv_dtype) && valid_dtype(plane_dtype), "sk_kv_append: bad dtype");
+    SK_REQUIRE(P <= 8, "sk_kv_append: the cache stores uint8 codes, P must be <= 8 (got %d)", P);
+    return launch_kv_append(k_new, v_new, kv_dtype, input_pos, planes, plane_dtype, k_cache, v_cache,
+                            codes, v_norm, prefill_len, status, B, S, Hkv, D, Tcap, L, P,
+                            (cudaStream_t)stream);
+}
+
+int sk_lut_head_tile(int rep) { return rep > 0 ? lut_head_tile(rep) : 0; }
+
+int sk_soft_hash(const void* q, int q_dtype, const void* planes, int plane_dtype,
+                 const float* protos_T, float temperature, int B, int H, int Hkv, int D, int L,
+                 int P, int R, float* q_probs, float* lut, void* stream) {
+    SK_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && D > 0 && L > 0 && P > 0 && R > 0,
+               "sk_soft_hash: sizes must be positive");
+    if (B == 0) return SK_OK;
+    SK_REQUIRE(H % Hkv == 0, "sk_soft_hash: H=%d not a multiple of Hkv=%d", H, Hkv);
+    SK_REQUIRE(q && planes && protos_T, "sk_soft_hash: null pointer");
+    SK_REQUIRE(q_probs || lut, "sk_soft_hash: no output requested");
+    SK_REQUIRE(valid_dtype(q_dtype) && valid_dtype(plane_dtype), "sk_soft_hash: bad dtype");
+    SK_REQUIRE(temperature > 0.f, "sk_soft_hash: temperature must be positive");
+    return launch_soft_hash(q, q_dtype, planes, plane_dtype, protos_T, temperature, B, H, Hkv, D, L, P,
+                            R, q_probs, lut, (cudaStream_t)stream);
+}
+
+int sk_lut_from_probs(const void* q_probs, int dtype, int B, int H, int Hkv, int L, int R,
+                      float* lut, void* stream) {
+    SK_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && L > 0 && R > 0, "sk_lut_from_probs: sizes must be positive");
+    if (B == 0) return SK_OK;
+    SK_REQUIRE(H % Hkv == 0, "sk_lut_from_probs: H=%d not a multiple of Hkv=%d", H, Hkv);
+    SK_REQUIRE(q_probs && lut, "sk_lut_from_probs: null pointer");
+    SK_REQUIRE(valid_dtype(dtype), "sk_lut_from_probs: bad dtype");
+    return launch_lut_from_probs(q_probs, dtype, B, H, Hkv, L, R, lut, (cudaStream_t)stream);
+}
+
+int sk_score(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
+             const uint8_t* allowed, int B, int H, int Hkv, int L, int R, int64_t T,
+             const int32_t* T_dev, int64_t Tcap, float* scores, int64_t score_row_stride,
+             int32_t* status, void* stream) {
+    SK_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && L > 0 && R > 0 && T >= 0, "sk_score: sizes must be positive");
+    if (B == 0 || T == 0) return SK_OK;
+    SK_REQUIRE(H % Hkv == 0, "sk_score: H=%d not a multiple of Hkv=%d", H, Hkv);
+    SK_REQUIRE(lut && codes && v_norm && scores, "sk_score: null pointer");
+    SK_REQUIRE(T <= Tcap, "sk_score: T=%lld exceeds cache capacity %lld", (long long)T, (long long)Tcap);
+    SK_REQUIRE(R <= 256, "sk_score: uint8 codes need R <= 256 (got %d)", R);
+    SK_REQUIRE(score_row_stride >= T, "sk_score: score_row_stride smaller than T");
+    SK_ALIGNED(lut, 16, "sk_score: lut");
+    SK_ALIGNED(codes, 16, "sk_score: codes");
+    if (L % 16 != 0) return fail(SK_ERR_UNSUPPORTED, "sk_score: L=%d must be a multiple of 16", L);
+    return launch_score(lut, codes, v_norm, allowed, B, H, Hkv, L, R, T, T_dev, Tcap, scores,
+                        score_row_stride, status, (cudaStream_t)stream);
+}
+
+int sk_score_compat(const float* q_probs, const int16_t* key_buckets, const uint8_t* allowed,
+                    const float* v_hist, float* out, int B, int H, int L, int R, int64_t T,
+                    void* stream) {
+    SK_REQUIRE(B >= 0 && H >= 0 && L > 0 && R > 0 && T >= 0, "sk_score_compat: sizes must be positive");
+    if (B == 0 || H == 0 || T == 0) return SK_OK;
+    SK_REQUIRE(q_probs && key_buckets && allowed && v_hist && out, "sk_score_compat: null pointer");
+    SK_REQUIRE((int64_t)B * H <= 65535, "sk_score_compat: B*H > 65535");
+    return launch_score_compat(q_probs, key_buckets, allowed, v_hist, out, B, H, L, R, T,
+                               (cudaStream_t)stream);
+}
+
+int64_t sk_list_len(int64_t T, int sink, int window, int64_t M) { return list_len_host(T, sink, window, M); }
+
+int sk_select_list(const float* scores, int64_t score_row_stride, const uint8_t* allowed,
+                   int64_t rows, int64_t T, const int32_t* T_dev, int64_t M, int sink,
+                   int window, int sorted, int32_t* list, int64_t list_row_stride,
+                   int32_t* list_len, int32_t* status, void* stream) {
+    SK_REQUIRE(rows >= 0 && T >= 0 && M >= 0, "sk_select_list: sizes must be non-negative");
+    if (rows == 0) return SK_OK;
+    SK_REQUIRE(scores && list && list_len, "sk_select_list: null pointer");
+    SK_REQUIRE(score_row_stride >= T, "sk_select_list: score_row_stride smaller than T");
+    SK_REQUIRE(list_row_stride >= list_len_host(T, sink, window, M),
+               "sk_select_list: list_row_stride %lld smaller than the list length %lld",
+               (long long)list_row_stride, (long long)list_len_host(T, sink, window, M));
+    return launch_select_list(scores, score_row_stride, allowed, rows, T, T_dev, M, sink, window, sorted,
+                              list, list_row_stride, list_len, status, (cudaStream_t)stream);
+}
+
+size_t sk_sparse_decode_workspace_bytes(int B, int H, int D, int64_t max_list_len) {
+    return sparse_decode_workspace_bytes(B, H, D, max_list_len);
+}
+
+int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, const void* v_cache,
+                     int kv_dtype, int64_t kv_batch_stride, int64_t kv_head_stride,
+                     int64_t kv_row_stride, const int32_t* list, int64_t list_row_stride,
+                     const int32_t* list_len, int64_t max_list_len, void* out, int B, int H,
+                     int Hkv, int D, int64_t T, const int32_t* T_dev, void* workspace,
+                     size_t workspace_bytes, int32_t* status, void* stream) {
+    SK_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && D > 0 && T >= 0, "sk_sparse_decode: sizes must be positive");
+    if (B == 0) return SK_OK;
+    SK_REQUIRE(H % Hkv == 0, "sk_sparse_decode: H=%d not a multiple of Hkv=%d", H, Hkv);
+    SK_REQUIRE(q && k_cache && v_cache && list && list_len && out && workspace, "sk_sparse_decode: null pointer");
+    SK_REQUIRE(valid_dtype(q_dtype) && valid_dtype(kv_dtype), "sk_sparse_decode: bad dtype");
+    SK_REQUIRE(list_row_stride >= max_list_len, "sk_sparse_decode: list_row_stride smaller than max_list_len");
+    SK_ALIGNED(q, 16, "sk_sparse_decode: q");
+    SK_ALIGNED(k_cache, 16, "sk_sparse_decode: k_cache");
+    SK_ALIGNED(v_cache, 16, "sk_sparse_decode: v_cache");
+    SK_ALIGNED(workspace, 256, "sk_sparse_decode: workspace");
+    const int64_t per16 = 16 / (int64_t)esize(kv_dtype);
+    if (kv_batch_stride % per16 || kv_head_stride % per16 || kv_row_stride % per16)
+        return fail(SK_ERR_MISALIGNED, "sk_sparse_decode: K/V strides must be multiples of 16 bytes");
+    return launch_sparse_decode(q, q_dtype, k_cache, v_cache, kv_dtype, kv_batch_stride, kv_head_stride,
+                                kv_row_stride, list, list_row_stride, list_len, max_list_len, out, B, H,
+                                Hkv, D, T, T_dev, workspace, workspace_bytes, status,
+                                (cudaStream_t)stream);
+}
+
+/* Workspace of one fused step: [decode scratch | table | scores | list | list_len] */
+struct StepLayout {
+    size_t dec, lut, scores, list, len, total;
+    int64_t score_stride, list_stride;
+};
+
+static StepLayout step_layout(int B, int H, int D, int L, int R, int64_t T_max, int64_t M, int sink,
+                              int window) {
+    StepLayout s;
+    s.list_stride = list_len_host(T_max, sink, window, M);
+    if (s.list_stride < 1) s.list_stride = 1;
+    s.score_stride = (T_max + 3) / 4 * 4;
+    size_t off = 0;
+    s.dec = off;    off += up256(sparse_decode_workspace_bytes(B, H, D, s.list_stride));
+    s.lut = off;    off += up256((size_t)B * H * L * R * sizeof(float));
+    s.scores = off; off += up256((size_t)B * H * s.score_stride * sizeof(float));
+    s.list = off;   off += up256((size_t)B * H * s.list_stride * sizeof(int32_t));
+    s.len = off;    off += up256((size_t)B * H * sizeof(int32_t));
+    s.total = off;
+    return s;
+}
+
+size_t sk_decode_step_workspace_bytes(int B, int H, int Hkv, int D, int L, int R, int64_t T_max,
+                                      int64_t M, int sink, int window) {
+    (void)Hkv;
+    if (B <= 0 || H <= 0 || T_max <= 0) return 256;
+    return step_layout(B, H, D, L, R, T_max, M, sink, window).total;
+}
+
+int sk_decode_step(const sk_decode_params* p, void* stream) {
+    SK_REQUIRE(p != nullptr, "sk_decode_step: null params");
+    SK_REQUIRE(p->B > 0 && p->H > 0 && p->Hkv > 0 && p->D > 0 && p->L > 0 && p->P > 0 && p->R > 0,
+               "sk_decode_step: sizes must be positive");
+    SK_REQUIRE(p->H % p->Hkv == 0, "sk_decode_step: H not a multiple of Hkv");
+    SK_REQUIRE(p->T_max > 0 && p->T_max <= p->Tcap, "sk_decode_step: T_max must be in (0, Tcap]");
+    SK_REQUIRE(p->q && p->planes && p->protos_T && p->k_cache && p->v_cache && p->codes && p->v_norm &&
+                   p->prefill_len && p->out && p->workspace,
+               "sk_decode_step: null pointer");
+    SK_REQUIRE((p->k_new == nullptr) == (p->v_new == nullptr), "sk_decode_step: k_new and v_new go together");
+    SK_REQUIRE(p->k_new == nullptr || p->input_pos != nullptr, "sk_decode_step: input_pos missing");
+    SK_REQUIRE((p->list == nullptr) == (p->list_len == nullptr), "sk_decode_step: list and list_len go together");
+    SK_ALIGNED(p->workspace, 256, "sk_decode_step: workspace");
+    const StepLayout lay = step_layout(p->B, p->H, p->D, p->L, p->R, p->T_max, p->M, p->sink, p->window);
+    if (p->workspace_bytes < lay.total)
+        return fail(SK_ERR_WORKSPACE, "sk_decode_step: workspace %zu < %zu bytes", p->workspace_bytes, lay.total);
+    SK_REQUIRE(p->list == nullptr || p->list_row_stride >= lay.list_stride,
+               "sk_decode_step: list_row_stride smaller than the list length %lld", (long long)lay.list_stride);
+    cudaStream_t st = (cudaStream_t)stream;
+    char* ws = static_cast<char*>(p->workspace);
+    float* lut = reinterpret_cast<float*>(ws + lay.lut);
+    float* scores = reinterpret_cast<float*>(ws + lay.scores);
+    int32_t* list = p->list ? p->list : reinterpret_cast<int32_t*>(ws + lay.list);
+    int32_t* list_len = p->list ? p->list_len : reinterpret_cast<int32_t*>(ws + lay.len);
+    const int64_t list_stride = p->list ? p->list_row_stride : lay.list_stride;
+    int rc;
+    if (p->k_new != nullptr) {
+        rc = sk_kv_append(p->k_new, p->v_new, p->kv_dtype, p->input_pos, p->planes, p->plane_dtype,
+                          p->k_cache, p->v_cache, p->codes, p->v_norm, p->prefill_len, p->status, p->B, 1,
+                          p->Hkv, p->D, p->Tcap, p->L, p->P, stream);
+        if (rc != SK_OK) return rc;
+    }
+    rc = sk_soft_hash(p->q, p->q_dtype, p->planes, p->plane_dtype, p->protos_T, p->temperature, p->B, p->H,
+                      p->Hkv, p->D, p->L, p->P, p->R, nullptr, lut, stream);
+    if (rc != SK_OK) return rc;
+    rc = sk_score(lut, p->codes, p->v_norm, nullptr, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
+                  p->prefill_len, p->Tcap, scores, lay.score_stride, p->status, stream);
+    if (rc != SK_OK) return rc;
+    rc = sk_select_list(scores, lay.score_stride, nullptr, (int64_t)p->B * p->H, p->T_max, p->prefill_len,
+                        p->M, p->sink, p->window, 0, list, list_stride, list_len, p->status, stream);
+    if (rc != SK_OK) return rc;
+    const int64_t kv_hs = p->Tcap * p->D;
+    rc = launch_sparse_decode(p->q, p->q_dtype, p->k_cache, p->v_cache, p->kv_dtype, kv_hs * p->Hkv, kv_hs,
+                              p->D, list, list_stride, list_len, lay.list_stride, p->out, p->B, p->H,
+                              p->Hkv, p->D, p->T_max, p->prefill_len, ws + lay.dec,
+                              up256(sparse_decode_workspace_bytes(p->B, p->H, p->D, lay.list_stride)),
+                              p->status, st);
+    return rc;
+}
+
+}  // extern "C"

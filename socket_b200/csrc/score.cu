@@ -1,0 +1,317 @@
+// Soft-collision scorer: streams the uint8 bucket codes of every cached key and sums, per
+// table, the query's probability mass on that bucket.
+//
+// Data movement: the scorer table of one (KV head, head tile) — R*L*ht floats, 128 KiB for
+// R=256, L=32, ht=4 — is brought into shared memory once per CTA by bulk asynchronous copies
+// (cp.async.bulk completing on an mbarrier); the code array is then streamed with 16-byte
+// loads, one key (L bytes) per thread, and never re-read: all ht query heads of the KV head
+// are scored from one pass.
+//
+// Shared-memory bandwidth is the limiter (one 16-byte word per key and table), so the
+// lookups are arranged to be bank-conflict free for ht = 4: the table is stored
+// [bucket][table][head], which puts table l in 16-byte bank group l mod 8, and the 8 lanes
+// of a quarter warp walk the tables of each group of 8 in a different order
+// (table = j ^ (lane & 7)), so that at every step they hit 8 distinct bank groups whatever
+// the bucket values are.  The permutation is applied to the code bytes with two PRMTs per
+// 8 bytes.  Consequence: the L terms of a score are added in a lane-dependent order; the
+// result differs from the ascending-order sum by fp32 rounding only (~1e-7 relative).
+#include "common.cuh"
+
+namespace sk {
+namespace {
+
+constexpr int SC_THREADS = 1024;
+constexpr int SC_WARPS = SC_THREADS / 32;
+constexpr uint32_t SC_WAIT_LIMIT = 1u << 20;   // bounded wait on the table copy
+constexpr int SC_COPY_CHUNK = 16384;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+            "r"(smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+// Returns false if the phase did not complete within the iteration limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < SC_WAIT_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+template <int HT> struct Word;
+template <> struct Word<4> { using type = float4; };
+template <> struct Word<2> { using type = float2; };
+template <> struct Word<1> { using type = float; };
+
+template <int HT>
+__device__ __forceinline__ void add_word(float (&acc)[HT], const char* p) {
+    if constexpr (HT == 4) {
+        const float4 w = *reinterpret_cast<const float4*>(p);
+        acc[0] += w.x; acc[1] += w.y; acc[2] += w.z; acc[3] += w.w;
+    } else if constexpr (HT == 2) {
+        const float2 w = *reinterpret_cast<const float2*>(p);
+        acc[0] += w.x; acc[1] += w.y;
+    } else {
+        acc[0] += *reinterpret_cast<const float*>(p);
+    }
+}
+
+// L: tables per key (bytes per key), HT: query heads per table word.
+template <int L, int HT>
+__global__ void __launch_bounds__(SC_THREADS, 1)
+score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
+             const __half* __restrict__ v_norm, const uint8_t* __restrict__ allowed,
+             float* __restrict__ scores, int64_t score_row_stride, int H, int Hkv, int R,
+             int64_t T, const int32_t* __restrict__ T_dev, int64_t Tcap, int64_t Tslots,
+             int64_t slots_per_cta, int n_groups, int32_t* status) {
+    static_assert(L % 16 == 0, "codes are read 16 bytes at a time");
+    constexpr int NV = L / 16;                 // uint4 per key
+    constexpr int L_STRIDE = HT * 4;           // bytes between tables of one bucket
+    constexpr int CODE_STRIDE = L * L_STRIDE;  // bytes between buckets
+    extern __shared__ __align__(128) char smem_raw[];
+    char* lut_s = smem_raw;
+    // room for all 256 possible code values, so that no byte value can index past the table
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw + (size_t)256 * CODE_STRIDE);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rep = H / Hkv;
+    const int tiles = rep / HT;
+    const int Teff = effective_len(T, T_dev);
+    const uint32_t lut_bytes = (uint32_t)R * CODE_STRIDE;
+
+    const int m = lane & 7;
+    const uint32_t sel_lo = 0x3210u ^ (0x1111u * m);
+    const uint32_t sel_hi = 0x7654u ^ (0x1111u * m);
+    const uint32_t mL = (uint32_t)m * L_STRIDE;
+
+    if (threadIdx.x == 0) mbar_init(bar, 1);
+    __syncthreads();
+
+    const int64_t total = (int64_t)n_groups * Tslots;
+    int64_t slot = (int64_t)blockIdx.x * slots_per_cta;
+    const int64_t slot_end = min(slot + slots_per_cta, total);
+    uint32_t phase = 0;
+
+    while (slot < slot_end) {
+        const int g = (int)(slot / Tslots);
+        const int64_t t0 = slot - (int64_t)g * Tslots;
+        const int64_t seg_end = min((int64_t)(g + 1) * Tslots, slot_end);
+        int64_t t1 = seg_end - (int64_t)g * Tslots;
+        slot = seg_end;
+        if (t1 > Teff) t1 = Teff;
+        if (t0 >= t1) continue;   // uniform across the CTA
+
+        const int tile = g % tiles;
+        const int bk = g / tiles;               // b*Hkv + kvh
+        const int b = bk / Hkv, kvh = bk - b * Hkv;
+        const int h0 = kvh * rep + tile * HT;
+
+        // previous segment's lookups are done before the table is overwritten
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(bar, lut_bytes);
+            const char* src = reinterpret_cast<const char*>(lut) + (size_t)g * lut_bytes;
+            for (uint32_t off = 0; off < lut_bytes; off += SC_COPY_CHUNK) {
+                const uint32_t n = min((uint32_t)SC_COPY_CHUNK, lut_bytes - off);
+                bulk_g2s(lut_s + off, src + off, n, bar);
+            }
+        }
+        const bool ok = mbar_wait(bar, phase);
+        phase ^= 1u;
+        if (!__syncthreads_and(ok)) {
+            if (threadIdx.x == 0 && status != nullptr) atomicOr(status, SK_DEV_WAIT_TIMEOUT);
+            return;
+        }
+
+        const uint4* cg = reinterpret_cast<const uint4*>(codes + (size_t)bk * Tcap * L);
+        const __half* vg = v_norm + (size_t)bk * Tcap;
+        const int64_t n_pieces = (t1 - t0 + 31) / 32;
+
+        uint4 cur[NV], nxt[NV];
+        int64_t piece = warp;
+        {
+            const int64_t t = t0 + piece * 32 + lane;
+            if (piece < n_pieces && t < t1) {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) cur[i] = __ldg(cg + t * NV + i);
+            }
+        }
+        for (; piece < n_pieces; piece += SC_WARPS) {
+            const int64_t t = t0 + piece * 32 + lane;
+            const int64_t tn = t + (int64_t)SC_WARPS * 32;
+            if (piece + SC_WARPS < n_pieces && tn < t1) {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + tn * NV + i);
+            }
+            if (t < t1) {
+                float acc[HT];
+#pragma unroll
+                for (int j = 0; j < HT; ++j) acc[j] = 0.f;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    const uint32_t w[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        // 8 tables: bytes permuted so that byte j holds table j ^ m
+                        const uint32_t lo = __byte_perm(w[2 * half], w[2 * half + 1], sel_lo);
+                        const uint32_t hi = __byte_perm(w[2 * half], w[2 * half + 1], sel_hi);
+                        const int lbase = (i * 16 + half * 8) * L_STRIDE;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t src = j < 4 ? lo : hi;
+                            const uint32_t code = (src >> (8 * (j & 3))) & 0xffu;
+                            const uint32_t off = code * CODE_STRIDE + (((uint32_t)j * L_STRIDE) ^ mL);
+                            add_word<HT>(acc, lut_s + lbase + off);
+                        }
+                    }
+                }
+                const float vn = __half2float(vg[t]);
+#pragma unroll
+                for (int j = 0; j < HT; ++j) {
+                    const size_t row = (size_t)b * H + h0 + j;
+                    float s = acc[j] * vn;
+                    if (allowed != nullptr && allowed[row * T + t] == 0) s = -INFINITY;
+                    scores[row * score_row_stride + t] = s;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
+        }
+    }
+}
+
+// Reference-surface scorer: [B,H,L,T] int16 codes, ascending-table summation.
+__global__ void __launch_bounds__(256)
+score_compat_kernel(const float* __restrict__ q_probs, const int16_t* __restrict__ key_buckets,
+                    const uint8_t* __restrict__ allowed, const float* __restrict__ v_hist,
+                    float* __restrict__ out, int L, int R, int64_t T, int use_smem) {
+    extern __shared__ float qp_s[];
+    const int bh = blockIdx.y;
+    const float* qp = q_probs + (size_t)bh * L * R;
+    if (use_smem) {
+        for (int i = threadIdx.x; i < L * R; i += blockDim.x) qp_s[i] = qp[i];
+        __syncthreads();
+    }
+    const int16_t* kb = key_buckets + (size_t)bh * L * T;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < T;
+         t += (int64_t)gridDim.x * blockDim.x) {
+        const size_t o = (size_t)bh * T + t;
+        if (allowed[o] == 0) {
+            out[o] = -INFINITY;
+            continue;
+        }
+        float s = 0.f;
+        for (int l = 0; l < L; ++l) {
+            const int r = (int)kb[(size_t)l * T + t];
+            s += use_smem ? qp_s[l * R + r] : __ldg(qp + (size_t)l * R + r);
+        }
+        out[o] = s * v_hist[o];
+    }
+}
+
+template <int L, int HT>
+int score_launch(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
+                 const uint8_t* allowed, int B, int H, int Hkv, int R, int64_t T,
+                 const int32_t* T_dev, int64_t Tcap, float* scores, int64_t srs, int32_t* status,
+                 cudaStream_t st) {
+    const int rep = H / Hkv;
+    const int n_groups = B * Hkv * (rep / HT);
+    const size_t smem = (size_t)256 * L * HT * 4 + 16;
+    auto kern = score_kernel<L, HT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "score_kernel smem attribute: %s", cudaGetErrorString(e));
+    int n_sm = 148;
+    int64_t Tslots, per_cta;
+    int64_t grid;
+    const int64_t total = (int64_t)n_groups * T;
+    if (total / n_sm >= 16384) {
+        // large: split the flat (group, key) space evenly; a CTA may cross one group boundary
+        Tslots = T;
+        per_cta = (total + n_sm - 1) / n_sm;
+        per_cta = (per_cta + 31) / 32 * 32;
+        grid = (total + per_cta - 1) / per_cta;
+    } else {
+        // small: whole CTAs per group, no CTA loads two tables
+        int64_t chunks = n_groups >= n_sm ? 1 : n_sm / n_groups;
+        const int64_t max_chunks = (T + 1023) / 1024;
+        if (chunks > max_chunks) chunks = max_chunks;
+        per_cta = (T + chunks - 1) / chunks;
+        per_cta = (per_cta + 31) / 32 * 32;
+        chunks = (T + per_cta - 1) / per_cta;
+        Tslots = chunks * per_cta;
+        grid = (int64_t)n_groups * chunks;
+    }
+    kern<<<(unsigned)grid, SC_THREADS, smem, st>>>(lut, codes, (const __half*)v_norm, allowed, scores,
+                                                   srs, H, Hkv, R, T, T_dev, Tcap, Tslots, per_cta,
+                                                   n_groups, status);
+    return check_launch("score_kernel");
+}
+
+}  // namespace
+
+int launch_score(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
+                 const uint8_t* allowed, int B, int H, int Hkv, int L, int R, int64_t T,
+                 const int32_t* T_dev, int64_t Tcap, float* scores, int64_t score_row_stride,
+                 int32_t* status, cudaStream_t st) {
+    if (T <= 0 || B * H == 0) return SK_OK;
+    const int ht = lut_head_tile(H / Hkv);
+    if ((size_t)256 * L * ht * 4 + 16 > 227 * 1024)
+        return fail(SK_ERR_UNSUPPORTED, "sk_score: table of R=%d L=%d does not fit shared memory", R, L);
+#define SK_SCORE_CASE(LL, HT)                                                                    \
+    if (L == LL && ht == HT)                                                                     \
+        return score_launch<LL, HT>(lut, codes, v_norm, allowed, B, H, Hkv, R, T, T_dev, Tcap,   \
+                                    scores, score_row_stride, status, st)
+    SK_SCORE_CASE(32, 4);
+    SK_SCORE_CASE(32, 2);
+    SK_SCORE_CASE(32, 1);
+    SK_SCORE_CASE(16, 4);
+    SK_SCORE_CASE(16, 2);
+    SK_SCORE_CASE(16, 1);
+    SK_SCORE_CASE(64, 2);
+    SK_SCORE_CASE(64, 1);
+#undef SK_SCORE_CASE
+    return fail(SK_ERR_UNSUPPORTED, "sk_score: L=%d with %d heads per KV head not supported", L, H / Hkv);
+}
+
+int launch_score_compat(const float* q_probs, const int16_t* key_buckets, const uint8_t* allowed,
+                        const float* v_hist, float* out, int B, int H, int L, int R, int64_t T,
+                        cudaStream_t st) {
+    if (T <= 0 || B * H == 0) return SK_OK;
+    const size_t smem = (size_t)L * R * 4;
+    const int use_smem = smem <= 160 * 1024;
+    if (use_smem && smem > 48 * 1024)
+        cudaFuncSetAttribute(score_compat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int64_t gx = (T + 255) / 256;
+    if (gx > 1024) gx = 1024;
+    dim3 grid((unsigned)gx, (unsigned)(B * H));
+    score_compat_kernel<<<grid, 256, use_smem ? smem : 0, st>>>(q_probs, key_buckets, allowed, v_hist,
+                                                                out, L, R, T, use_smem);
+    return check_launch("score_compat_kernel");
+}
+
+}  // namespace sk

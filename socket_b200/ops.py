@@ -1,0 +1,273 @@
+"""Tensor-level wrappers of the C-ABI entry points.
+
+Each function checks what the reference checks at the same place (device, dtype, shape,
+contiguity — `TORCH_CHECK`s of GPT-FAST/kernels/soft_hash_collision_loader.py:22-58 and the
+asserts of GPT-FAST/kernels/sparse.py:29-35), allocates the outputs with torch and enqueues
+the kernels on torch's current stream.  No function here synchronises with the host, and
+none has a CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check, dtype_code, lib, ptr, stream_ptr
+
+_workspaces = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch, one buffer per (device, stream), grown on demand.  The
+    decode kernel leaves its ticket counters at zero, so the buffer is only cleared when
+    it is (re)allocated."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("socket_b200 operators need CUDA tensors (there is no CPU path)")
+
+
+def list_len(T: int, sink: int, window: int, M: int) -> int:
+    return int(lib().sk_list_len(T, sink, window, M))
+
+
+def hash_keys(keys: torch.Tensor, planes: torch.Tensor, code_dtype=torch.uint8) -> torch.Tensor:
+    """keys [..., D] -> bucket codes [..., L] (uint8, or int16 like the reference)."""
+    _require_cuda(keys, planes)
+    L, P, D = planes.shape
+    if keys.shape[-1] != D:
+        raise RuntimeError(f"keys last dim {keys.shape[-1]} != planes head_dim {D}")
+    keys = keys.contiguous()
+    planes = planes.contiguous()
+    N = keys.numel() // D
+    code_bytes = {torch.uint8: 1, torch.int16: 2}[code_dtype]
+    codes = torch.empty(*keys.shape[:-1], L, dtype=code_dtype, device=keys.device)
+    check(lib().sk_hash_keys(ptr(keys), dtype_code(keys), D, ptr(planes), dtype_code(planes), N, D, L,
+                             P, ptr(codes), code_bytes, L, stream_ptr(keys.device)), "sk_hash_keys")
+    return codes
+
+
+def kv_append(k_cache, v_cache, codes, v_norm, prefill_len, input_pos, k_new, v_new, planes,
+              status: Optional[torch.Tensor] = None) -> None:
+    """Write S new tokens (k_new/v_new [B,S,Hkv,D]) at `input_pos` [S] (int64, device) into
+    the cache tensors, with their bucket codes and value norms."""
+    _require_cuda(k_cache, v_cache, codes, v_norm, prefill_len, input_pos, k_new, v_new, planes)
+    B, Hkv, Tcap, D = k_cache.shape
+    L, P, _ = planes.shape
+    S = k_new.shape[1]
+    assert k_new.shape == (B, S, Hkv, D) and v_new.shape == (B, S, Hkv, D)
+    assert input_pos.dtype == torch.int64 and input_pos.numel() == S
+    assert codes.dtype == torch.uint8 and codes.shape == (B, Hkv, Tcap, L)
+    assert v_norm.dtype == torch.float16 and v_norm.shape == (B, Hkv, Tcap)
+    assert k_new.dtype == k_cache.dtype == v_cache.dtype == v_new.dtype
+    for t in (k_cache, v_cache, codes, v_norm):
+        assert t.is_contiguous()
+    k_new = k_new.contiguous()
+    v_new = v_new.contiguous()
+    planes = planes.contiguous()
+    check(lib().sk_kv_append(ptr(k_new), ptr(v_new), dtype_code(k_new), ptr(input_pos), ptr(planes),
+                             dtype_code(planes), ptr(k_cache), ptr(v_cache), ptr(codes), ptr(v_norm),
+                             ptr(prefill_len), ptr(status), B, S, Hkv, D, Tcap, L, P,
+                             stream_ptr(k_cache.device)), "sk_kv_append")
+
+
+def soft_hash(q_bhd: torch.Tensor, planes: torch.Tensor, protos_T: torch.Tensor,
+              temperature: float = 1.0, n_kv_heads: Optional[int] = None,
+              want_probs: bool = True, want_lut: bool = False):
+    """q [B,H,D] -> (q_probs [B,H,L,R] fp32 or None, scorer table or None)."""
+    _require_cuda(q_bhd, planes, protos_T)
+    B, H, D = q_bhd.shape
+    L, P, D2 = planes.shape
+    assert D2 == D
+    R = protos_T.shape[1]
+    assert protos_T.shape[0] == P
+    Hkv = n_kv_heads if n_kv_heads is not None else H
+    q = q_bhd.contiguous()
+    planes = planes.contiguous()
+    protos = protos_T.to(torch.float32).contiguous()
+    probs = torch.empty(B, H, L, R, dtype=torch.float32, device=q.device) if want_probs else None
+    lut = torch.empty(B * H * L * R, dtype=torch.float32, device=q.device) if want_lut else None
+    check(lib().sk_soft_hash(ptr(q), dtype_code(q), ptr(planes), dtype_code(planes), ptr(protos),
+                             float(temperature), B, H, Hkv, D, L, P, R, ptr(probs), ptr(lut),
+                             stream_ptr(q.device)), "sk_soft_hash")
+    return probs, lut
+
+
+def lut_from_probs(q_probs: torch.Tensor, n_kv_heads: int) -> torch.Tensor:
+    _require_cuda(q_probs)
+    B, H, L, R = q_probs.shape
+    q_probs = q_probs.contiguous()
+    lut = torch.empty(B * H * L * R, dtype=torch.float32, device=q_probs.device)
+    check(lib().sk_lut_from_probs(ptr(q_probs), dtype_code(q_probs), B, H, n_kv_heads, L, R, ptr(lut),
+                                  stream_ptr(q_probs.device)), "sk_lut_from_probs")
+    return lut
+
+
+def score(lut: torch.Tensor, codes: torch.Tensor, v_norm: torch.Tensor, n_heads: int, T: int,
+          R: int = 256, allowed: Optional[torch.Tensor] = None,
+          T_dev: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+          status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """codes [B,Hkv,Tcap,L] uint8, v_norm [B,Hkv,Tcap] fp16 -> scores [B,H,T] fp32."""
+    _require_cuda(lut, codes, v_norm, allowed)
+    B, Hkv, Tcap, L = codes.shape
+    assert codes.dtype == torch.uint8 and codes.is_contiguous()
+    assert v_norm.dtype == torch.float16 and v_norm.is_contiguous() and v_norm.shape == (B, Hkv, Tcap)
+    if allowed is not None:
+        assert allowed.shape == (B, n_heads, T)
+        allowed = allowed.to(torch.uint8).contiguous() if allowed.dtype != torch.uint8 else allowed.contiguous()
+    if out is None:
+        out = torch.empty(B, n_heads, T, dtype=torch.float32, device=codes.device)
+    assert out.dtype == torch.float32 and out.stride(2) == 1 and out.stride(0) == n_heads * out.stride(1)
+    check(lib().sk_score(ptr(lut), ptr(codes), ptr(v_norm), ptr(allowed), B, n_heads, Hkv, L, R, T,
+                         ptr(T_dev), Tcap, ptr(out), out.stride(1), ptr(status),
+                         stream_ptr(codes.device)), "sk_score")
+    return out
+
+
+def soft_hash_collision(q_probs: torch.Tensor, key_buckets: torch.Tensor, allowed_ext: torch.Tensor,
+                        v_hist: torch.Tensor) -> torch.Tensor:
+    """Same call as the reference's scorer extension
+    (GPT-FAST/kernels/soft_hash_collision_loader.py:16-72): q_probs [B,H,1,L,R] fp32,
+    key_buckets [B,H,L,T] int16, allowed_ext [B,H,1,T] bool, v_hist [B,H,1,T] fp32 ->
+    [B,H,1,T] fp32.  Same checks, same RuntimeError on violation."""
+    for name, t in (("q_probs", q_probs), ("key_buckets", key_buckets),
+                    ("allowed_ext", allowed_ext), ("v_hist", v_hist)):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be CUDA")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{name} must be contiguous")
+    if q_probs.dtype != torch.float32:
+        raise RuntimeError("q_probs must be float32")
+    if key_buckets.dtype != torch.int16:
+        raise RuntimeError("key_buckets must be int16")
+    if allowed_ext.dtype != torch.bool:
+        raise RuntimeError("allowed_ext must be bool")
+    if v_hist.dtype != torch.float32:
+        raise RuntimeError("v_hist must be float32")
+    if q_probs.dim() != 5:
+        raise RuntimeError("q_probs must be [B,H,1,L,R]")
+    if key_buckets.dim() != 4:
+        raise RuntimeError("key_buckets must be [B,H,L,T_k]")
+    if allowed_ext.dim() != 4:
+        raise RuntimeError("allowed_ext must be [B,H,1,T_k]")
+    if v_hist.dim() != 4:
+        raise RuntimeError("v_hist must be [B,H,1,T_k]")
+    B, H, _, L, R = q_probs.shape
+    T = key_buckets.shape[3]
+    if tuple(key_buckets.shape[:3]) != (B, H, L):
+        raise RuntimeError("key_buckets shape mismatch")
+    if tuple(allowed_ext.shape) != (B, H, 1, T):
+        raise RuntimeError("allowed_ext shape mismatch")
+    if tuple(v_hist.shape) != (B, H, 1, T):
+        raise RuntimeError("v_hist shape mismatch")
+    out = torch.empty(B, H, 1, T, dtype=torch.float32, device=q_probs.device)
+    check(lib().sk_score_compat(ptr(q_probs), ptr(key_buckets), ptr(allowed_ext), ptr(v_hist), ptr(out),
+                                B, H, L, R, T, stream_ptr(q_probs.device)), "sk_score_compat")
+    return out
+
+
+def select_list(scores: torch.Tensor, T: int, M: int, sink: int, window: int,
+                sorted_by_score: bool = False, allowed: Optional[torch.Tensor] = None,
+                T_dev: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """scores [B,H,>=T] fp32 -> (sparse_list int32 [B,H,Ktot], sparse_len int32 [B,H])."""
+    _require_cuda(scores, allowed)
+    B, H = scores.shape[:2]
+    assert scores.dtype == torch.float32 and scores.stride(2) == 1
+    assert scores.stride(0) == H * scores.stride(1)
+    if allowed is not None:
+        assert allowed.shape == (B, H, T)
+        allowed = allowed.to(torch.uint8).contiguous() if allowed.dtype != torch.uint8 else allowed.contiguous()
+    Ktot = list_len(T, sink, window, M)
+    lst = torch.empty(B, H, Ktot, dtype=torch.int32, device=scores.device)
+    ln = torch.empty(B, H, dtype=torch.int32, device=scores.device)
+    check(lib().sk_select_list(ptr(scores), scores.stride(1), ptr(allowed), B * H, T, ptr(T_dev), M, sink,
+                               window, int(sorted_by_score), ptr(lst), Ktot, ptr(ln), 0,
+                               stream_ptr(scores.device)), "sk_select_list")
+    return lst, ln
+
+
+def sparse_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  sparse_list: torch.Tensor, sparse_len: torch.Tensor, T: Optional[int] = None,
+                  T_dev: Optional[torch.Tensor] = None,
+                  status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [B,H,D]; k_cache/v_cache [B,Hkv,Tcap,D] (any strides with a unit last stride) ->
+    out [B,H,D] in q's dtype."""
+    _require_cuda(q, k_cache, v_cache, sparse_list, sparse_len)
+    B, H, D = q.shape
+    Hkv = k_cache.shape[1]
+    assert k_cache.shape == v_cache.shape and k_cache.stride() == v_cache.stride()
+    assert k_cache.stride(3) == 1 and k_cache.dtype == v_cache.dtype
+    assert sparse_list.dtype == torch.int32 and sparse_len.dtype == torch.int32
+    assert sparse_list.shape[:2] == (B, H) and sparse_len.shape == (B, H)
+    q = q.contiguous()
+    sparse_list = sparse_list.contiguous()
+    sparse_len = sparse_len.contiguous()
+    Kmax = sparse_list.shape[2]
+    if T is None:
+        T = k_cache.shape[2]
+    out = torch.empty(B, H, D, dtype=q.dtype, device=q.device)
+    if Kmax == 0:
+        return out.zero_()
+    need = int(lib().sk_sparse_decode_workspace_bytes(B, H, D, Kmax))
+    ws = _workspace(q.device, need)
+    check(lib().sk_sparse_decode(ptr(q), dtype_code(q), ptr(k_cache), ptr(v_cache), dtype_code(k_cache),
+                                 k_cache.stride(0), k_cache.stride(1), k_cache.stride(2),
+                                 ptr(sparse_list), Kmax, ptr(sparse_len), Kmax, ptr(out), B, H, Hkv, D, T,
+                                 ptr(T_dev), ptr(ws), ws.numel(), ptr(status), stream_ptr(q.device)),
+          "sk_sparse_decode")
+    return out
+
+
+class DecodeStep:
+    """One fused decode step of one layer (`sk_decode_step`): append+hash the new token,
+    soft-hash the query, score, select, attend — five launches on the current stream, no
+    host synchronisation, so it can be captured in a CUDA graph.  Holds the parameter
+    block and the scratch memory; `run()` re-enqueues the step on whatever the tensors
+    given at construction contain at that moment."""
+
+    def __init__(self, cache, q: torch.Tensor, k_new: Optional[torch.Tensor],
+                 v_new: Optional[torch.Tensor], input_pos: Optional[torch.Tensor],
+                 planes: torch.Tensor, protos_T: torch.Tensor, out: torch.Tensor, *, topk: int,
+                 sink: int, window: int, T_max: int, temperature: float = 1.0,
+                 keep_list: bool = False):
+        B, Hkv, Tcap, D = cache.k_cache.shape
+        H = q.shape[1]
+        L, P, _ = planes.shape
+        R = protos_T.shape[1]
+        dev = q.device
+        self._keep = (cache, q, k_new, v_new, input_pos, planes, protos_T, out)
+        self.protos = protos_T.to(torch.float32).contiguous()
+        nbytes = int(lib().sk_decode_step_workspace_bytes(B, H, Hkv, D, L, R, T_max, topk, sink, window))
+        self.workspace = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.list = self.list_len = None
+        ktot = list_len(T_max, sink, window, topk)
+        if keep_list:
+            self.list = torch.full((B, H, ktot), -1, dtype=torch.int32, device=dev)
+            self.list_len = torch.zeros(B, H, dtype=torch.int32, device=dev)
+        p = _lib.DecodeParams()
+        p.q, p.k_new, p.v_new, p.input_pos = ptr(q), ptr(k_new), ptr(v_new), ptr(input_pos)
+        p.planes, p.protos_T, p.temperature = ptr(planes), ptr(self.protos), float(temperature)
+        p.k_cache, p.v_cache = ptr(cache.k_cache), ptr(cache.v_cache)
+        p.codes, p.v_norm, p.prefill_len = ptr(cache.k_hard), ptr(cache.v_norm), ptr(cache.prefill_len)
+        p.out, p.list, p.list_len, p.list_row_stride = ptr(out), ptr(self.list), ptr(self.list_len), ktot
+        p.workspace, p.workspace_bytes, p.status = ptr(self.workspace), nbytes, ptr(self.status)
+        p.q_dtype, p.kv_dtype, p.plane_dtype = dtype_code(q), dtype_code(cache.k_cache), dtype_code(planes)
+        p.B, p.H, p.Hkv, p.D, p.L, p.P, p.R = B, H, Hkv, D, L, P, R
+        p.Tcap, p.T_max, p.M, p.sink, p.window = Tcap, T_max, topk, sink, window
+        self.params = p
+        self.device = dev
+        self.n_launches = 4 + (1 if k_new is not None else 0)
+
+    def run(self) -> None:
+        check(lib().sk_decode_step(C.byref(self.params), stream_ptr(self.device)), "sk_decode_step")
