@@ -54,6 +54,8 @@ def parse_args():
                          "strong = the workload's KV heads are split over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--skip-stages", action="store_true", help="skip the per-kernel timing loops")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end loop")
     ap.add_argument("--seed", type=int, default=1234)
     return ap.parse_args()
 
@@ -336,11 +338,14 @@ def main():
         v = sorted(a.elapsed_time(b) for a, b in ts[3:])
         return sum(v) / len(v) * 1e3    # us
 
+    us = {}
+    if args.skip_stages:
+        return finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, None, {}, None,
+                      sampler, step, peak, peak_src)
     probs, lut = ops.soft_hash(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv, want_probs=False,
                                want_lut=True)
     scores = ops.score(lut, cache.k_hard, cache.v_norm, H, T_now)
     lst, ln = ops.select_list(scores, T_now, cfg.topk, cfg.sink, cfg.window)
-    us = {}
     us["kv_append"] = time_kernel(lambda: cache.append(pos_s, k_s, v_s, attn.planes))
     us["soft_hash"] = time_kernel(lambda: ops.soft_hash(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv,
                                                         want_probs=False, want_lut=True))
@@ -365,6 +370,9 @@ def main():
                 "traffic": NCU_TRAFFIC.get((dominant, args.workload))}
 
     # ---- end to end through the public API with host buffers -----------------------------
+    if args.skip_e2e:
+        return finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, roofline, stages, None,
+                      sampler, step, peak, peak_src)
     n_e2e = min(K, 200)
     hq = q_all[:n_e2e + 3].cpu().pin_memory()
     hk = k_all[:n_e2e + 3].cpu().pin_memory()
@@ -404,6 +412,12 @@ def main():
     e2e = {"value": B * (world if args.shard == "weak" else 1) / (e2e_ms_step * 1e-3), "unit": UNIT,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms_step,
            "steps": len(e2e_ms)}
+    finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, roofline, stages, e2e, sampler,
+           step, peak, peak_src)
+
+
+def finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, roofline, stages, e2e, sampler,
+           step, peak, peak_src):
     clocks = sampler.stop() if sampler is not None else None
 
     cpu_baseline = None

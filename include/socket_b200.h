@@ -140,8 +140,9 @@ SK_API int sk_score_compat(const float* q_probs, const int16_t* key_buckets, con
  *   list[r] = [0..sink) ++ [max(T-window,sink)..T) ++ topM(scores[r]),  list_len[r] = its length
  * (a single entry T-1 replaces an empty sink+window part; duplicates between the parts are
  * kept; entries whose position is not allowed become -1, as in the reference).  Among equal
- * scores the smallest index wins.  Order of the top-M part: ascending index (sorted == 0)
- * or descending score like torch.topk (sorted != 0).
+ * scores the smallest index wins.  Order of the top-M part: descending score like torch.topk
+ * when sorted != 0; otherwise a deterministic order that is a function of the scores only
+ * (runs of ascending indices) — attention over the list does not depend on it.
  *   scores [rows, score_row_stride] fp32, allowed [rows, T] bytes or NULL
  *   list   [rows, list_row_stride] int32, list_row_stride >= sk_list_len(T, sink, window, M)
  * ---------------------------------------------------------------------------------- */
@@ -161,8 +162,9 @@ SK_API int sk_select_list(const float* scores, int64_t score_row_stride, const u
  *   q, out [B,H,D] (q_dtype); k_cache, v_cache (kv_dtype) with batch/head/row strides
  *   T: positions >= T are rejected (SK_DEV_INDEX_OUT_OF_RANGE), T_dev as in sk_score
  *   workspace: sk_sparse_decode_workspace_bytes(B,H,D,max_list_len) bytes, 256-byte aligned.
- *              Its first B*H int32 must be zero before the first call; every call leaves
- *              them zero again.
+ *              Its first 256 KiB (ticket counters, independent of the shape) must be zero
+ *              before the first call; every call leaves them zero again, so one buffer
+ *              zeroed once serves calls of any shape, one call at a time.
  * ---------------------------------------------------------------------------------- */
 SK_API size_t sk_sparse_decode_workspace_bytes(int B, int H, int D, int64_t max_list_len);
 SK_API int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, const void* v_cache,

@@ -54,6 +54,12 @@ struct DecodeWs {
 
 __host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// The ticket counters sit in a region of fixed size at the start of the workspace, whatever
+// the shape of the call, so that one zero-initialised buffer can serve calls of any shape:
+// every call leaves the counters at zero and nothing else is ever written there.
+constexpr int64_t DEC_MAX_ROWS = 65536;
+constexpr size_t DEC_TICKET_BYTES = DEC_MAX_ROWS * sizeof(int32_t);
+
 inline int decode_splits(int64_t rows, int64_t max_len) {
     int64_t s = (148 * 6 + rows - 1) / rows;
     const int64_t cap = (max_len + 31) / 32;
@@ -217,9 +223,9 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
 
 size_t sparse_decode_workspace_bytes(int B, int H, int D, int64_t max_list_len) {
     const int64_t rows = (int64_t)B * H;
-    if (rows <= 0) return 256;
+    if (rows <= 0) return DEC_TICKET_BYTES;
     const int splits = decode_splits(rows, max_list_len > 0 ? max_list_len : 1);
-    return align256(rows * sizeof(int32_t)) + align256((size_t)rows * splits * 2 * sizeof(float)) +
+    return DEC_TICKET_BYTES + align256((size_t)rows * splits * 2 * sizeof(float)) +
            align256((size_t)rows * splits * D * sizeof(float));
 }
 
@@ -233,15 +239,15 @@ int launch_sparse_decode(const void* q, int q_dtype, const void* k_cache, const 
     if (rows == 0) return SK_OK;
     if (D != DEC_D) return fail(SK_ERR_UNSUPPORTED, "sk_sparse_decode: head_dim %d not supported (128)", D);
     if (max_list_len <= 0) return fail(SK_ERR_INVALID_ARGUMENT, "sk_sparse_decode: max_list_len must be positive");
-    if (rows > 65535) return fail(SK_ERR_UNSUPPORTED, "sk_sparse_decode: B*H > 65535");
+    if (rows >= DEC_MAX_ROWS) return fail(SK_ERR_UNSUPPORTED, "sk_sparse_decode: B*H > 65535");
     const size_t need = sparse_decode_workspace_bytes(B, H, D, max_list_len);
     if (workspace_bytes < need)
         return fail(SK_ERR_WORKSPACE, "sk_sparse_decode: workspace %zu < %zu bytes", workspace_bytes, need);
     const int splits = decode_splits(rows, max_list_len);
     char* ws = static_cast<char*>(workspace);
     int32_t* tickets = reinterpret_cast<int32_t*>(ws);
-    float* ws_ml = reinterpret_cast<float*>(ws + align256(rows * sizeof(int32_t)));
-    float* ws_acc = reinterpret_cast<float*>(ws + align256(rows * sizeof(int32_t)) +
+    float* ws_ml = reinterpret_cast<float*>(ws + DEC_TICKET_BYTES);
+    float* ws_acc = reinterpret_cast<float*>(ws + DEC_TICKET_BYTES +
                                              align256((size_t)rows * splits * 2 * sizeof(float)));
     dim3 grid(splits, (unsigned)rows);
 #define SK_DEC_LAUNCH(QT, KT)                                                                       \
