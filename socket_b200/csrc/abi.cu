@@ -239,6 +239,8 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
                "sk_decode_step: sizes must be positive");
     SK_REQUIRE(p->H % p->Hkv == 0, "sk_decode_step: H not a multiple of Hkv");
     SK_REQUIRE(p->T_max > 0 && p->T_max <= p->Tcap, "sk_decode_step: T_max must be in (0, Tcap]");
+    SK_REQUIRE(p->P <= 8 && p->R <= 256, "sk_decode_step: the cache stores uint8 codes (P <= 8, R <= 256)");
+    SK_REQUIRE(p->temperature > 0.f, "sk_decode_step: temperature must be positive");
     SK_REQUIRE(p->q && p->planes && p->protos_T && p->k_cache && p->v_cache && p->codes && p->v_norm &&
                    p->prefill_len && p->out && p->workspace,
                "sk_decode_step: null pointer");
@@ -259,15 +261,26 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
     int32_t* list_len = p->list ? p->list_len : reinterpret_cast<int32_t*>(ws + lay.len);
     const int64_t list_stride = p->list ? p->list_row_stride : lay.list_stride;
     int rc;
-    if (p->k_new != nullptr) {
-        rc = sk_kv_append(p->k_new, p->v_new, p->kv_dtype, p->input_pos, p->planes, p->plane_dtype,
-                          p->k_cache, p->v_cache, p->codes, p->v_norm, p->prefill_len, p->status, p->B, 1,
-                          p->Hkv, p->D, p->Tcap, p->L, p->P, stream);
+    bool fused = false;
+    if (p->k_new != nullptr && p->q_dtype == p->kv_dtype) {
+        // append + soft hash in one launch
+        rc = launch_decode_prologue(p->q, p->k_new, p->v_new, p->kv_dtype, p->input_pos, p->planes,
+                                    p->plane_dtype, p->protos_T, p->temperature, p->k_cache, p->v_cache,
+                                    p->codes, p->v_norm, p->prefill_len, p->status, lut, p->B, p->H, p->Hkv,
+                                    p->D, p->Tcap, p->L, p->P, p->R, st, &fused);
         if (rc != SK_OK) return rc;
     }
-    rc = sk_soft_hash(p->q, p->q_dtype, p->planes, p->plane_dtype, p->protos_T, p->temperature, p->B, p->H,
-                      p->Hkv, p->D, p->L, p->P, p->R, nullptr, lut, stream);
-    if (rc != SK_OK) return rc;
+    if (!fused) {
+        if (p->k_new != nullptr) {
+            rc = sk_kv_append(p->k_new, p->v_new, p->kv_dtype, p->input_pos, p->planes, p->plane_dtype,
+                              p->k_cache, p->v_cache, p->codes, p->v_norm, p->prefill_len, p->status, p->B,
+                              1, p->Hkv, p->D, p->Tcap, p->L, p->P, stream);
+            if (rc != SK_OK) return rc;
+        }
+        rc = sk_soft_hash(p->q, p->q_dtype, p->planes, p->plane_dtype, p->protos_T, p->temperature, p->B,
+                          p->H, p->Hkv, p->D, p->L, p->P, p->R, nullptr, lut, stream);
+        if (rc != SK_OK) return rc;
+    }
     rc = sk_score(lut, p->codes, p->v_norm, nullptr, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
                   p->prefill_len, p->Tcap, scores, lay.score_stride, p->status, stream);
     if (rc != SK_OK) return rc;

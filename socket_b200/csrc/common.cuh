@@ -82,5 +82,11 @@ int launch_sparse_decode(const void* q, int q_dtype, const void* k_cache, const 
                          size_t workspace_bytes, int32_t* status, cudaStream_t st);
 
 int lut_head_tile(int rep);
+int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, int dtype,
+                           const int64_t* input_pos, const void* planes, int plane_dtype,
+                           const float* protos_T, float temperature, void* k_cache, void* v_cache,
+                           uint8_t* codes, uint16_t* v_norm, int32_t* prefill_len, int32_t* status,
+                           float* lut, int B, int H, int Hkv, int D, int64_t Tcap, int L, int P, int R,
+                           cudaStream_t st, bool* launched);
 
 }  // namespace sk

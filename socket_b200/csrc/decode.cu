@@ -1,56 +1,29 @@
 // GQA sparse flash-decode: exact softmax attention of one query per head over the K/V rows
 // named by that head's sparse list, read in place from the KV cache.
 //
-// Work split: grid (splits, B*H).  A CTA owns a contiguous slice of one row's list; each of
-// its 8 half-warps streams whole K and V rows (16 lanes x 16 bytes = one 256-byte bf16 row
-// per load instruction), four list entries at a time so that 8 independent 16-byte loads per
-// lane are in flight, and keeps a private online-softmax state (max, sum, 8 output lanes per
-// thread) in registers with fp32 accumulation.  The half-warp states are merged through
-// shared memory, the CTA writes one partial (max, sum, acc[D]) and takes a ticket; the CTA
-// that draws the last ticket of a row merges the row's partials and writes the output.  No
-// CTA ever waits for another one.
+// Work split: grid (splits, B*H), sized so that every CTA is resident at once.  A CTA owns a
+// contiguous slice of one row's list, each of its 4 warps a contiguous part of that slice.
+// A warp streams its rows through a private two-stage ring in shared memory with 16-byte
+// asynchronous copies (cp.async): a stage is 8 list entries = 8 K rows + 8 V rows (4 KiB for
+// bf16), the next stage is in flight while the current one is consumed, and the list indices
+// are fetched 32 at a time one batch ahead, so the gather never waits on an index load.
+// Each half-warp then handles one entry at a time (16 lanes x 16 bytes = one 256-byte row),
+// with a private online-softmax state (max, sum, 8 output lanes per thread) in fp32 registers.
+// The half-warp states are merged through shared memory, the CTA writes one partial
+// (max, sum, acc[D]) and takes a ticket; the CTA that draws the last ticket of a row merges
+// the row's partials and writes the output.  No CTA ever waits for another one.
 #include "common.cuh"
 
 namespace sk {
 namespace {
 
 constexpr int DEC_THREADS = 128;
+constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int DEC_HW = DEC_THREADS / 16;   // half-warps per CTA
-constexpr int DEC_U = 4;                   // list entries per half-warp per iteration
+constexpr int DEC_G = 8;                   // list entries per stage and warp
+constexpr int DEC_STAGES = 2;
 constexpr int DEC_D = 128;
 constexpr float LOG2E = 1.4426950408889634f;
-
-__device__ __forceinline__ void load8(const float* p, float (&d)[8]) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-    d[0] = a.x; d[1] = a.y; d[2] = a.z; d[3] = a.w;
-    d[4] = b.x; d[5] = b.y; d[6] = b.z; d[7] = b.w;
-}
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&d)[8]) {
-    const uint4 w = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        d[2 * i] = __uint_as_float(u[i] << 16);
-        d[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
-    }
-}
-__device__ __forceinline__ void load8(const __half* p, float (&d)[8]) {
-    const uint4 w = __ldg(reinterpret_cast<const uint4*>(p));
-    const __half2* h = reinterpret_cast<const __half2*>(&w);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(h[i]);
-        d[2 * i] = f.x;
-        d[2 * i + 1] = f.y;
-    }
-}
-
-struct DecodeWs {
-    int32_t* tickets;   // [rows]
-    float* ml;          // [rows][splits][2]
-    float* acc;         // [rows][splits][D]
-};
 
 __host__ __device__ inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
@@ -61,13 +34,61 @@ constexpr int64_t DEC_MAX_ROWS = 65536;
 constexpr size_t DEC_TICKET_BYTES = DEC_MAX_ROWS * sizeof(int32_t);
 
 inline int decode_splits(int64_t rows, int64_t max_len) {
-    int64_t s = (148 * 6 + rows - 1) / rows;
-    const int64_t cap = (max_len + 31) / 32;
+    int64_t s = (148 * 6) / rows;                       // all CTAs resident: <= 6 per SM
+    const int64_t cap = (max_len + 31) / 32;            // at least 8 entries per warp
     if (s > cap) s = cap;
     if (s < 1) s = 1;
     if (s > 256) s = 256;
     return (int)s;
 }
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(smem_dst)),
+                 "l"(gmem_src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// eight consecutive elements -> fp32
+__device__ __forceinline__ void cvt8(const float* p, float (&d)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *(reinterpret_cast<const float4*>(p) + 1);
+    d[0] = a.x; d[1] = a.y; d[2] = a.z; d[3] = a.w;
+    d[4] = b.x; d[5] = b.y; d[6] = b.z; d[7] = b.w;
+}
+__device__ __forceinline__ void cvt8(const __nv_bfloat16* p, float (&d)[8]) {
+    const uint4 w = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        d[2 * i] = __uint_as_float(u[i] << 16);
+        d[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void cvt8(const __half* p, float (&d)[8]) {
+    const uint4 w = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        d[2 * i] = f.x;
+        d[2 * i + 1] = f.y;
+    }
+}
+
+template <typename KT> struct DecSmem {
+    static constexpr int ROW = DEC_D * (int)sizeof(KT);                 // bytes per K or V row
+    static constexpr int STAGE = DEC_G * 2 * ROW;                       // K rows then V rows
+    static constexpr int RING = DEC_WARPS * DEC_STAGES * STAGE;
+    static constexpr int IDX = DEC_WARPS * DEC_STAGES * DEC_G * 4;
+    static constexpr int MERGE = DEC_HW * (DEC_D + 2) * 4;              // aliases the ring
+    static constexpr int TOTAL = RING + IDX + 16;
+    static_assert(MERGE <= RING, "merge buffers alias the ring");
+};
 
 template <typename QT, typename KT>
 __global__ void __launch_bounds__(DEC_THREADS)
@@ -77,15 +98,20 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
                      const int32_t* __restrict__ list_len, int64_t max_len, QT* __restrict__ out,
                      int H, int Hkv, int64_t T, const int32_t* __restrict__ T_dev, int32_t* tickets,
                      float* ws_ml, float* ws_acc, int32_t* status) {
-    __shared__ float m_s[DEC_HW], l_s[DEC_HW];
-    __shared__ float acc_s[DEC_HW][DEC_D];
-    __shared__ int is_last;
+    using S = DecSmem<KT>;
+    constexpr int CPR = S::ROW / 16;                    // 16-byte chunks per row
+    constexpr int COPIES = DEC_G * CPR / 32;            // cp.async per lane for the K (or V) rows
+    constexpr int EPC = 16 / (int)sizeof(KT);           // elements per chunk
+    extern __shared__ __align__(128) char smem[];
+    int32_t* sidx_all = reinterpret_cast<int32_t*>(smem + S::RING);
+    int* is_last = reinterpret_cast<int*>(smem + S::RING + S::IDX);
 
     const int splits = gridDim.x, split = blockIdx.x;
     const int row = blockIdx.y;                    // b*H + h
     const int b = row / H, h = row - b * H;
     const int kvh = h / (H / Hkv);
-    const int tid = threadIdx.x, hw = tid >> 4, hl = tid & 15;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hw = tid >> 4, hw2 = lane >> 4, hl = tid & 15;
     const int Teff = effective_len(T, T_dev);
 
     int len = list_len[row];
@@ -93,58 +119,97 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
     const int chunk = (int)((max_len + splits - 1) / splits);
     const int c0 = split * chunk;
     const int c1 = min(len, c0 + chunk);
+    // this warp's part of the slice, a multiple of the stage size
+    const int per_warp = ((chunk + DEC_WARPS - 1) / DEC_WARPS + DEC_G - 1) / DEC_G * DEC_G;
+    const int w0 = c0 + warp * per_warp;
+    const int w1 = min(c1, w0 + per_warp);
+    const int n_stage = w1 > w0 ? (w1 - w0 + DEC_G - 1) / DEC_G : 0;
 
     float qf[8];
-    load8(q + (size_t)row * DEC_D + hl * 8, qf);
+    cvt8(q + (size_t)row * DEC_D + hl * 8, qf);
     const float qscale = rsqrtf((float)DEC_D) * LOG2E;
 #pragma unroll
     for (int i = 0; i < 8; ++i) qf[i] *= qscale;
 
-    const KT* kb = k_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs + hl * 8;
-    const KT* vb = v_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs + hl * 8;
+    const KT* kb = k_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs;
+    const KT* vb = v_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs;
     const int32_t* lst = list + (size_t)row * list_rs;
+    char* ring = smem + (size_t)warp * DEC_STAGES * S::STAGE;
+    int32_t* sidx = sidx_all + warp * DEC_STAGES * DEC_G;
+    bool bad_index = false;
+
+    // list indices, 32 per batch, validated once
+    auto load_batch = [&](int batch) -> int {
+        const int e = w0 + batch * 32 + lane;
+        int idx = -1;
+        if (e < w1) {
+            idx = __ldg(lst + e);
+            if (idx >= Teff) {
+                bad_index = true;
+                idx = -1;
+            }
+        }
+        return idx;
+    };
+    int idx0 = load_batch(0), idx1 = load_batch(1);
+
+    auto issue = [&](int s) {
+        if (s < n_stage) {
+            const int reg = ((s >> 2) & 1) ? idx1 : idx0;
+            char* buf = ring + (s % DEC_STAGES) * S::STAGE;
+#pragma unroll
+            for (int i = 0; i < COPIES; ++i) {
+                const int c = lane + 32 * i;
+                const int r = c / CPR, ch = c % CPR;
+                const int ridx = __shfl_sync(FULL, reg, (s & 3) * DEC_G + r);
+                if (ridx >= 0) {
+                    const size_t goff = (size_t)ridx * kv_rs + ch * EPC;
+                    cp_async16(buf + r * S::ROW + ch * 16, kb + goff);
+                    cp_async16(buf + (DEC_G + r) * S::ROW + ch * 16, vb + goff);
+                }
+            }
+            const int mine = __shfl_sync(FULL, reg, (s & 3) * DEC_G + (lane & (DEC_G - 1)));
+            if (lane < DEC_G) sidx[(s % DEC_STAGES) * DEC_G + lane] = mine;
+            if ((s & 3) == 3) {               // batch fully issued: fetch the one after next
+                const int nb = load_batch((s >> 2) + 2);
+                if ((s >> 2) & 1) idx1 = nb; else idx0 = nb;
+            }
+        }
+        cp_async_commit();
+    };
 
     float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    bool bad_index = false;
 
-    // trip count is uniform over the CTA: the shuffles below need whole warps
-    const int n_iter = c1 > c0 ? (c1 - c0 + DEC_HW * DEC_U - 1) / (DEC_HW * DEC_U) : 0;
-    for (int it = 0; it < n_iter; ++it) {
-        const int e0 = c0 + (it * DEC_HW + hw) * DEC_U;
-        int idx[DEC_U];
-        float kf[DEC_U][8], vf[DEC_U][8];
 #pragma unroll
-        for (int u = 0; u < DEC_U; ++u) {
-            idx[u] = (e0 + u < c1) ? __ldg(lst + e0 + u) : -1;
-            if (idx[u] >= Teff) {
-                bad_index = true;
-                idx[u] = -1;
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < DEC_U; ++u) {
-            if (idx[u] >= 0) {
-                load8(kb + (size_t)idx[u] * kv_rs, kf[u]);
-                load8(vb + (size_t)idx[u] * kv_rs, vf[u]);
-            }
-        }
-        float s[DEC_U];
+    for (int s = 0; s < DEC_STAGES; ++s) issue(s);
+
+    for (int s = 0; s < n_stage; ++s) {
+        cp_async_wait<DEC_STAGES - 1>();
+        __syncwarp();
+        const char* buf = ring + (s % DEC_STAGES) * S::STAGE;
+        const int32_t* si = sidx + (s % DEC_STAGES) * DEC_G;
+        float sc[DEC_G / 2];
+        int ok[DEC_G / 2];
         float m_new = m;
 #pragma unroll
-        for (int u = 0; u < DEC_U; ++u) {
+        for (int j = 0; j < DEC_G / 2; ++j) {
+            const int e = 2 * j + hw2;
+            ok[j] = si[e] >= 0;
             float d = 0.f;
-            if (idx[u] >= 0) {
+            if (ok[j]) {
+                float kf[8];
+                cvt8(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8, kf);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kf[u][i], d);
+                for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kf[i], d);
             }
             d += __shfl_xor_sync(FULL, d, 8);
             d += __shfl_xor_sync(FULL, d, 4);
             d += __shfl_xor_sync(FULL, d, 2);
             d += __shfl_xor_sync(FULL, d, 1);
-            s[u] = idx[u] >= 0 ? d : -INFINITY;
-            m_new = fmaxf(m_new, s[u]);
+            sc[j] = ok[j] ? d : -INFINITY;
+            m_new = fmaxf(m_new, sc[j]);
         }
         if (m_new > -INFINITY) {
             const float resc = exp2f(m - m_new);
@@ -152,26 +217,36 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[i] *= resc;
 #pragma unroll
-            for (int u = 0; u < DEC_U; ++u) {
-                if (idx[u] >= 0) {
-                    const float p = exp2f(s[u] - m_new);
+            for (int j = 0; j < DEC_G / 2; ++j) {
+                if (ok[j]) {
+                    const int e = 2 * j + hw2;
+                    const float p = exp2f(sc[j] - m_new);
                     l += p;
+                    float vf[8];
+                    cvt8(reinterpret_cast<const KT*>(buf + (DEC_G + e) * S::ROW) + hl * 8, vf);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[u][i], acc[i]);
+                    for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
                 }
             }
             m = m_new;
         }
+        __syncwarp();                      // the stage is free again
+        issue(s + DEC_STAGES);
     }
+    cp_async_wait<0>();
     if (bad_index && status != nullptr) atomicOr(status, SK_DEV_INDEX_OUT_OF_RANGE);
 
-    // ---- merge the half-warps of this CTA
+    // ---- merge the half-warps of this CTA (buffers alias the ring, all copies have landed)
+    __syncthreads();
+    float* m_s = reinterpret_cast<float*>(smem);
+    float* l_s = m_s + DEC_HW;
+    float* acc_s = l_s + DEC_HW;           // [DEC_HW][DEC_D]
     if (hl == 0) {
         m_s[hw] = m;
         l_s[hw] = l;
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc_s[hw][hl * 8 + i] = acc[i];
+    for (int i = 0; i < 8; ++i) acc_s[hw * DEC_D + hl * 8 + i] = acc[i];
     __syncthreads();
     {
         float mm = -INFINITY;
@@ -183,7 +258,7 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
             for (int w = 0; w < DEC_HW; ++w) {
                 const float f = exp2f(m_s[w] - mm);
                 ll += l_s[w] * f;
-                a += acc_s[w][tid] * f;
+                a += acc_s[w * DEC_D + tid] * f;
             }
         }
         const size_t slot = (size_t)row * splits + split;
@@ -198,18 +273,17 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
     __syncthreads();
     if (tid == 0) {
         const int t = atomicAdd(&tickets[row], 1);
-        is_last = (t == splits - 1);
+        *is_last = (t == splits - 1);
     }
     __syncthreads();
-    if (!is_last) return;
+    if (!*is_last) return;
     __threadfence();
     float mm = -INFINITY;
-    for (int sidx = 0; sidx < splits; ++sidx)
-        mm = fmaxf(mm, __ldcg(ws_ml + ((size_t)row * splits + sidx) * 2));
+    for (int i = 0; i < splits; ++i) mm = fmaxf(mm, __ldcg(ws_ml + ((size_t)row * splits + i) * 2));
     float ll = 0.f, a = 0.f;
     if (mm > -INFINITY) {
-        for (int sidx = 0; sidx < splits; ++sidx) {
-            const size_t slot = (size_t)row * splits + sidx;
+        for (int i = 0; i < splits; ++i) {
+            const size_t slot = (size_t)row * splits + i;
             const float f = exp2f(__ldcg(ws_ml + slot * 2) - mm);
             ll += __ldcg(ws_ml + slot * 2 + 1) * f;
             a += __ldcg(ws_acc + slot * DEC_D + tid) * f;
@@ -217,6 +291,24 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
     }
     out[(size_t)row * DEC_D + tid] = from_f32<QT>(ll > 0.f ? a / ll : 0.f);
     if (tid == 0) tickets[row] = 0;   // ready for the next call
+}
+
+template <typename QT, typename KT>
+int decode_launch(dim3 grid, cudaStream_t st, const void* q, const void* k_cache, const void* v_cache,
+                  int64_t kv_bs, int64_t kv_hs, int64_t kv_rs, const int32_t* list, int64_t list_rs,
+                  const int32_t* list_len, int64_t max_list_len, void* out, int H, int Hkv, int64_t T,
+                  const int32_t* T_dev, int32_t* tickets, float* ws_ml, float* ws_acc, int32_t* status) {
+    auto kern = sparse_decode_kernel<QT, KT>;
+    constexpr int smem = DecSmem<KT>::TOTAL;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess)
+            return fail(SK_ERR_CUDA, "sparse_decode_kernel smem attribute: %s", cudaGetErrorString(e));
+    }
+    kern<<<grid, DEC_THREADS, smem, st>>>((const QT*)q, (const KT*)k_cache, (const KT*)v_cache, kv_bs,
+                                          kv_hs, kv_rs, list, list_rs, list_len, max_list_len, (QT*)out,
+                                          H, Hkv, T, T_dev, tickets, ws_ml, ws_acc, status);
+    return check_launch("sparse_decode_kernel");
 }
 
 }  // namespace
@@ -250,17 +342,16 @@ int launch_sparse_decode(const void* q, int q_dtype, const void* k_cache, const 
     float* ws_acc = reinterpret_cast<float*>(ws + DEC_TICKET_BYTES +
                                              align256((size_t)rows * splits * 2 * sizeof(float)));
     dim3 grid(splits, (unsigned)rows);
-#define SK_DEC_LAUNCH(QT, KT)                                                                       \
-    sparse_decode_kernel<QT, KT><<<grid, DEC_THREADS, 0, st>>>(                                     \
-        (const QT*)q, (const KT*)k_cache, (const KT*)v_cache, kv_bs, kv_hs, kv_rs, list, list_rs,   \
-        list_len, max_list_len, (QT*)out, H, Hkv, T, T_dev, tickets, ws_ml, ws_acc, status)
+#define SK_DEC_LAUNCH(QT, KT)                                                                        \
+    return decode_launch<QT, KT>(grid, st, q, k_cache, v_cache, kv_bs, kv_hs, kv_rs, list, list_rs,  \
+                                 list_len, max_list_len, out, H, Hkv, T, T_dev, tickets, ws_ml,      \
+                                 ws_acc, status)
     if (q_dtype == SK_BF16 && kv_dtype == SK_BF16) SK_DEC_LAUNCH(__nv_bfloat16, __nv_bfloat16);
-    else if (q_dtype == SK_F32 && kv_dtype == SK_F32) SK_DEC_LAUNCH(float, float);
-    else if (q_dtype == SK_F16 && kv_dtype == SK_F16) SK_DEC_LAUNCH(__half, __half);
-    else if (q_dtype == SK_F32 && kv_dtype == SK_BF16) SK_DEC_LAUNCH(float, __nv_bfloat16);
-    else return fail(SK_ERR_UNSUPPORTED, "sk_sparse_decode: unsupported q/kv dtype pair (%d,%d)", q_dtype, kv_dtype);
+    if (q_dtype == SK_F32 && kv_dtype == SK_F32) SK_DEC_LAUNCH(float, float);
+    if (q_dtype == SK_F16 && kv_dtype == SK_F16) SK_DEC_LAUNCH(__half, __half);
+    if (q_dtype == SK_F32 && kv_dtype == SK_BF16) SK_DEC_LAUNCH(float, __nv_bfloat16);
 #undef SK_DEC_LAUNCH
-    return check_launch("sparse_decode_kernel");
+    return fail(SK_ERR_UNSUPPORTED, "sk_sparse_decode: unsupported q/kv dtype pair (%d,%d)", q_dtype, kv_dtype);
 }
 
 }  // namespace sk

@@ -1,16 +1,23 @@
 // Top-k select + sparse-list assembly, one CTA per (batch, query head) row.
 //
-// Exact radix select on order-preserving uint32 keys with deterministic tie-breaking (among
-// equal scores the smallest index wins) and ordered, atomic-free compaction (warp ballots +
-// block prefix scans), so the output is a pure function of the scores.
+// Exact selection on order-preserving uint32 keys with deterministic tie-breaking (among
+// equal scores the smallest index wins) and ordered, atomic-free compaction (block prefix
+// scans), so the output is a pure function of the scores.
 //
-// Rows that fit the shared-memory candidate buffer are selected entirely on chip.  Longer
-// rows take two streaming passes: a 4096-bin histogram over a range found by sampling
-// (bins are linear in the key between the sampled min and max, clamped outside, which keeps
-// the map monotone), then one pass that emits every element above the threshold bin and
-// collects the threshold bin's elements as on-chip candidates.  A row whose threshold bin
-// overflows the buffer (e.g. all scores equal) falls back to the textbook 4-pass radix
-// select over global memory.
+// The exact work always happens on chip, on a candidate set held in shared memory (up to
+// SEL_CAP entries, kept in index order): a 4 x 8-bit radix select finds the k-th key and the
+// number of ties to take, an ordered scan emits the winners.  How the candidates get there:
+//   * rows with T <= SEL_CAP: the whole row;
+//   * longer rows, main path: 8192 strided samples are radix-selected for a cut that about
+//     2k elements exceed; ONE streaming pass (16-byte loads, 16 elements per thread and scan)
+//     then collects every element >= cut.  If the collected set turns out smaller than k or
+//     larger than the buffer, the row is redone by
+//   * the two-pass path: a 4096-bin histogram (bins linear in the key between the sampled
+//     min and max, clamped outside, hence monotone) finds the bin holding the k-th element;
+//     a second pass emits everything above that bin and keeps the bin itself as candidates;
+//   * rows whose threshold bin overflows the buffer (e.g. all scores equal) fall back to
+//     the textbook 4-pass radix select over global memory.
+// NaN scores are not ordered; rows containing them get an unspecified (but in-range) list.
 #include "common.cuh"
 
 namespace sk {
@@ -20,7 +27,11 @@ constexpr int SEL_THREADS = 1024;
 constexpr int SEL_WARPS = SEL_THREADS / 32;
 constexpr int SEL_CAP = 16384;
 constexpr int SEL_BINS = 4096;
-constexpr int SEL_CHUNK = SEL_THREADS * 4;
+constexpr int SEL_EPT = 8;                        // consecutive elements per thread (two-pass path)
+constexpr int SEL_CHUNK = SEL_THREADS * SEL_EPT;
+constexpr int SEL_EPT1 = 16;                      // consecutive elements per thread (one-pass path)
+constexpr int SEL_CHUNK1 = SEL_THREADS * SEL_EPT1;
+constexpr int SEL_SAMPLES = 8192;
 
 struct SelShared {
     uint32_t hist[SEL_BINS];
@@ -74,7 +85,11 @@ struct BinMap {
     }
 };
 
-// One 8-bit radix step over `count(d)` = hist[d]: finds the digit d with
+__device__ __forceinline__ float key_to_float(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
+// One 8-bit radix step over hist[0..256): finds the digit d with
 // #(digit > d) < remaining <= #(digit >= d).  Executed by warp 0; results in shared memory.
 __device__ __forceinline__ void find_digit(SelShared& s, uint32_t remaining) {
     if (threadIdx.x < 32) {
@@ -104,6 +119,46 @@ __device__ __forceinline__ void find_digit(SelShared& s, uint32_t remaining) {
     }
 }
 
+// k-th largest (k >= 1) of keys[0..n) in shared memory, n >= k.  Returns the key; `quota` =
+// how many elements equal to it belong to the top k.
+__device__ __forceinline__ uint32_t smem_kth(SelShared& s, const uint32_t* keys, int n, uint32_t k,
+                                             uint32_t& quota) {
+    uint32_t prefix = 0, mask = 0, remaining = k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = threadIdx.x; i < 256; i += SEL_THREADS) s.hist[i] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += SEL_THREADS) {
+            const uint32_t key = keys[i];
+            if ((key & mask) == prefix) atomicAdd(&s.hist[(key >> shift) & 0xffu], 1u);
+        }
+        __syncthreads();
+        find_digit(s, remaining);
+        __syncthreads();
+        remaining -= s.digit_above;
+        prefix |= s.digit << shift;
+        mask |= 0xffu << shift;
+    }
+    quota = remaining;
+    return prefix;
+}
+
+// N consecutive scores starting at t0 (a multiple of 4); positions >= T read as 0 and are
+// masked by the caller.  `vec`: the row base is 16-byte aligned.
+template <int N>
+__device__ __forceinline__ void load_scores(const float* __restrict__ sc, int t0, int T, bool vec,
+                                            float (&f)[N]) {
+    if (vec && t0 + N <= T) {
+#pragma unroll
+        for (int v = 0; v < N / 4; ++v) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(sc + t0) + v);
+            f[4 * v] = a.x; f[4 * v + 1] = a.y; f[4 * v + 2] = a.z; f[4 * v + 3] = a.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) f[j] = (t0 + j < T) ? __ldg(sc + t0 + j) : 0.f;
+    }
+}
+
 __global__ void __launch_bounds__(SEL_THREADS, 1)
 select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
                    const uint8_t* __restrict__ allowed, int64_t T_host,
@@ -118,6 +173,7 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
     const uint8_t* al = allowed ? allowed + row * T_host : nullptr;
     int32_t* out = list + row * list_row_stride;
     const int T = effective_len(T_host, T_dev);
+    const bool vec = (reinterpret_cast<uintptr_t>(sc) & 15u) == 0;
     Scan scan;
 
     if (T <= 0) {
@@ -143,10 +199,10 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
     if (Me == T) {
         for (int i = tid; i < T; i += SEL_THREADS) heavy[i] = i;
     } else if (Me > 0) {
-        int n_cand = 0;        // candidates in shared memory
+        int n_cand = 0;        // candidates in shared memory (index order)
         int need = Me;         // how many of them to take
         int out_pos = 0;       // heavy entries already emitted
-        bool global_fallback = false;
+        bool have_cand = false, global_fallback = false;
 
         if (T <= SEL_CAP) {
             for (int i = tid; i < T; i += SEL_THREADS) {
@@ -154,141 +210,190 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
                 s.cand_idx[i] = i;
             }
             n_cand = T;
+            have_cand = true;
             __syncthreads();
         } else {
-            // ---- sampled range
-            uint32_t kmin = 0xffffffffu, kmax = 0u;
-            const int stride = T / SEL_CHUNK;
-            for (int j = 0; j < 4; ++j) {
-                const int t = (tid * 4 + j) * stride;
-                const float f = sc[t];
-                if (f > -INFINITY && f < INFINITY) {
-                    const uint32_t k = order_key(f);
-                    kmin = min(kmin, k);
-                    kmax = max(kmax, k);
-                }
-            }
+            // ---- main path: cut from a sample, then one streaming pass
+            const int stride = T / SEL_SAMPLES;                     // >= 2
+            const int64_t rs64 = (2 * (int64_t)Me * SEL_SAMPLES + T - 1) / T + 32;
+            if (rs64 <= SEL_SAMPLES / 4 && rs64 * stride <= SEL_CAP / 2) {
+                const uint32_t r_s = (uint32_t)rs64;
+                for (int i = tid; i < SEL_SAMPLES; i += SEL_THREADS)
+                    s.cand_key[i] = order_key(__ldg(sc + (size_t)i * stride));
+                __syncthreads();
+                uint32_t quota;
+                const uint32_t cut_key = smem_kth(s, s.cand_key, SEL_SAMPLES, r_s, quota);
+                const float cut = key_to_float(cut_key);
+                __syncthreads();                                    // samples are consumed
+                int base_cnt = 0;
+                float cur[SEL_EPT1], nxt[SEL_EPT1];
+                load_scores<SEL_EPT1>(sc, tid * SEL_EPT1, T, vec, cur);
+                for (int base = 0; base < T; base += SEL_CHUNK1) {
+                    const int t0 = base + tid * SEL_EPT1;
+                    if (base + SEL_CHUNK1 < T) load_scores<SEL_EPT1>(sc, t0 + SEL_CHUNK1, T, vec, nxt);
+                    unsigned hit = 0;
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) {
-                kmin = min(kmin, __shfl_xor_sync(FULL, kmin, o));
-                kmax = max(kmax, __shfl_xor_sync(FULL, kmax, o));
-            }
-            if (lane == 0) {
-                s.red_lo[warp] = kmin;
-                s.red_hi[warp] = kmax;
-            }
-            for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
-            __syncthreads();
-            kmin = s.red_lo[lane];
-            kmax = s.red_hi[lane];
+                    for (int j = 0; j < SEL_EPT1; ++j)
+                        if (cur[j] >= cut && t0 + j < T) hit |= 1u << j;
+                    int total;
+                    int pos = base_cnt + scan.excl(__popc(hit), total, s);
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) {
-                kmin = min(kmin, __shfl_xor_sync(FULL, kmin, o));
-                kmax = max(kmax, __shfl_xor_sync(FULL, kmax, o));
-            }
-            BinMap bin;
-            if (kmin > kmax) {  // no finite sample
-                bin.lo = 0;
-                bin.shift = 20;
-            } else {
-                const uint32_t range = kmax - kmin;
-                const int bits = 32 - __clz(range | 1u);
-                bin.lo = kmin;
-                bin.shift = max(0, bits - 11);
-            }
-            // ---- pass 1: histogram
-            for (int t = tid; t < T; t += SEL_THREADS) atomicAdd(&s.hist[bin(order_key(sc[t]))], 1u);
-            __syncthreads();
-            {
-                int c[4], local = 0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    c[j] = (int)s.hist[SEL_BINS - 1 - (4 * tid + j)];
-                    local += c[j];
-                }
-                int total;
-                int before = scan.excl(local, total, s);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (before < Me && before + c[j] >= Me) {
-                        s.thr_bin = SEL_BINS - 1 - (4 * tid + j);
-                        s.thr_above = before;
-                        s.thr_inbin = c[j];
+                    for (int j = 0; j < SEL_EPT1; ++j) {
+                        if (hit & (1u << j)) {
+                            if (pos < SEL_CAP) {
+                                s.cand_key[pos] = order_key(cur[j]);
+                                s.cand_idx[pos] = t0 + j;
+                            }
+                            ++pos;
+                        }
                     }
-                    before += c[j];
+                    base_cnt += total;
+#pragma unroll
+                    for (int j = 0; j < SEL_EPT1; ++j) cur[j] = nxt[j];
+                }
+                __syncthreads();
+                if (base_cnt >= Me && base_cnt <= SEL_CAP) {
+                    n_cand = base_cnt;
+                    have_cand = true;
                 }
             }
-            __syncthreads();
-            const int thr = s.thr_bin;
-            const int above = s.thr_above;
-            const int inbin = s.thr_inbin;
-            if (inbin > SEL_CAP) {
-                global_fallback = true;
-            } else {
-                // ---- pass 2: emit the sure ones, keep the threshold bin on chip (index order)
-                int sure_base = 0, cand_base = 0;
-                for (int base = 0; base < T; base += SEL_CHUNK) {
-                    const int t0 = base + tid * 4;
-                    uint32_t k[4];
-                    int cls[4];  // 2 = sure, 1 = candidate
-                    int n_sure = 0, n_cnd = 0;
+            if (!have_cand) {
+                // ---- two-pass path: sampled range, histogram, threshold bin
+                uint32_t kmin = 0xffffffffu, kmax = 0u;
+                const int sstride = T / (SEL_THREADS * 4);
+                for (int j = 0; j < 4; ++j) {
+                    const float f = sc[(size_t)(tid * 4 + j) * sstride];
+                    if (f > -INFINITY && f < INFINITY) {
+                        const uint32_t k = order_key(f);
+                        kmin = min(kmin, k);
+                        kmax = max(kmax, k);
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) {
+                    kmin = min(kmin, __shfl_xor_sync(FULL, kmin, o));
+                    kmax = max(kmax, __shfl_xor_sync(FULL, kmax, o));
+                }
+                if (lane == 0) {
+                    s.red_lo[warp] = kmin;
+                    s.red_hi[warp] = kmax;
+                }
+                for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
+                __syncthreads();
+                kmin = s.red_lo[lane];
+                kmax = s.red_hi[lane];
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) {
+                    kmin = min(kmin, __shfl_xor_sync(FULL, kmin, o));
+                    kmax = max(kmax, __shfl_xor_sync(FULL, kmax, o));
+                }
+                BinMap bin;
+                if (kmin > kmax) {  // no finite sample
+                    bin.lo = 0;
+                    bin.shift = 20;
+                } else {
+                    const uint32_t range = kmax - kmin;
+                    const int bits = 32 - __clz(range | 1u);
+                    bin.lo = kmin;
+                    bin.shift = max(0, bits - 11);
+                }
+                // pass 1: histogram; two independent groups per thread keep 4 x 16 B in flight
+                for (int base = 0; base < T; base += 2 * SEL_CHUNK) {
+                    float fa[SEL_EPT], fb[SEL_EPT];
+                    const int ta = base + tid * SEL_EPT, tb = ta + SEL_CHUNK;
+                    load_scores<SEL_EPT>(sc, ta, T, vec, fa);
+                    load_scores<SEL_EPT>(sc, tb, T, vec, fb);
+#pragma unroll
+                    for (int j = 0; j < SEL_EPT; ++j)
+                        if (ta + j < T) atomicAdd(&s.hist[bin(order_key(fa[j]))], 1u);
+#pragma unroll
+                    for (int j = 0; j < SEL_EPT; ++j)
+                        if (tb + j < T) atomicAdd(&s.hist[bin(order_key(fb[j]))], 1u);
+                }
+                __syncthreads();
+                {
+                    int c[4], local = 0;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        cls[j] = 0;
-                        if (t0 + j < T) {
-                            k[j] = order_key(sc[t0 + j]);
-                            const int b = bin(k[j]);
-                            cls[j] = b > thr ? 2 : (b == thr ? 1 : 0);
-                            n_sure += cls[j] == 2;
-                            n_cnd += cls[j] == 1;
-                        }
+                        c[j] = (int)s.hist[SEL_BINS - 1 - (4 * tid + j)];
+                        local += c[j];
                     }
                     int total;
-                    const int off = scan.excl(n_sure | (n_cnd << 16), total, s);
-                    int so = sure_base + (off & 0xffff), co = cand_base + (off >> 16);
+                    int before = scan.excl(local, total, s);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        // bounds hold by construction; the guards keep a row whose scores
-                        // change under the kernel from writing outside its buffers
-                        if (cls[j] == 2) {
-                            if (so < Me) heavy[so] = t0 + j;
-                            ++so;
-                        } else if (cls[j] == 1) {
-                            if (co < SEL_CAP) {
-                                s.cand_key[co] = k[j];
-                                s.cand_idx[co] = t0 + j;
-                            }
-                            ++co;
+                        if (before < Me && before + c[j] >= Me) {
+                            s.thr_bin = SEL_BINS - 1 - (4 * tid + j);
+                            s.thr_above = before;
+                            s.thr_inbin = c[j];
                         }
+                        before += c[j];
                     }
-                    sure_base += total & 0xffff;
-                    cand_base += total >> 16;
                 }
-                out_pos = above;
-                need = Me - above;
-                n_cand = inbin;
                 __syncthreads();
+                const int thr = s.thr_bin;
+                const int above = s.thr_above;
+                const int inbin = s.thr_inbin;
+                if (inbin > SEL_CAP) {
+                    global_fallback = true;
+                } else {
+                    // pass 2: emit the sure ones, keep the threshold bin on chip (index order)
+                    int sure_base = 0, cand_base = 0;
+                    float cur[SEL_EPT], nxt[SEL_EPT];
+                    load_scores<SEL_EPT>(sc, tid * SEL_EPT, T, vec, cur);
+                    for (int base = 0; base < T; base += SEL_CHUNK) {
+                        const int t0 = base + tid * SEL_EPT;
+                        if (base + SEL_CHUNK < T) load_scores<SEL_EPT>(sc, t0 + SEL_CHUNK, T, vec, nxt);
+                        uint32_t k[SEL_EPT];
+                        int cls[SEL_EPT];  // 2 = sure, 1 = candidate
+                        int n_sure = 0, n_cnd = 0;
+#pragma unroll
+                        for (int j = 0; j < SEL_EPT; ++j) {
+                            cls[j] = 0;
+                            k[j] = order_key(cur[j]);
+                            if (t0 + j < T) {
+                                const int b = bin(k[j]);
+                                cls[j] = b > thr ? 2 : (b == thr ? 1 : 0);
+                                n_sure += cls[j] == 2;
+                                n_cnd += cls[j] == 1;
+                            }
+                        }
+                        int total;
+                        const int off = scan.excl(n_sure | (n_cnd << 16), total, s);
+                        int so = sure_base + (off & 0xffff), co = cand_base + (off >> 16);
+#pragma unroll
+                        for (int j = 0; j < SEL_EPT; ++j) {
+                            // bounds hold by construction; the guards keep a row whose scores
+                            // change under the kernel from writing outside its buffers
+                            if (cls[j] == 2) {
+                                if (so < Me) heavy[so] = t0 + j;
+                                ++so;
+                            } else if (cls[j] == 1) {
+                                if (co < SEL_CAP) {
+                                    s.cand_key[co] = k[j];
+                                    s.cand_idx[co] = t0 + j;
+                                }
+                                ++co;
+                            }
+                        }
+                        sure_base += total & 0xffff;
+                        cand_base += total >> 16;
+#pragma unroll
+                        for (int j = 0; j < SEL_EPT; ++j) cur[j] = nxt[j];
+                    }
+                    out_pos = above;
+                    need = Me - above;
+                    n_cand = inbin;
+                    have_cand = true;
+                    __syncthreads();
+                }
             }
         }
 
-        if (!global_fallback) {
-            // ---- exact select among the on-chip candidates: 4 x 8-bit radix from the top
-            uint32_t prefix = 0, mask = 0, remaining = (uint32_t)need;
-            for (int shift = 24; shift >= 0; shift -= 8) {
-                for (int i = tid; i < 256; i += SEL_THREADS) s.hist[i] = 0;
-                __syncthreads();
-                for (int i = tid; i < n_cand; i += SEL_THREADS) {
-                    const uint32_t k = s.cand_key[i];
-                    if ((k & mask) == prefix) atomicAdd(&s.hist[(k >> shift) & 0xffu], 1u);
-                }
-                __syncthreads();
-                find_digit(s, remaining);
-                __syncthreads();
-                remaining -= s.digit_above;
-                prefix |= s.digit << shift;
-                mask |= 0xffu << shift;
-            }
-            // prefix = k-th key, remaining = how many equal to it are taken (lowest index first)
+        if (have_cand) {
+            // ---- exact select among the on-chip candidates
+            uint32_t quota;
+            const uint32_t kth = smem_kth(s, s.cand_key, n_cand, (uint32_t)need, quota);
             int gt_base = 0, eq_base = 0;
             for (int base = 0; base < n_cand; base += SEL_THREADS) {
                 const int i = base + tid;
@@ -299,18 +404,17 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
                     k = s.cand_key[i];
                     idx = s.cand_idx[i];
                 }
-                const int gt = live && k > prefix, eq = live && k == prefix;
+                const int gt = live && k > kth, eq = live && k == kth;
                 int total;
                 const int off = scan.excl(gt | (eq << 16), total, s);
                 const int gt_before = gt_base + (off & 0xffff);
                 const int eq_before = eq_base + (off >> 16);
-                const int eq_taken_before = min(eq_before, (int)remaining);
-                const int dst = out_pos + gt_before + eq_taken_before;
-                if ((gt || (eq && eq_before < (int)remaining)) && dst < Me) heavy[dst] = idx;
+                const int dst = out_pos + gt_before + min(eq_before, (int)quota);
+                if ((gt || (eq && eq_before < (int)quota)) && dst < Me) heavy[dst] = idx;
                 gt_base += total & 0xffff;
                 eq_base += total >> 16;
             }
-        } else {
+        } else if (global_fallback) {
             // ---- fallback: radix select over the whole row in global memory
             uint32_t prefix = 0, mask = 0, remaining = (uint32_t)Me;
             for (int shift = 24; shift >= 0; shift -= 8) {
@@ -329,10 +433,10 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
             }
             int gt_base = 0, eq_base = 0;
             for (int base = 0; base < T; base += SEL_CHUNK) {
-                const int t0 = base + tid * 4;
-                int gt[4], eq[4], n_gt = 0, n_eq = 0;
+                const int t0 = base + tid * SEL_EPT;
+                int gt[SEL_EPT], eq[SEL_EPT], n_gt = 0, n_eq = 0;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < SEL_EPT; ++j) {
                     gt[j] = eq[j] = 0;
                     if (t0 + j < T) {
                         const uint32_t k = order_key(sc[t0 + j]);
@@ -347,7 +451,7 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
                 int gt_before = gt_base + (off & 0xffff);
                 int eq_before = eq_base + (off >> 16);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < SEL_EPT; ++j) {
                     const int dst = gt_before + min(eq_before, (int)remaining);
                     if ((gt[j] || (eq[j] && eq_before < (int)remaining)) && dst < Me) heavy[dst] = t0 + j;
                     gt_before += gt[j];

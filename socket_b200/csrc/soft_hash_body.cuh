@@ -1,0 +1,116 @@
+// Device code of the query soft hash: for one KV-head group, one head tile and a few tables,
+// the softmax over the R buckets of (tanh(<q, plane>) / sqrt(D)) . protos_T / temperature.
+#pragma once
+#include "common.cuh"
+
+namespace sk {
+
+constexpr int SH_THREADS = 256;
+constexpr int SH_WARPS = SH_THREADS / 32;
+
+__device__ __forceinline__ float warp_sum_f(float x) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) x += __shfl_xor_sync(FULL, x, o);
+    return x;
+}
+__device__ __forceinline__ float warp_max_f(float x) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) x = fmaxf(x, __shfl_xor_sync(FULL, x, o));
+    return x;
+}
+
+// shared memory (floats): protos [P*R] | t [SH_WARPS*16] | stage [tables_per_cta * R * ht]
+inline size_t soft_hash_smem_bytes(int P, int R, int ht) {
+    return sizeof(float) * ((size_t)P * R + SH_WARPS * 16 + (size_t)(SH_WARPS / ht) * R * ht);
+}
+
+// One CTA: head tile `g` (= (b*Hkv + kvh)*tiles + tile) and tables [l0, l0 + SH_WARPS/ht).
+// Warp w handles (table l0 + w / ht, head w % ht).  All global loads of a warp are issued
+// before the first use, so a cold call costs one memory round trip.
+template <typename QT, typename PT>
+__device__ __forceinline__ void soft_hash_body(
+    const QT* __restrict__ q, const PT* __restrict__ planes, const float* __restrict__ protos_T,
+    float inv_temperature, int H, int Hkv, int D, int L, int P, int R, int ht, int g, int l0,
+    float* __restrict__ q_probs, float* __restrict__ lut, float* smem) {
+    const int rep = H / Hkv;
+    const int tiles = rep / ht;
+    const int tile = g % tiles;
+    const int bk = g / tiles;
+    const int b = bk / Hkv, kvh = bk - b * Hkv;
+    const int h0 = kvh * rep + tile * ht;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tpc = SH_WARPS / ht;                // tables per CTA
+    const int lt = warp / ht, j = warp - lt * ht;
+    const int l = l0 + lt;
+    const bool active = l < L;
+
+    float* pr_s = smem;                           // [P][R]
+    float* t_s = pr_s + (size_t)P * R;            // [SH_WARPS][16]
+    float* stage = t_s + SH_WARPS * 16;           // [tpc][R][ht]
+
+    // issue the plane / query loads first, then the protos copy, then reduce
+    float part[16];
+#pragma unroll
+    for (int p = 0; p < 16; ++p) part[p] = 0.f;
+    if (active) {
+        const QT* qh = q + ((size_t)b * H + h0 + j) * D;
+        const PT* pl = planes + (size_t)l * P * D;
+        for (int d = lane; d < D; d += 32) {
+            const float qv = to_f32(qh[d]);
+#pragma unroll
+            for (int p = 0; p < 16; ++p)
+                if (p < P) part[p] = fmaf(qv, to_f32(pl[(size_t)p * D + d]), part[p]);
+        }
+    }
+    for (int i = threadIdx.x; i < P * R; i += SH_THREADS) pr_s[i] = protos_T[i];
+    const float inv_sqrt_d = 1.0f / fmaxf(sqrtf((float)D), 1e-6f);
+#pragma unroll
+    for (int p = 0; p < 16; ++p) {
+        if (p < P) {
+            const float s = warp_sum_f(part[p]);
+            if (lane == 0) t_s[warp * 16 + p] = tanhf(s) * inv_sqrt_d;
+        }
+    }
+    __syncthreads();
+
+    if (active) {
+        const float* t = t_s + warp * 16;
+        float mx = -INFINITY;
+        for (int r = lane; r < R; r += 32) {
+            float lg = 0.f;
+            for (int p = 0; p < P; ++p) lg = fmaf(t[p], pr_s[p * R + r], lg);
+            mx = fmaxf(mx, lg * inv_temperature);
+        }
+        mx = warp_max_f(mx);
+        float se = 0.f;
+        for (int r = lane; r < R; r += 32) {
+            float lg = 0.f;
+            for (int p = 0; p < P; ++p) lg = fmaf(t[p], pr_s[p * R + r], lg);
+            se += expf(lg * inv_temperature - mx);
+        }
+        se = warp_sum_f(se);
+        float* qp_row = q_probs ? q_probs + (((size_t)b * H + h0 + j) * L + l) * R : nullptr;
+        for (int r = lane; r < R; r += 32) {
+            float lg = 0.f;
+            for (int p = 0; p < P; ++p) lg = fmaf(t[p], pr_s[p * R + r], lg);
+            const float pr = expf(lg * inv_temperature - mx) / se;
+            if (qp_row) qp_row[r] = pr;
+            stage[((size_t)lt * R + r) * ht + j] = pr;
+        }
+    }
+    if (lut == nullptr) return;
+    __syncthreads();
+    // scorer table rows: lut[g][r][l][0..ht)
+    float* lut_g = lut + (size_t)g * R * L * ht;
+    for (int i = threadIdx.x; i < tpc * R; i += SH_THREADS) {
+        const int lt2 = i / R, r = i - lt2 * R;
+        if (l0 + lt2 >= L) continue;
+        const float* src = stage + (size_t)i * ht;
+        float* dst = lut_g + ((size_t)r * L + l0 + lt2) * ht;
+        if (ht == 4) *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+        else if (ht == 2) *reinterpret_cast<float2*>(dst) = *reinterpret_cast<const float2*>(src);
+        else *dst = *src;
+    }
+}
+
+}  // namespace sk

@@ -230,7 +230,7 @@ def sparse_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 
 class DecodeStep:
     """One fused decode step of one layer (`sk_decode_step`): append+hash the new token,
-    soft-hash the query, score, select, attend — five launches on the current stream, no
+    soft-hash the query, score, select, attend — four launches on the current stream, no
     host synchronisation, so it can be captured in a CUDA graph.  Holds the parameter
     block and the scratch memory; `run()` re-enqueues the step on whatever the tensors
     given at construction contain at that moment."""
@@ -267,7 +267,9 @@ class DecodeStep:
         p.Tcap, p.T_max, p.M, p.sink, p.window = Tcap, T_max, topk, sink, window
         self.params = p
         self.device = dev
-        self.n_launches = 4 + (1 if k_new is not None else 0)
+        # prologue (append + soft hash in one launch when q and the cache share a dtype), score,
+        # select, decode
+        self.n_launches = 4 if (k_new is None or q.dtype == cache.k_cache.dtype) else 5
 
     def run(self) -> None:
         check(lib().sk_decode_step(C.byref(self.params), stream_ptr(self.device)), "sk_decode_step")
