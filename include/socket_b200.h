@@ -175,6 +175,37 @@ SK_API int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, con
                      size_t workspace_bytes, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * sk_sparse_decode without any caller-provided or allocated scratch.  No counterpart in the
+ * reference (its sparse_attention_fwd allocates its partial-result tensors on every call,
+ * GPT-FAST/kernels/sparse.py:323-325).
+ *
+ * For callers that may not allocate device memory at the point of the call: a serving
+ * process that handed the whole GPU to its own memory pool at start-up (a later cudaMalloc
+ * fails there), a plug-in that only receives tensors and a stream and owns no allocator, or a
+ * latency-critical loop in which an allocator call (and its possible implicit synchronisation)
+ * is not acceptable.  The partial results of the split list and the per-row ticket counters
+ * live in a buffer of SK_SPARSE_DECODE_STATIC_BYTES that is part of the library image: every
+ * GPU that loads the library holds one copy until the process exits.
+ *
+ * Same arguments and result as sk_sparse_decode, minus the workspace.  Limits and rules:
+ *   - shapes whose scratch need (sk_sparse_decode_workspace_bytes) exceeds the built-in
+ *     buffer are rejected with SK_ERR_WORKSPACE and a message naming both sizes; nothing is
+ *     enqueued.  The buffer covers e.g. B*H = 128 rows with lists of a few thousand entries.
+ *   - the first call on each device looks up the buffer's device address (with that device
+ *     current); make that first call outside any stream capture.
+ *   - all calls on a device share the one buffer: calls that can overlap on the GPU (two
+ *     streams, two threads) race on it.  Serialise them, or use sk_sparse_decode with
+ *     separate workspaces.  Each call clears the ticket counters it uses before its kernel.
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine.
+ * ---------------------------------------------------------------------------------- */
+#define SK_SPARSE_DECODE_STATIC_BYTES (2u << 20)
+SK_API int sk_sparse_decode_static(const void* q, int q_dtype, const void* k_cache, const void* v_cache,
+                     int kv_dtype, int64_t kv_batch_stride, int64_t kv_head_stride,
+                     int64_t kv_row_stride, const int32_t* list, int64_t list_row_stride,
+                     const int32_t* list_len, int64_t max_list_len, void* out, int B, int H,
+                     int Hkv, int D, int64_t T, const int32_t* T_dev, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * One decode step of one layer, fused on one stream with no host synchronisation: the
  * body of Attention.sparse_forward between the QKV projection and the output projection
  * (GPT-FAST/model.py:449-552): append+hash the new token, soft-hash the query, score,

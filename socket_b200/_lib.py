@@ -17,6 +17,7 @@ DTYPE_CODE = {torch.float32: SK_F32, torch.bfloat16: SK_BF16, torch.float16: SK_
 SK_DEV_POS_OUT_OF_RANGE = 1
 SK_DEV_INDEX_OUT_OF_RANGE = 2
 SK_DEV_WAIT_TIMEOUT = 4
+SK_SPARSE_DECODE_STATIC_BYTES = 2 << 20
 
 
 class SocketError(RuntimeError):
@@ -60,6 +61,8 @@ SIGNATURES = {
     "sk_sparse_decode_workspace_bytes": (_sz, [_i, _i, _i, _i64]),
     "sk_sparse_decode": (_i, [_p, _i, _p, _p, _i, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _i, _i,
                               _i, _i, _i64, _p, _p, _sz, _p, _p]),
+    "sk_sparse_decode_static": (_i, [_p, _i, _p, _p, _i, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _i, _i,
+                                     _i, _i, _i64, _p, _p, _p]),
     "sk_decode_step_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i64, _i64, _i, _i]),
     "sk_decode_step": (_i, [C.POINTER(DecodeParams), _p]),
 }

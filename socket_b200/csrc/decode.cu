@@ -12,7 +12,14 @@
 // The half-warp states are merged through shared memory, the CTA writes one partial
 // (max, sum, acc[D]) and takes a ticket; the CTA that draws the last ticket of a row merges
 // the row's partials and writes the output.  No CTA ever waits for another one.
+#include <mutex>
+
 #include "common.cuh"
+
+// Scratch for sk_sparse_decode_static: lives in the library image, one copy per GPU that
+// loads the library, for the life of the process.  In host code this name is only a handle
+// for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_static_decode_scratch[SK_SPARSE_DECODE_STATIC_BYTES];
 
 namespace sk {
 namespace {
@@ -355,3 +362,73 @@ int launch_sparse_decode(const void* q, int q_dtype, const void* k_cache, const 
 }
 
 }  // namespace sk
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant
+// ------------------------------------------------------------------------------------------
+namespace {
+constexpr int MAX_DEVICES = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[MAX_DEVICES] = {nullptr};
+
+// Device address of the static scratch on the current device, resolved once per device.
+int static_scratch_address(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return sk::fail(SK_ERR_CUDA, "sk_sparse_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return sk::fail(SK_ERR_UNSUPPORTED, "sk_sparse_decode_static: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_decode_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return sk::fail(SK_ERR_CUDA, "sk_sparse_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return SK_OK;
+}
+}  // namespace
+
+extern "C" SK_API int sk_sparse_decode_static(
+    const void* q, int q_dtype, const void* k_cache, const void* v_cache, int kv_dtype,
+    int64_t kv_batch_stride, int64_t kv_head_stride, int64_t kv_row_stride, const int32_t* list,
+    int64_t list_row_stride, const int32_t* list_len, int64_t max_list_len, void* out, int B, int H,
+    int Hkv, int D, int64_t T, const int32_t* T_dev, int32_t* status, void* stream) {
+    using namespace sk;
+    if (B < 0 || H <= 0 || Hkv <= 0 || D <= 0 || T < 0 || max_list_len <= 0)
+        return fail(SK_ERR_INVALID_ARGUMENT, "sk_sparse_decode_static: sizes must be positive");
+    if (B == 0) return SK_OK;
+    if (H % Hkv != 0) return fail(SK_ERR_INVALID_ARGUMENT, "sk_sparse_decode_static: H=%d not a multiple of Hkv=%d", H, Hkv);
+    if (!q || !k_cache || !v_cache || !list || !list_len || !out)
+        return fail(SK_ERR_INVALID_ARGUMENT, "sk_sparse_decode_static: null pointer");
+    if (list_row_stride < max_list_len)
+        return fail(SK_ERR_INVALID_ARGUMENT, "sk_sparse_decode_static: list_row_stride smaller than max_list_len");
+    if ((q_dtype != SK_F32 && q_dtype != SK_BF16 && q_dtype != SK_F16) ||
+        (kv_dtype != SK_F32 && kv_dtype != SK_BF16 && kv_dtype != SK_F16))
+        return fail(SK_ERR_INVALID_ARGUMENT, "sk_sparse_decode_static: bad dtype");
+    const int64_t per16 = kv_dtype == SK_F32 ? 4 : 8;   // elements per 16 bytes
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
+         reinterpret_cast<uintptr_t>(v_cache)) & 15u)
+        return fail(SK_ERR_MISALIGNED, "sk_sparse_decode_static: q, k_cache and v_cache must be 16-byte aligned");
+    if (kv_batch_stride % per16 || kv_head_stride % per16 || kv_row_stride % per16)
+        return fail(SK_ERR_MISALIGNED, "sk_sparse_decode_static: K/V strides must be multiples of 16 bytes");
+    const size_t need = sparse_decode_workspace_bytes(B, H, D, max_list_len);
+    if (need > (size_t)SK_SPARSE_DECODE_STATIC_BYTES)
+        return fail(SK_ERR_WORKSPACE,
+                    "sk_sparse_decode_static: B=%d H=%d max_list_len=%lld needs %zu bytes of scratch, the "
+                    "built-in buffer holds %zu; use sk_sparse_decode with a caller-provided workspace",
+                    B, H, (long long)max_list_len, need, (size_t)SK_SPARSE_DECODE_STATIC_BYTES);
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != SK_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // the ticket counters must read zero when the kernel starts, whatever an earlier call left
+    cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)B * H * sizeof(int32_t), st);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "sk_sparse_decode_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return launch_sparse_decode(q, q_dtype, k_cache, v_cache, kv_dtype, kv_batch_stride, kv_head_stride,
+                                kv_row_stride, list, list_row_stride, list_len, max_list_len, out, B, H,
+                                Hkv, D, T, T_dev, scratch, (size_t)SK_SPARSE_DECODE_STATIC_BYTES, status, st);
+}
+
