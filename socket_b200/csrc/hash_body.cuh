@@ -41,55 +41,82 @@ __device__ __forceinline__ void store_code(void* base, int code_bytes, int l, un
     else static_cast<int16_t*>(base)[l] = (int16_t)code;
 }
 
-// One warp: codes of table `l` for HASH_ROWS rows whose elements are already in registers.
+// The 8 planes of table `l`, EPL elements per lane each.
+template <typename PT, int EPL>
+__device__ __forceinline__ void load_planes8(const PT* __restrict__ planes, int l, int lane,
+                                             double (&pd)[8][EPL]) {
+    constexpr int D = EPL * 32;
+    const PT* pl = planes + (size_t)l * 8 * D;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) load_row_f64<PT, EPL>(pl + (size_t)p * D, lane, pd[p]);
+}
+
+// One warp, P == 8: codes of one table for HASH_ROWS rows; keys and planes are in registers.
 // code_ptr[r] == nullptr marks an absent row.
+template <int EPL>
+__device__ __forceinline__ void hash_rows_planes8(const double (&kd)[HASH_ROWS][EPL],
+                                                  const double (&pd)[8][EPL],
+                                                  void* const (&code_ptr)[HASH_ROWS], int l,
+                                                  int code_bytes, int lane) {
+    // slot j = r*8 + (7-p): after the ballot, byte r of the mask is row r's code
+    double v[32];
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+#pragma unroll
+        for (int r = 0; r < HASH_ROWS; ++r) {
+            double s = 0.0;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) s = fma(kd[r][i], pd[p][i], s);
+            v[r * 8 + (7 - p)] = s;
+        }
+    }
+    const double tot = transpose_reduce32(v, lane);
+    const unsigned bits = __ballot_sync(FULL, tot >= 0.0);
+#pragma unroll
+    for (int r = 0; r < HASH_ROWS; ++r)
+        if (lane == r && code_ptr[r] != nullptr) store_code(code_ptr[r], code_bytes, l, (bits >> (8 * r)) & 0xffu);
+}
+
+// One warp, any P <= 15: plane by plane.
+template <typename PT, int EPL>
+__device__ __forceinline__ void hash_rows_generic(const double (&kd)[HASH_ROWS][EPL],
+                                                  void* const (&code_ptr)[HASH_ROWS],
+                                                  const PT* __restrict__ planes, int l, int P,
+                                                  int code_bytes, int lane) {
+    constexpr int D = EPL * 32;
+    const PT* pl = planes + (size_t)l * P * D;
+    unsigned code[HASH_ROWS];
+#pragma unroll
+    for (int r = 0; r < HASH_ROWS; ++r) code[r] = 0;
+    for (int p = 0; p < P; ++p) {
+        double pd[EPL];
+        load_row_f64<PT, EPL>(pl + (size_t)p * D, lane, pd);
+#pragma unroll
+        for (int r = 0; r < HASH_ROWS; ++r) {
+            double s = 0.0;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) s = fma(kd[r][i], pd[i], s);
+            s = warp_sum_f64(s);
+            code[r] = code[r] * 2u + (s >= 0.0 ? 1u : 0u);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < HASH_ROWS; ++r)
+        if (lane == 0 && code_ptr[r] != nullptr) store_code(code_ptr[r], code_bytes, l, code[r]);
+}
+
+// One warp: codes of table `l` for HASH_ROWS rows whose elements are already in registers.
 template <typename PT, int EPL>
 __device__ __forceinline__ void hash_table_rows(const double (&kd)[HASH_ROWS][EPL],
                                                 void* const (&code_ptr)[HASH_ROWS],
                                                 const PT* __restrict__ planes, int l, int P,
                                                 int code_bytes, int lane) {
-    constexpr int D = EPL * 32;
-    const PT* pl = planes + (size_t)l * P * D;
     if (P == 8) {
-        // slot j = r*8 + (7-p): after the ballot, byte r of the mask is row r's code
         double pd[8][EPL];
-#pragma unroll
-        for (int p = 0; p < 8; ++p) load_row_f64<PT, EPL>(pl + (size_t)p * D, lane, pd[p]);
-        double v[32];
-#pragma unroll
-        for (int p = 0; p < 8; ++p) {
-#pragma unroll
-            for (int r = 0; r < HASH_ROWS; ++r) {
-                double s = 0.0;
-#pragma unroll
-                for (int i = 0; i < EPL; ++i) s = fma(kd[r][i], pd[p][i], s);
-                v[r * 8 + (7 - p)] = s;
-            }
-        }
-        const double tot = transpose_reduce32(v, lane);
-        const unsigned bits = __ballot_sync(FULL, tot >= 0.0);
-#pragma unroll
-        for (int r = 0; r < HASH_ROWS; ++r)
-            if (lane == r && code_ptr[r] != nullptr) store_code(code_ptr[r], code_bytes, l, (bits >> (8 * r)) & 0xffu);
+        load_planes8<PT, EPL>(planes, l, lane, pd);
+        hash_rows_planes8<EPL>(kd, pd, code_ptr, l, code_bytes, lane);
     } else {
-        unsigned code[HASH_ROWS];
-#pragma unroll
-        for (int r = 0; r < HASH_ROWS; ++r) code[r] = 0;
-        for (int p = 0; p < P; ++p) {
-            double pd[EPL];
-            load_row_f64<PT, EPL>(pl + (size_t)p * D, lane, pd);
-#pragma unroll
-            for (int r = 0; r < HASH_ROWS; ++r) {
-                double s = 0.0;
-#pragma unroll
-                for (int i = 0; i < EPL; ++i) s = fma(kd[r][i], pd[i], s);
-                s = warp_sum_f64(s);
-                code[r] = code[r] * 2u + (s >= 0.0 ? 1u : 0u);
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < HASH_ROWS; ++r)
-            if (lane == 0 && code_ptr[r] != nullptr) store_code(code_ptr[r], code_bytes, l, code[r]);
+        hash_rows_generic<PT, EPL>(kd, code_ptr, planes, l, P, code_bytes, lane);
     }
 }
 
@@ -105,6 +132,12 @@ __device__ __forceinline__ void kv_append_body(
     constexpr int D = EPL * 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t N = (int64_t)B * S * Hkv;
+    const int l = l0 + warp;
+    // the plane loads do not depend on anything: issue them first, so that they overlap the
+    // input_pos -> key dependent loads below
+    double pd[8][EPL];
+    const bool fast = (P == 8) && (l < L);
+    if (fast) load_planes8<PT, EPL>(planes, l, lane, pd);
     double kd[HASH_ROWS][EPL];
     void* code_ptr[HASH_ROWS];
     int64_t cache_row[HASH_ROWS];
@@ -130,8 +163,8 @@ __device__ __forceinline__ void kv_append_body(
             }
         }
     }
-    const int l = l0 + warp;
-    if (l < L) hash_table_rows<PT, EPL>(kd, code_ptr, planes, l, P, 1, lane);
+    if (fast) hash_rows_planes8<EPL>(kd, pd, code_ptr, l, 1, lane);
+    else if (l < L) hash_rows_generic<PT, EPL>(kd, code_ptr, planes, l, P, 1, lane);
     if (l0 == 0 && warp < HASH_ROWS) {
         // warp r moves row r (static indexing of the per-row arrays)
 #pragma unroll

@@ -10,7 +10,7 @@ namespace {
 static_assert(HASH_THREADS == SH_THREADS, "both roles share one block size");
 
 template <typename T, typename PT>
-__global__ void __launch_bounds__(SH_THREADS)
+__global__ void __launch_bounds__(SH_THREADS, 2)
 decode_prologue_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T* __restrict__ v_new,
                        const int64_t* __restrict__ input_pos, const PT* __restrict__ planes,
                        const float* __restrict__ protos_T, float inv_temperature, T* __restrict__ k_cache,

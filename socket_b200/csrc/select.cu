@@ -119,24 +119,73 @@ __device__ __forceinline__ void find_digit(SelShared& s, uint32_t remaining) {
     }
 }
 
+// Histogram increment with the lanes of a warp that hit the same bin merged into one atomic
+// (score keys share their high bits, so without this thousands of atomics would serialise on
+// one address).  Must be called by all 32 lanes.
+__device__ __forceinline__ void warp_hist_add(uint32_t* hist, uint32_t bin, bool active) {
+    const unsigned live = __ballot_sync(FULL, active);
+    if (active) {
+        const unsigned peers = __match_any_sync(live, bin);
+        if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
+    }
+}
+
 // k-th largest (k >= 1) of keys[0..n) in shared memory, n >= k.  Returns the key; `quota` =
-// how many elements equal to it belong to the top k.
+// how many elements equal to it belong to the top k.  Radix select, 8 bits per pass, over the
+// bits in which the keys actually differ (found from their min and max).
 __device__ __forceinline__ uint32_t smem_kth(SelShared& s, const uint32_t* keys, int n, uint32_t k,
                                              uint32_t& quota) {
-    uint32_t prefix = 0, mask = 0, remaining = k;
-    for (int shift = 24; shift >= 0; shift -= 8) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t kmin = 0xffffffffu, kmax = 0u;
+    for (int i = threadIdx.x; i < n; i += SEL_THREADS) {
+        const uint32_t key = keys[i];
+        kmin = min(kmin, key);
+        kmax = max(kmax, key);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        kmin = min(kmin, __shfl_xor_sync(FULL, kmin, o));
+        kmax = max(kmax, __shfl_xor_sync(FULL, kmax, o));
+    }
+    if (lane == 0) {
+        s.red_lo[warp] = kmin;
+        s.red_hi[warp] = kmax;
+    }
+    __syncthreads();
+    kmin = s.red_lo[lane];
+    kmax = s.red_hi[lane];
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        kmin = min(kmin, __shfl_xor_sync(FULL, kmin, o));
+        kmax = max(kmax, __shfl_xor_sync(FULL, kmax, o));
+    }
+    __syncthreads();                                   // red_lo / red_hi may be reused
+    int hi = 32 - __clz(kmin ^ kmax);                  // bits [0, hi) may differ
+    uint32_t mask = hi >= 32 ? 0u : ~((1u << hi) - 1u);
+    uint32_t prefix = kmin & mask;
+    uint32_t remaining = k;
+    while (hi > 0) {
+        const int lo = max(hi - 8, 0);
+        const uint32_t dmask = (1u << (hi - lo)) - 1u;
         for (int i = threadIdx.x; i < 256; i += SEL_THREADS) s.hist[i] = 0;
         __syncthreads();
-        for (int i = threadIdx.x; i < n; i += SEL_THREADS) {
-            const uint32_t key = keys[i];
-            if ((key & mask) == prefix) atomicAdd(&s.hist[(key >> shift) & 0xffu], 1u);
+        for (int base = 0; base < n; base += SEL_THREADS) {
+            const int i = base + threadIdx.x;
+            uint32_t key = 0;
+            bool active = false;
+            if (i < n) {
+                key = keys[i];
+                active = (key & mask) == prefix;
+            }
+            warp_hist_add(s.hist, (key >> lo) & dmask, active);
         }
         __syncthreads();
         find_digit(s, remaining);
         __syncthreads();
         remaining -= s.digit_above;
-        prefix |= s.digit << shift;
-        mask |= 0xffu << shift;
+        prefix |= s.digit << lo;
+        mask |= dmask << lo;
+        hi = lo;
     }
     quota = remaining;
     return prefix;
@@ -305,10 +354,10 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
                     load_scores<SEL_EPT>(sc, tb, T, vec, fb);
 #pragma unroll
                     for (int j = 0; j < SEL_EPT; ++j)
-                        if (ta + j < T) atomicAdd(&s.hist[bin(order_key(fa[j]))], 1u);
+                        warp_hist_add(s.hist, (uint32_t)bin(order_key(fa[j])), ta + j < T);
 #pragma unroll
                     for (int j = 0; j < SEL_EPT; ++j)
-                        if (tb + j < T) atomicAdd(&s.hist[bin(order_key(fb[j]))], 1u);
+                        warp_hist_add(s.hist, (uint32_t)bin(order_key(fb[j])), tb + j < T);
                 }
                 __syncthreads();
                 {
@@ -420,9 +469,10 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
             for (int shift = 24; shift >= 0; shift -= 8) {
                 for (int i = tid; i < 256; i += SEL_THREADS) s.hist[i] = 0;
                 __syncthreads();
-                for (int t = tid; t < T; t += SEL_THREADS) {
-                    const uint32_t k = order_key(sc[t]);
-                    if ((k & mask) == prefix) atomicAdd(&s.hist[(k >> shift) & 0xffu], 1u);
+                for (int base = 0; base < T; base += SEL_THREADS) {
+                    const int t = base + tid;
+                    const uint32_t k = t < T ? order_key(sc[t]) : 0u;
+                    warp_hist_add(s.hist, (k >> shift) & 0xffu, t < T && (k & mask) == prefix);
                 }
                 __syncthreads();
                 find_digit(s, remaining);

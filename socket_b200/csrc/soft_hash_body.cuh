@@ -55,11 +55,26 @@ __device__ __forceinline__ void soft_hash_body(
     if (active) {
         const QT* qh = q + ((size_t)b * H + h0 + j) * D;
         const PT* pl = planes + (size_t)l * P * D;
-        for (int d = lane; d < D; d += 32) {
-            const float qv = to_f32(qh[d]);
+        if (D == 128 && P == 8) {
+            // four consecutive elements per lane: every load of the warp is issued up front
+            float qv[4], pv[8][4];
 #pragma unroll
-            for (int p = 0; p < 16; ++p)
-                if (p < P) part[p] = fmaf(qv, to_f32(pl[(size_t)p * D + d]), part[p]);
+            for (int i = 0; i < 4; ++i) qv[i] = to_f32(qh[lane * 4 + i]);
+#pragma unroll
+            for (int p = 0; p < 8; ++p)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pv[p][i] = to_f32(pl[p * 128 + lane * 4 + i]);
+#pragma unroll
+            for (int p = 0; p < 8; ++p)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) part[p] = fmaf(qv[i], pv[p][i], part[p]);
+        } else {
+            for (int d = lane; d < D; d += 32) {
+                const float qv = to_f32(qh[d]);
+#pragma unroll
+                for (int p = 0; p < 16; ++p)
+                    if (p < P) part[p] = fmaf(qv, to_f32(pl[(size_t)p * D + d]), part[p]);
+            }
         }
     }
     for (int i = threadIdx.x; i < P * R; i += SH_THREADS) pr_s[i] = protos_T[i];
@@ -75,27 +90,55 @@ __device__ __forceinline__ void soft_hash_body(
 
     if (active) {
         const float* t = t_s + warp * 16;
-        float mx = -INFINITY;
-        for (int r = lane; r < R; r += 32) {
-            float lg = 0.f;
-            for (int p = 0; p < P; ++p) lg = fmaf(t[p], pr_s[p * R + r], lg);
-            mx = fmaxf(mx, lg * inv_temperature);
-        }
-        mx = warp_max_f(mx);
-        float se = 0.f;
-        for (int r = lane; r < R; r += 32) {
-            float lg = 0.f;
-            for (int p = 0; p < P; ++p) lg = fmaf(t[p], pr_s[p * R + r], lg);
-            se += expf(lg * inv_temperature - mx);
-        }
-        se = warp_sum_f(se);
         float* qp_row = q_probs ? q_probs + (((size_t)b * H + h0 + j) * L + l) * R : nullptr;
-        for (int r = lane; r < R; r += 32) {
-            float lg = 0.f;
-            for (int p = 0; p < P; ++p) lg = fmaf(t[p], pr_s[p * R + r], lg);
-            const float pr = expf(lg * inv_temperature - mx) / se;
-            if (qp_row) qp_row[r] = pr;
-            stage[((size_t)lt * R + r) * ht + j] = pr;
+        if (R == 256 && P <= 16) {
+            // 8 buckets per lane, logits kept in registers
+            float lg[8];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float a = 0.f;
+                for (int p = 0; p < P; ++p) a = fmaf(t[p], pr_s[p * 256 + lane + 32 * i], a);
+                lg[i] = a * inv_temperature;
+                mx = fmaxf(mx, lg[i]);
+            }
+            mx = warp_max_f(mx);
+            float se = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                lg[i] = expf(lg[i] - mx);
+                se += lg[i];
+            }
+            se = warp_sum_f(se);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = lane + 32 * i;
+                const float pr = lg[i] / se;
+                if (qp_row) qp_row[r] = pr;
+                stage[((size_t)lt * 256 + r) * ht + j] = pr;
+            }
+        } else {
+            float mx = -INFINITY;
+            for (int r = lane; r < R; r += 32) {
+                float lg = 0.f;
+                for (int p = 0; p < P; ++p) lg = fmaf(t[p], pr_s[p * R + r], lg);
+                mx = fmaxf(mx, lg * inv_temperature);
+            }
+            mx = warp_max_f(mx);
+            float se = 0.f;
+            for (int r = lane; r < R; r += 32) {
+                float lg = 0.f;
+                for (int p = 0; p < P; ++p) lg = fmaf(t[p], pr_s[p * R + r], lg);
+                se += expf(lg * inv_temperature - mx);
+            }
+            se = warp_sum_f(se);
+            for (int r = lane; r < R; r += 32) {
+                float lg = 0.f;
+                for (int p = 0; p < P; ++p) lg = fmaf(t[p], pr_s[p * R + r], lg);
+                const float pr = expf(lg * inv_temperature - mx) / se;
+                if (qp_row) qp_row[r] = pr;
+                stage[((size_t)lt * R + r) * ht + j] = pr;
+            }
         }
     }
     if (lut == nullptr) return;
