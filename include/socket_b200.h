@@ -153,6 +153,24 @@ SK_API int sk_select_list(const float* scores, int64_t score_row_stride, const u
                    int32_t* list_len, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Scorer and select fused: the same list as sk_score followed by sk_select_list (sorted == 0,
+ * no mask), without writing the [B,H,T] score array.  The scorer keeps only keys above a cut
+ * estimated from a sample (about 3*M per row), the select kernel proves that this candidate
+ * set contains the exact top-M and otherwise rescores the row itself, so the result is exact
+ * in every case.  Replaces the same reference code as the two calls it fuses
+ * (GPT-FAST/kernels/soft_hash_collision.cu:25-54 + GPT-FAST/kernels/sparse.py:57-95).
+ *   applicable shapes: sk_score_select_applicable(...) != 0  (L = 32, R <= 256, T >= 4096,
+ *   12*M <= T, M <= 4096); workspace: sk_score_select_workspace_bytes, 256-byte aligned,
+ *   zero-initialised once.
+ * ---------------------------------------------------------------------------------- */
+SK_API int sk_score_select_applicable(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M);
+SK_API size_t sk_score_select_workspace_bytes(int B, int H, int Hkv, int L, int64_t T, int64_t M);
+SK_API int sk_score_select_list(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
+                         int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
+                         int sink, int window, int32_t* list, int64_t list_row_stride, int32_t* list_len,
+                         void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * GQA sparse flash-decode.  Replaces sparse_attention_fwd and its two Triton kernels
  * (GPT-FAST/kernels/sparse.py:309-329, 102-235):
  *   out[b,h,:] = sum_j softmax_j(<q[b,h], K[b,h/rep,idx_j]>/sqrt(D)) V[b,h/rep,idx_j],

@@ -175,6 +175,46 @@ int sk_select_list(const float* scores, int64_t score_row_stride, const uint8_t*
                               list, list_row_stride, list_len, status, (cudaStream_t)stream);
 }
 
+size_t sk_score_select_workspace_bytes(int B, int H, int Hkv, int L, int64_t T, int64_t M) {
+    return score_select_workspace_bytes(B, H, Hkv, L, T, M);
+}
+
+int sk_score_select_applicable(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M) {
+    if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || L != 32 || R > 256 || T <= 0) return 0;
+    const int ht = lut_head_tile(H / Hkv);
+    const ScorePlan plan = make_score_plan(B * Hkv * ((H / Hkv) / ht), T, M);
+    return fused_filter_applicable(plan, T, M) ? 1 : 0;
+}
+
+int sk_score_select_list(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
+                         int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
+                         int sink, int window, int32_t* list, int64_t list_row_stride, int32_t* list_len,
+                         void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+    SK_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && L > 0 && R > 0 && T > 0 && M >= 0,
+               "sk_score_select_list: sizes must be positive");
+    if (B == 0) return SK_OK;
+    SK_REQUIRE(H % Hkv == 0, "sk_score_select_list: H=%d not a multiple of Hkv=%d", H, Hkv);
+    SK_REQUIRE(lut && codes && v_norm && list && list_len && workspace, "sk_score_select_list: null pointer");
+    SK_REQUIRE(T <= Tcap, "sk_score_select_list: T exceeds the cache capacity");
+    SK_REQUIRE(list_row_stride >= list_len_host(T, sink, window, M),
+               "sk_score_select_list: list_row_stride smaller than the list length");
+    SK_ALIGNED(lut, 16, "sk_score_select_list: lut");
+    SK_ALIGNED(codes, 16, "sk_score_select_list: codes");
+    SK_ALIGNED(workspace, 256, "sk_score_select_list: workspace");
+    if (!sk_score_select_applicable(B, H, Hkv, L, R, T, M))
+        return fail(SK_ERR_UNSUPPORTED,
+                    "sk_score_select_list: shape outside the fused path (needs L=32, R<=256, T>=4096, 12*M<=T, M<=4096); "
+                    "use sk_score + sk_select_list");
+    if (workspace_bytes < score_select_workspace_bytes(B, H, Hkv, L, T, M))
+        return fail(SK_ERR_WORKSPACE, "sk_score_select_list: workspace %zu < %zu bytes", workspace_bytes,
+                    score_select_workspace_bytes(B, H, Hkv, L, T, M));
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc = launch_score_filter(lut, codes, v_norm, B, H, Hkv, L, R, T, T_dev, Tcap, M, workspace, status, st);
+    if (rc != SK_OK) return rc;
+    return launch_select_candidates(lut, codes, v_norm, B, H, Hkv, L, R, T, T_dev, Tcap, M, sink, window, 0,
+                                    list, list_row_stride, list_len, workspace, status, st);
+}
+
 size_t sk_sparse_decode_workspace_bytes(int B, int H, int D, int64_t max_list_len) {
     return sparse_decode_workspace_bytes(B, H, D, max_list_len);
 }
@@ -208,18 +248,22 @@ int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, const void
 struct StepLayout {
     size_t dec, lut, scores, list, len, total;
     int64_t score_stride, list_stride;
+    bool fused;      // scores region holds the fused scorer+select workspace instead
 };
 
-static StepLayout step_layout(int B, int H, int D, int L, int R, int64_t T_max, int64_t M, int sink,
-                              int window) {
+static StepLayout step_layout(int B, int H, int Hkv, int D, int L, int R, int64_t T_max, int64_t M,
+                              int sink, int window) {
     StepLayout s;
+    s.fused = sk_score_select_applicable(B, H, Hkv, L, R, T_max, M) != 0;
     s.list_stride = list_len_host(T_max, sink, window, M);
     if (s.list_stride < 1) s.list_stride = 1;
     s.score_stride = (T_max + 3) / 4 * 4;
     size_t off = 0;
     s.dec = off;    off += up256(sparse_decode_workspace_bytes(B, H, D, s.list_stride));
     s.lut = off;    off += up256((size_t)B * H * L * R * sizeof(float));
-    s.scores = off; off += up256((size_t)B * H * s.score_stride * sizeof(float));
+    s.scores = off;
+    off += s.fused ? up256(score_select_workspace_bytes(B, H, Hkv, L, T_max, M))
+                   : up256((size_t)B * H * s.score_stride * sizeof(float));
     s.list = off;   off += up256((size_t)B * H * s.list_stride * sizeof(int32_t));
     s.len = off;    off += up256((size_t)B * H * sizeof(int32_t));
     s.total = off;
@@ -228,9 +272,8 @@ static StepLayout step_layout(int B, int H, int D, int L, int R, int64_t T_max, 
 
 size_t sk_decode_step_workspace_bytes(int B, int H, int Hkv, int D, int L, int R, int64_t T_max,
                                       int64_t M, int sink, int window) {
-    (void)Hkv;
-    if (B <= 0 || H <= 0 || T_max <= 0) return 256;
-    return step_layout(B, H, D, L, R, T_max, M, sink, window).total;
+    if (B <= 0 || H <= 0 || Hkv <= 0 || T_max <= 0) return 256;
+    return step_layout(B, H, Hkv, D, L, R, T_max, M, sink, window).total;
 }
 
 int sk_decode_step(const sk_decode_params* p, void* stream) {
@@ -248,7 +291,7 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
     SK_REQUIRE(p->k_new == nullptr || p->input_pos != nullptr, "sk_decode_step: input_pos missing");
     SK_REQUIRE((p->list == nullptr) == (p->list_len == nullptr), "sk_decode_step: list and list_len go together");
     SK_ALIGNED(p->workspace, 256, "sk_decode_step: workspace");
-    const StepLayout lay = step_layout(p->B, p->H, p->D, p->L, p->R, p->T_max, p->M, p->sink, p->window);
+    const StepLayout lay = step_layout(p->B, p->H, p->Hkv, p->D, p->L, p->R, p->T_max, p->M, p->sink, p->window);
     if (p->workspace_bytes < lay.total)
         return fail(SK_ERR_WORKSPACE, "sk_decode_step: workspace %zu < %zu bytes", p->workspace_bytes, lay.total);
     SK_REQUIRE(p->list == nullptr || p->list_row_stride >= lay.list_stride,
@@ -281,12 +324,23 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
                           p->H, p->Hkv, p->D, p->L, p->P, p->R, nullptr, lut, stream);
         if (rc != SK_OK) return rc;
     }
-    rc = sk_score(lut, p->codes, p->v_norm, nullptr, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
-                  p->prefill_len, p->Tcap, scores, lay.score_stride, p->status, stream);
-    if (rc != SK_OK) return rc;
-    rc = sk_select_list(scores, lay.score_stride, nullptr, (int64_t)p->B * p->H, p->T_max, p->prefill_len,
-                        p->M, p->sink, p->window, 0, list, list_stride, list_len, p->status, stream);
-    if (rc != SK_OK) return rc;
+    if (lay.fused) {
+        // filtering scorer + candidate select: no score array is written or re-read
+        rc = launch_score_filter(lut, p->codes, p->v_norm, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
+                                 p->prefill_len, p->Tcap, p->M, ws + lay.scores, p->status, st);
+        if (rc != SK_OK) return rc;
+        rc = launch_select_candidates(lut, p->codes, p->v_norm, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
+                                      p->prefill_len, p->Tcap, p->M, p->sink, p->window, 0, list, list_stride,
+                                      list_len, ws + lay.scores, p->status, st);
+        if (rc != SK_OK) return rc;
+    } else {
+        rc = sk_score(lut, p->codes, p->v_norm, nullptr, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
+                      p->prefill_len, p->Tcap, scores, lay.score_stride, p->status, stream);
+        if (rc != SK_OK) return rc;
+        rc = sk_select_list(scores, lay.score_stride, nullptr, (int64_t)p->B * p->H, p->T_max, p->prefill_len,
+                            p->M, p->sink, p->window, 0, list, list_stride, list_len, p->status, stream);
+        if (rc != SK_OK) return rc;
+    }
     const int64_t kv_hs = p->Tcap * p->D;
     rc = launch_sparse_decode(p->q, p->q_dtype, p->k_cache, p->v_cache, p->kv_dtype, kv_hs * p->Hkv, kv_hs,
                               p->D, list, list_stride, list_len, lay.list_stride, p->out, p->B, p->H,

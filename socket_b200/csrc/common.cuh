@@ -49,6 +49,76 @@ __device__ __forceinline__ int effective_len(int64_t T, const int32_t* T_dev) {
     return t < 0 ? 0 : (int)t;
 }
 
+// ---------------------------------------------------------------- scorer work split
+// How the flat (KV-head group, key) space is cut into CTAs; shared by the scorer, which writes
+// per-(row, chunk, warp) candidate runs in its filtering mode, and the select kernel, which
+// reads them back.  chunk = CTA index - first CTA of the group.
+struct ScorePlan {
+    int64_t Tslots;       // slots per group (>= T; padded in the small mode)
+    int64_t per_cta;      // slots per CTA, multiple of 32
+    int64_t grid;         // CTAs
+    int chunks_max;       // upper bound of chunks per group
+    int cap_w;            // candidate capacity of one warp's run (filter mode)
+    float frac;           // fraction of keys the filter aims to keep
+};
+constexpr int SC_THREADS = 1024;
+constexpr int SC_WARPS = SC_THREADS / 32;
+constexpr int SEL_CAP = 16384;   // candidates the select kernel can hold on chip
+
+inline ScorePlan make_score_plan(int n_groups, int64_t T, int64_t M) {
+    ScorePlan p;
+    const int n_sm = 148;
+    const int64_t total = (int64_t)n_groups * T;
+    if (total / n_sm >= 16384) {
+        // large: split the flat (group, key) space evenly; a CTA may cross one group boundary
+        p.Tslots = T;
+        p.per_cta = (total + n_sm - 1) / n_sm;
+        p.per_cta = (p.per_cta + 31) / 32 * 32;
+        p.grid = (total + p.per_cta - 1) / p.per_cta;
+        p.chunks_max = (int)((T + p.per_cta - 1) / p.per_cta) + 1;
+    } else {
+        // small: whole CTAs per group, no CTA loads two tables
+        int64_t chunks = n_groups >= n_sm ? 1 : n_sm / n_groups;
+        const int64_t max_chunks = (T + 1023) / 1024;
+        if (chunks > max_chunks) chunks = max_chunks;
+        p.per_cta = (T + chunks - 1) / chunks;
+        p.per_cta = (p.per_cta + 31) / 32 * 32;
+        chunks = (T + p.per_cta - 1) / p.per_cta;
+        p.Tslots = chunks * p.per_cta;
+        p.grid = (int64_t)n_groups * chunks;
+        p.chunks_max = (int)chunks;
+    }
+    const int64_t per_warp = ((p.per_cta + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32;
+    double f = T > 0 ? 3.0 * (double)M / (double)T : 1.0;
+    if (f > 1.0) f = 1.0;
+    p.frac = (float)f;
+    p.cap_w = (int)((int64_t)(4.0 * f * (double)per_warp + 7) / 8 * 8) + 16;
+    return p;
+}
+// The filtering scorer pays off (and its buffers stay small) only for small k / T.
+inline bool fused_filter_applicable(const ScorePlan& p, int64_t T, int64_t M) {
+    return M > 0 && T >= 4096 && 12 * M <= T && 3 * M <= (SEL_CAP * 3) / 4 && p.chunks_max * SC_WARPS <= 1024;
+}
+
+// Workspace of the fused scorer + select: [fallback counter | cnt | cut | cand | scratch scores]
+struct FusedLayout {
+    size_t stats, cnt, cut, cand, scores, total;
+    int64_t score_stride;
+};
+inline size_t sk_up256(size_t x) { return (x + 255) & ~(size_t)255; }
+inline FusedLayout make_fused_layout(int64_t rows, const ScorePlan& p, int64_t T) {
+    FusedLayout f;
+    f.score_stride = (T + 3) / 4 * 4;
+    size_t off = 0;
+    f.stats = off;  off += 256;
+    f.cnt = off;    off += sk_up256((size_t)rows * p.chunks_max * SC_WARPS * sizeof(int32_t));
+    f.cut = off;    off += sk_up256((size_t)rows * p.chunks_max * sizeof(float));
+    f.cand = off;   off += sk_up256((size_t)rows * p.chunks_max * SC_WARPS * p.cap_w * 8);
+    f.scores = off; off += sk_up256((size_t)rows * f.score_stride * sizeof(float));
+    f.total = off;
+    return f;
+}
+
 // ---------------------------------------------------------------- launchers (one per .cu)
 int launch_hash_keys(const void* keys, int key_dtype, int64_t key_row_stride, const void* planes,
                      int plane_dtype, int64_t N, int D, int L, int P, void* codes, int code_bytes,
@@ -80,6 +150,16 @@ int launch_sparse_decode(const void* q, int q_dtype, const void* k_cache, const 
                          const int32_t* list_len, int64_t max_list_len, void* out, int B, int H,
                          int Hkv, int D, int64_t T, const int32_t* T_dev, void* workspace,
                          size_t workspace_bytes, int32_t* status, cudaStream_t st);
+
+// Filtering scorer + candidate select (fused path of the decode step)
+size_t score_select_workspace_bytes(int B, int H, int Hkv, int L, int64_t T, int64_t M);
+int launch_score_filter(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
+                        int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
+                        void* workspace, int32_t* status, cudaStream_t st);
+int launch_select_candidates(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
+                             int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
+                             int sink, int window, int sorted, int32_t* list, int64_t list_row_stride,
+                             int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st);
 
 int lut_head_tile(int rep);
 int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, int dtype,

@@ -20,8 +20,6 @@
 namespace sk {
 namespace {
 
-constexpr int SC_THREADS = 1024;
-constexpr int SC_WARPS = SC_THREADS / 32;
 constexpr uint32_t SC_WAIT_LIMIT = 1u << 20;   // bounded wait on the table copy
 constexpr int SC_COPY_CHUNK = 16384;
 
@@ -80,22 +78,84 @@ __device__ __forceinline__ void add_word(float (&acc)[HT], const char* p) {
     }
 }
 
-// L: tables per key (bytes per key), HT: query heads per table word.
+// Sum over the L tables of one key's table words (ht heads at once).
 template <int L, int HT>
+__device__ __forceinline__ void score_key(const uint4 (&c)[L / 16], const char* lut_s, uint32_t sel_lo,
+                                          uint32_t sel_hi, uint32_t mL, float (&acc)[HT]) {
+    constexpr int L_STRIDE = HT * 4;
+    constexpr int CODE_STRIDE = L * L_STRIDE;
+#pragma unroll
+    for (int j = 0; j < HT; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < L / 16; ++i) {
+        const uint32_t w[4] = {c[i].x, c[i].y, c[i].z, c[i].w};
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            // 8 tables: bytes permuted so that byte j holds table j ^ m
+            const uint32_t lo = __byte_perm(w[2 * half], w[2 * half + 1], sel_lo);
+            const uint32_t hi = __byte_perm(w[2 * half], w[2 * half + 1], sel_hi);
+            const int lbase = (i * 16 + half * 8) * L_STRIDE;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t src = j < 4 ? lo : hi;
+                const uint32_t code = (src >> (8 * (j & 3))) & 0xffu;
+                const uint32_t off = code * CODE_STRIDE + (((uint32_t)j * L_STRIDE) ^ mL);
+                add_word<HT>(acc, lut_s + lbase + off);
+            }
+        }
+    }
+}
+
+// Shared memory after the table: mbarrier | per-head sample statistics for the filter mode.
+struct FilterShared {
+    uint64_t bar;
+    float red_min[4][SC_WARPS], red_max[4][SC_WARPS];
+    float fmin[4], scale[4], cut[4];
+    uint32_t hist[4][256];
+};
+
+struct FilterArgs {
+    int32_t* cnt;        // [rows][chunks_max][32]
+    float* cut;          // [rows][chunks_max]
+    uint2* cand;         // [rows][chunks_max][32][cap_w]  (score bits, key index)
+    int chunks_max, cap_w;
+    float frac;
+};
+
+__device__ __forceinline__ void warp_hist_add256(uint32_t* hist, uint32_t bin, bool active) {
+    const unsigned live = __ballot_sync(FULL, active);
+    if (active) {
+        const unsigned peers = __match_any_sync(live, bin);
+        if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
+    }
+}
+
+// L: tables per key (bytes per key), HT: query heads per table word.
+// FILTER = false: every score is written to `scores`.
+// FILTER = true:  nothing is written for most keys.  Each CTA estimates, per head, a cut from
+//   the first 32 keys of each of its warps (a value histogram of up to 1024 scores) that about
+//   `frac` of the keys exceed, and every warp appends the (score, index) pairs >= cut to its own
+//   run of the row's candidate buffer — runs are ordered (chunk, warp, index), so the candidates
+//   of a row are in ascending index order without atomics.  The select kernel checks that the
+//   k-th largest candidate is >= every chunk's cut, which proves the candidate set contains the
+//   exact top-k; rows failing the check are rescored there.
+template <int L, int HT, bool FILTER>
 __global__ void __launch_bounds__(SC_THREADS, 1)
 score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
              const __half* __restrict__ v_norm, const uint8_t* __restrict__ allowed,
              float* __restrict__ scores, int64_t score_row_stride, int H, int Hkv, int R,
              int64_t T, const int32_t* __restrict__ T_dev, int64_t Tcap, int64_t Tslots,
-             int64_t slots_per_cta, int n_groups, int32_t* status) {
+             int64_t slots_per_cta, int n_groups, int32_t* status, FilterArgs fa) {
     static_assert(L % 16 == 0, "codes are read 16 bytes at a time");
+    static_assert(HT <= 4, "at most 4 heads per table word");
     constexpr int NV = L / 16;                 // uint4 per key
     constexpr int L_STRIDE = HT * 4;           // bytes between tables of one bucket
     constexpr int CODE_STRIDE = L * L_STRIDE;  // bytes between buckets
     extern __shared__ __align__(128) char smem_raw[];
     char* lut_s = smem_raw;
     // room for all 256 possible code values, so that no byte value can index past the table
-    uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw + (size_t)256 * CODE_STRIDE);
+    FilterShared& fs = *reinterpret_cast<FilterShared*>(smem_raw + (size_t)256 * CODE_STRIDE);
+    uint64_t* bar = &fs.bar;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rep = H / Hkv;
@@ -120,15 +180,28 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         const int g = (int)(slot / Tslots);
         const int64_t t0 = slot - (int64_t)g * Tslots;
         const int64_t seg_end = min((int64_t)(g + 1) * Tslots, slot_end);
-        int64_t t1 = seg_end - (int64_t)g * Tslots;
+        const int64_t t1_raw = seg_end - (int64_t)g * Tslots;
+        int64_t t1 = t1_raw;
         slot = seg_end;
         if (t1 > Teff) t1 = Teff;
-        if (t0 >= t1) continue;   // uniform across the CTA
 
         const int tile = g % tiles;
         const int bk = g / tiles;               // b*Hkv + kvh
         const int b = bk / Hkv, kvh = bk - b * Hkv;
         const int h0 = kvh * rep + tile * HT;
+        const size_t row0 = (size_t)b * H + h0;
+        const int chunk = (int)((int64_t)blockIdx.x - ((int64_t)g * Tslots) / slots_per_cta);
+
+        if (t0 >= t1) {   // uniform across the CTA: nothing live in this segment
+            if (FILTER) {
+                if (threadIdx.x < SC_WARPS * HT) {
+                    const int j = threadIdx.x / SC_WARPS, w = threadIdx.x % SC_WARPS;
+                    fa.cnt[((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + w] = 0;
+                }
+                if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
+            }
+            continue;
+        }
 
         // previous segment's lookups are done before the table is overwritten
         __syncthreads();
@@ -141,6 +214,28 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
                 bulk_g2s(lut_s + off, src + off, n, bar);
             }
         }
+        if (FILTER) {
+            for (int i = threadIdx.x; i < 4 * 256; i += SC_THREADS) (&fs.hist[0][0])[i] = 0;
+        }
+
+        // each warp owns a contiguous run of keys (a multiple of 32 long)
+        const int64_t per_warp = ((t1_raw - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32;
+        const int64_t ws = t0 + (int64_t)warp * per_warp;
+        const int64_t we = min(t1, ws + per_warp);
+        const uint4* cg = reinterpret_cast<const uint4*>(codes + (size_t)bk * Tcap * L);
+        const __half* vg = v_norm + (size_t)bk * Tcap;
+
+        uint4 cur[NV], nxt[NV];
+        int64_t t = ws + lane;
+        if (t < we) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) cur[i] = __ldg(cg + t * NV + i);
+        }
+        if (t + 32 < we) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (t + 32) * NV + i);
+        }
+
         const bool ok = mbar_wait(bar, phase);
         phase ^= 1u;
         if (!__syncthreads_and(ok)) {
@@ -148,59 +243,171 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             return;
         }
 
-        const uint4* cg = reinterpret_cast<const uint4*>(codes + (size_t)bk * Tcap * L);
-        const __half* vg = v_norm + (size_t)bk * Tcap;
-        const int64_t n_pieces = (t1 - t0 + 31) / 32;
-
-        uint4 cur[NV], nxt[NV];
-        int64_t piece = warp;
-        {
-            const int64_t t = t0 + piece * 32 + lane;
-            if (piece < n_pieces && t < t1) {
+        int cnt[HT];
+        float cutv[HT];
 #pragma unroll
-                for (int i = 0; i < NV; ++i) cur[i] = __ldg(cg + t * NV + i);
-            }
+        for (int j = 0; j < HT; ++j) {
+            cnt[j] = 0;
+            cutv[j] = -INFINITY;
         }
-        for (; piece < n_pieces; piece += SC_WARPS) {
-            const int64_t t = t0 + piece * 32 + lane;
-            const int64_t tn = t + (int64_t)SC_WARPS * 32;
-            if (piece + SC_WARPS < n_pieces && tn < t1) {
-#pragma unroll
-                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + tn * NV + i);
-            }
-            if (t < t1) {
+        bool first = true;
+
+        if (FILTER) {
+            // ---- sample = first key of every lane: scores, min / max, histogram, cut
+            float sv[HT];
+            const bool valid = t < we;
+            if (valid) {
                 float acc[HT];
-#pragma unroll
-                for (int j = 0; j < HT; ++j) acc[j] = 0.f;
-#pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    const uint32_t w[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        // 8 tables: bytes permuted so that byte j holds table j ^ m
-                        const uint32_t lo = __byte_perm(w[2 * half], w[2 * half + 1], sel_lo);
-                        const uint32_t hi = __byte_perm(w[2 * half], w[2 * half + 1], sel_hi);
-                        const int lbase = (i * 16 + half * 8) * L_STRIDE;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const uint32_t src = j < 4 ? lo : hi;
-                            const uint32_t code = (src >> (8 * (j & 3))) & 0xffu;
-                            const uint32_t off = code * CODE_STRIDE + (((uint32_t)j * L_STRIDE) ^ mL);
-                            add_word<HT>(acc, lut_s + lbase + off);
-                        }
-                    }
-                }
+                score_key<L, HT>(cur, lut_s, sel_lo, sel_hi, mL, acc);
                 const float vn = __half2float(vg[t]);
 #pragma unroll
+                for (int j = 0; j < HT; ++j) sv[j] = acc[j] * vn;
+            } else {
+#pragma unroll
+                for (int j = 0; j < HT; ++j) sv[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < HT; ++j) {
+                const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
+                float lo = fin ? sv[j] : INFINITY, hi = fin ? sv[j] : -INFINITY;
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) {
+                    lo = fminf(lo, __shfl_xor_sync(FULL, lo, o));
+                    hi = fmaxf(hi, __shfl_xor_sync(FULL, hi, o));
+                }
+                if (lane == 0) {
+                    fs.red_min[j][warp] = lo;
+                    fs.red_max[j][warp] = hi;
+                }
+            }
+            __syncthreads();
+            if (warp < HT) {
+                float lo = fs.red_min[warp][lane], hi = fs.red_max[warp][lane];
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) {
+                    lo = fminf(lo, __shfl_xor_sync(FULL, lo, o));
+                    hi = fmaxf(hi, __shfl_xor_sync(FULL, hi, o));
+                }
+                if (lane == 0) {
+                    fs.fmin[warp] = lo;
+                    fs.scale[warp] = hi > lo ? 254.0f / (hi - lo) : 0.f;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < HT; ++j) {
+                const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
+                const uint32_t bin = min(__float2uint_rz((sv[j] - fs.fmin[j]) * fs.scale[j]), 255u);
+                warp_hist_add256(fs.hist[j], fin ? bin : 0u, fin);
+            }
+            __syncthreads();
+            if (warp < HT) {
+                // bins in descending order, 8 per lane
+                uint32_t c[8], local = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    c[i] = fs.hist[warp][255 - (8 * lane + i)];
+                    local += c[i];
+                }
+                uint32_t inc = local;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t n = __shfl_up_sync(FULL, inc, o);
+                    if (lane >= o) inc += n;
+                }
+                const uint32_t n_samp = __shfl_sync(FULL, inc, 31);
+                uint32_t target = (uint32_t)ceilf(fa.frac * (float)n_samp) + 4u;
+                if (target > n_samp) target = n_samp;
+                uint32_t before = inc - local;
+                int found = -1;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (target > 0 && before < target && before + c[i] >= target) found = 255 - (8 * lane + i);
+                    before += c[i];
+                }
+                // exactly one lane finds the bin (none if the sample is empty)
+                const unsigned who = __ballot_sync(FULL, found >= 0);
+                float cut = -INFINITY;       // empty or degenerate sample: keep everything
+                if (who) {
+                    const int bin = __shfl_sync(FULL, found, __ffs(who) - 1);
+                    if (fs.scale[warp] > 0.f && bin >= 1) cut = fs.fmin[warp] + (float)bin / fs.scale[warp];
+                }
+                if (lane == 0) {
+                    fs.cut[warp] = cut;
+                    fa.cut[(row0 + warp) * fa.chunks_max + chunk] = cut;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < HT; ++j) cutv[j] = fs.cut[j];
+            // the sample keys themselves
+#pragma unroll
+            for (int j = 0; j < HT; ++j) {
+                const bool hit = valid && sv[j] >= cutv[j];
+                const unsigned bal = __ballot_sync(FULL, hit);
+                if (hit) {
+                    const int pos = cnt[j] + __popc(bal & ((1u << lane) - 1u));
+                    if (pos < fa.cap_w)
+                        fa.cand[(((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w + pos] =
+                            make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
+                }
+                cnt[j] += __popc(bal);
+            }
+            first = false;
+        }
+
+        // ---- main loop over this warp's keys, codes double-buffered in registers
+        if (!first) {
+            t += 32;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
+            if (t + 32 < we) {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (t + 32) * NV + i);
+            }
+        }
+        for (; t - lane < we; t += 32) {
+            const bool valid = t < we;
+            float sv[HT];
+            if (valid) {
+                float acc[HT];
+                score_key<L, HT>(cur, lut_s, sel_lo, sel_hi, mL, acc);
+                const float vn = __half2float(vg[t]);
+#pragma unroll
+                for (int j = 0; j < HT; ++j) sv[j] = acc[j] * vn;
+            }
+            if (FILTER) {
+#pragma unroll
                 for (int j = 0; j < HT; ++j) {
-                    const size_t row = (size_t)b * H + h0 + j;
-                    float s = acc[j] * vn;
-                    if (allowed != nullptr && allowed[row * T + t] == 0) s = -INFINITY;
-                    scores[row * score_row_stride + t] = s;
+                    const bool hit = valid && sv[j] >= cutv[j];
+                    const unsigned bal = __ballot_sync(FULL, hit);
+                    if (hit) {
+                        const int pos = cnt[j] + __popc(bal & ((1u << lane) - 1u));
+                        if (pos < fa.cap_w)
+                            fa.cand[(((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w + pos] =
+                                make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
+                    }
+                    cnt[j] += __popc(bal);
+                }
+            } else if (valid) {
+#pragma unroll
+                for (int j = 0; j < HT; ++j) {
+                    float sc = sv[j];
+                    if (allowed != nullptr && allowed[(row0 + j) * T + t] == 0) sc = -INFINITY;
+                    scores[(row0 + j) * score_row_stride + t] = sc;
                 }
             }
 #pragma unroll
             for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
+            if (t + 64 < we) {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (t + 64) * NV + i);
+            }
+        }
+        if (FILTER && lane == 0) {
+#pragma unroll
+            for (int j = 0; j < HT; ++j)
+                fa.cnt[((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp] = cnt[j];
         }
     }
 }
@@ -234,41 +441,20 @@ score_compat_kernel(const float* __restrict__ q_probs, const int16_t* __restrict
     }
 }
 
-template <int L, int HT>
+template <int L, int HT, bool FILTER>
 int score_launch(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
                  const uint8_t* allowed, int B, int H, int Hkv, int R, int64_t T,
                  const int32_t* T_dev, int64_t Tcap, float* scores, int64_t srs, int32_t* status,
-                 cudaStream_t st) {
+                 const ScorePlan& plan, FilterArgs fa, cudaStream_t st) {
     const int rep = H / Hkv;
     const int n_groups = B * Hkv * (rep / HT);
-    const size_t smem = (size_t)256 * L * HT * 4 + 16;
-    auto kern = score_kernel<L, HT>;
+    const size_t smem = (size_t)256 * L * HT * 4 + sizeof(FilterShared);
+    auto kern = score_kernel<L, HT, FILTER>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "score_kernel smem attribute: %s", cudaGetErrorString(e));
-    int n_sm = 148;
-    int64_t Tslots, per_cta;
-    int64_t grid;
-    const int64_t total = (int64_t)n_groups * T;
-    if (total / n_sm >= 16384) {
-        // large: split the flat (group, key) space evenly; a CTA may cross one group boundary
-        Tslots = T;
-        per_cta = (total + n_sm - 1) / n_sm;
-        per_cta = (per_cta + 31) / 32 * 32;
-        grid = (total + per_cta - 1) / per_cta;
-    } else {
-        // small: whole CTAs per group, no CTA loads two tables
-        int64_t chunks = n_groups >= n_sm ? 1 : n_sm / n_groups;
-        const int64_t max_chunks = (T + 1023) / 1024;
-        if (chunks > max_chunks) chunks = max_chunks;
-        per_cta = (T + chunks - 1) / chunks;
-        per_cta = (per_cta + 31) / 32 * 32;
-        chunks = (T + per_cta - 1) / per_cta;
-        Tslots = chunks * per_cta;
-        grid = (int64_t)n_groups * chunks;
-    }
-    kern<<<(unsigned)grid, SC_THREADS, smem, st>>>(lut, codes, (const __half*)v_norm, allowed, scores,
-                                                   srs, H, Hkv, R, T, T_dev, Tcap, Tslots, per_cta,
-                                                   n_groups, status);
+    kern<<<(unsigned)plan.grid, SC_THREADS, smem, st>>>(lut, codes, (const __half*)v_norm, allowed, scores,
+                                                        srs, H, Hkv, R, T, T_dev, Tcap, plan.Tslots,
+                                                        plan.per_cta, n_groups, status, fa);
     return check_launch("score_kernel");
 }
 
@@ -280,12 +466,14 @@ int launch_score(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
                  int32_t* status, cudaStream_t st) {
     if (T <= 0 || B * H == 0) return SK_OK;
     const int ht = lut_head_tile(H / Hkv);
-    if ((size_t)256 * L * ht * 4 + 16 > 227 * 1024)
+    if ((size_t)256 * L * ht * 4 + sizeof(FilterShared) > 227 * 1024)
         return fail(SK_ERR_UNSUPPORTED, "sk_score: table of R=%d L=%d does not fit shared memory", R, L);
+    const ScorePlan plan = make_score_plan(B * Hkv * ((H / Hkv) / ht), T, 0);
+    FilterArgs none{};
 #define SK_SCORE_CASE(LL, HT)                                                                    \
     if (L == LL && ht == HT)                                                                     \
-        return score_launch<LL, HT>(lut, codes, v_norm, allowed, B, H, Hkv, R, T, T_dev, Tcap,   \
-                                    scores, score_row_stride, status, st)
+        return score_launch<LL, HT, false>(lut, codes, v_norm, allowed, B, H, Hkv, R, T, T_dev,  \
+                                           Tcap, scores, score_row_stride, status, plan, none, st)
     SK_SCORE_CASE(32, 4);
     SK_SCORE_CASE(32, 2);
     SK_SCORE_CASE(32, 1);
@@ -296,6 +484,39 @@ int launch_score(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
     SK_SCORE_CASE(64, 1);
 #undef SK_SCORE_CASE
     return fail(SK_ERR_UNSUPPORTED, "sk_score: L=%d with %d heads per KV head not supported", L, H / Hkv);
+}
+
+size_t score_select_workspace_bytes(int B, int H, int Hkv, int L, int64_t T, int64_t M) {
+    (void)L;
+    if (B <= 0 || H <= 0 || Hkv <= 0 || T <= 0) return 256;
+    const int ht = lut_head_tile(H / Hkv);
+    const ScorePlan plan = make_score_plan(B * Hkv * ((H / Hkv) / ht), T, M);
+    return make_fused_layout((int64_t)B * H, plan, T).total;
+}
+
+int launch_score_filter(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
+                        int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
+                        void* workspace, int32_t* status, cudaStream_t st) {
+    const int ht = lut_head_tile(H / Hkv);
+    const ScorePlan plan = make_score_plan(B * Hkv * ((H / Hkv) / ht), T, M);
+    const FusedLayout lay = make_fused_layout((int64_t)B * H, plan, T);
+    char* ws = static_cast<char*>(workspace);
+    FilterArgs fa;
+    fa.cnt = reinterpret_cast<int32_t*>(ws + lay.cnt);
+    fa.cut = reinterpret_cast<float*>(ws + lay.cut);
+    fa.cand = reinterpret_cast<uint2*>(ws + lay.cand);
+    fa.chunks_max = plan.chunks_max;
+    fa.cap_w = plan.cap_w;
+    fa.frac = plan.frac;
+#define SK_SCORE_CASE(LL, HT)                                                                      \
+    if (L == LL && ht == HT)                                                                       \
+        return score_launch<LL, HT, true>(lut, codes, v_norm, nullptr, B, H, Hkv, R, T, T_dev, Tcap, \
+                                          nullptr, 0, status, plan, fa, st)
+    SK_SCORE_CASE(32, 4);
+    SK_SCORE_CASE(32, 2);
+    SK_SCORE_CASE(32, 1);
+#undef SK_SCORE_CASE
+    return fail(SK_ERR_UNSUPPORTED, "fused scorer: L=%d with %d heads per KV head not supported", L, H / Hkv);
 }
 
 int launch_score_compat(const float* q_probs, const int16_t* key_buckets, const uint8_t* allowed,

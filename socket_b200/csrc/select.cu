@@ -5,12 +5,13 @@
 // scans), so the output is a pure function of the scores.
 //
 // The exact work always happens on chip, on a candidate set held in shared memory (up to
-// SEL_CAP entries, kept in index order): a 4 x 8-bit radix select finds the k-th key and the
-// number of ties to take, an ordered scan emits the winners.  How the candidates get there:
+// SEL_CAP entries, kept in index order): a radix select on (key - min), 12 bits per pass, finds
+// the k-th key and the number of ties to take, an ordered scan emits the winners.  How the
+// candidates get there:
 //   * rows with T <= SEL_CAP: the whole row;
-//   * longer rows, main path: 8192 strided samples are radix-selected for a cut that about
-//     2k elements exceed; ONE streaming pass (16-byte loads, 16 elements per thread and scan)
-//     then collects every element >= cut.  If the collected set turns out smaller than k or
+//   * longer rows, main path: a 4096-bin value histogram of 8192 strided samples gives a cut
+//     that about 2k elements exceed; ONE streaming pass (16-byte loads, 16 elements per thread
+//     and scan) then collects every element >= cut.  If the collected set turns out smaller than k or
 //     larger than the buffer, the row is redone by
 //   * the two-pass path: a 4096-bin histogram (bins linear in the key between the sampled
 //     min and max, clamped outside, hence monotone) finds the bin holding the k-th element;
@@ -25,7 +26,6 @@ namespace {
 
 constexpr int SEL_THREADS = 1024;
 constexpr int SEL_WARPS = SEL_THREADS / 32;
-constexpr int SEL_CAP = 16384;
 constexpr int SEL_BINS = 4096;
 constexpr int SEL_EPT = 8;                        // consecutive elements per thread (two-pass path)
 constexpr int SEL_CHUNK = SEL_THREADS * SEL_EPT;
@@ -40,7 +40,6 @@ struct SelShared {
     int scan_buf[2][40];
     uint32_t red_lo[SEL_WARPS], red_hi[SEL_WARPS];
     int thr_bin, thr_above, thr_inbin;
-    uint32_t digit, digit_above;
 };
 
 struct Scan {
@@ -89,36 +88,6 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
     return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
 }
 
-// One 8-bit radix step over hist[0..256): finds the digit d with
-// #(digit > d) < remaining <= #(digit >= d).  Executed by warp 0; results in shared memory.
-__device__ __forceinline__ void find_digit(SelShared& s, uint32_t remaining) {
-    if (threadIdx.x < 32) {
-        const int lane = threadIdx.x;
-        uint32_t c[8];
-        uint32_t local = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            c[j] = s.hist[255 - (8 * lane + j)];
-            local += c[j];
-        }
-        uint32_t inc = local;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t n = __shfl_up_sync(FULL, inc, o);
-            if (lane >= o) inc += n;
-        }
-        uint32_t before = inc - local;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (before < remaining && before + c[j] >= remaining) {
-                s.digit = 255 - (8 * lane + j);
-                s.digit_above = before;
-            }
-            before += c[j];
-        }
-    }
-}
-
 // Histogram increment with the lanes of a warp that hit the same bin merged into one atomic
 // (score keys share their high bits, so without this thousands of atomics would serialise on
 // one address).  Must be called by all 32 lanes.
@@ -130,65 +99,97 @@ __device__ __forceinline__ void warp_hist_add(uint32_t* hist, uint32_t bin, bool
     }
 }
 
-// k-th largest (k >= 1) of keys[0..n) in shared memory, n >= k.  Returns the key; `quota` =
-// how many elements equal to it belong to the top k.  Radix select, 8 bits per pass, over the
-// bits in which the keys actually differ (found from their min and max).
-__device__ __forceinline__ uint32_t smem_kth(SelShared& s, const uint32_t* keys, int n, uint32_t k,
-                                             uint32_t& quota) {
+// Block-wide min / max of one uint32 per thread; every thread gets the result.
+__device__ __forceinline__ void block_minmax(SelShared& s, uint32_t& lo, uint32_t& hi) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(FULL, lo, o));
+        hi = max(hi, __shfl_xor_sync(FULL, hi, o));
+    }
+    if (lane == 0) {
+        s.red_lo[warp] = lo;
+        s.red_hi[warp] = hi;
+    }
+    __syncthreads();
+    lo = s.red_lo[lane];
+    hi = s.red_hi[lane];
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(FULL, lo, o));
+        hi = max(hi, __shfl_xor_sync(FULL, hi, o));
+    }
+    __syncthreads();                                   // red_lo / red_hi may be reused
+}
+
+// Over hist[0..SEL_BINS): the bin b with  #(bins > b) < target <= #(bins >= b)  (target >= 1,
+// total count >= target).  All threads take part (4 bins each, descending); result in shared
+// memory, valid after the trailing barrier.
+__device__ __forceinline__ void find_bin_desc(SelShared& s, Scan& scan, int target) {
+    int c[4], local = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        c[j] = (int)s.hist[SEL_BINS - 1 - (4 * threadIdx.x + j)];
+        local += c[j];
+    }
+    int total;
+    int before = scan.excl(local, total, s);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (before < target && before + c[j] >= target) {
+            s.thr_bin = SEL_BINS - 1 - (4 * threadIdx.x + j);
+            s.thr_above = before;
+            s.thr_inbin = c[j];
+        }
+        before += c[j];
+    }
+    __syncthreads();
+}
+
+// k-th largest (k >= 1) of keys[0..n) in shared memory, n >= k.  Returns the key; `quota` =
+// how many elements equal to it belong to the top k.  Radix select on (key - min) with up to
+// 12 bits per pass, so score keys that span a few octaves need two passes.
+__device__ __forceinline__ uint32_t smem_kth(SelShared& s, Scan& scan, const uint32_t* keys, int n,
+                                             uint32_t k, uint32_t& quota) {
     uint32_t kmin = 0xffffffffu, kmax = 0u;
     for (int i = threadIdx.x; i < n; i += SEL_THREADS) {
         const uint32_t key = keys[i];
         kmin = min(kmin, key);
         kmax = max(kmax, key);
     }
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) {
-        kmin = min(kmin, __shfl_xor_sync(FULL, kmin, o));
-        kmax = max(kmax, __shfl_xor_sync(FULL, kmax, o));
-    }
-    if (lane == 0) {
-        s.red_lo[warp] = kmin;
-        s.red_hi[warp] = kmax;
-    }
-    __syncthreads();
-    kmin = s.red_lo[lane];
-    kmax = s.red_hi[lane];
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) {
-        kmin = min(kmin, __shfl_xor_sync(FULL, kmin, o));
-        kmax = max(kmax, __shfl_xor_sync(FULL, kmax, o));
-    }
-    __syncthreads();                                   // red_lo / red_hi may be reused
-    int hi = 32 - __clz(kmin ^ kmax);                  // bits [0, hi) may differ
+    block_minmax(s, kmin, kmax);
+    const uint32_t range = kmax - kmin;
+    int hi = range == 0 ? 0 : 32 - __clz(range);       // bits [0, hi) of (key - kmin) may be set
+    const int n_pass = (hi + 11) / 12;
+    const int width = n_pass ? (hi + n_pass - 1) / n_pass : 0;
     uint32_t mask = hi >= 32 ? 0u : ~((1u << hi) - 1u);
-    uint32_t prefix = kmin & mask;
+    uint32_t prefix = 0;
     uint32_t remaining = k;
     while (hi > 0) {
-        const int lo = max(hi - 8, 0);
+        const int lo = max(hi - width, 0);
         const uint32_t dmask = (1u << (hi - lo)) - 1u;
-        for (int i = threadIdx.x; i < 256; i += SEL_THREADS) s.hist[i] = 0;
+        for (int i = threadIdx.x; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
         __syncthreads();
         for (int base = 0; base < n; base += SEL_THREADS) {
             const int i = base + threadIdx.x;
-            uint32_t key = 0;
+            uint32_t kp = 0;
             bool active = false;
             if (i < n) {
-                key = keys[i];
-                active = (key & mask) == prefix;
+                kp = keys[i] - kmin;
+                active = (kp & mask) == prefix;
             }
-            warp_hist_add(s.hist, (key >> lo) & dmask, active);
+            warp_hist_add(s.hist, (kp >> lo) & dmask, active);
         }
         __syncthreads();
-        find_digit(s, remaining);
-        __syncthreads();
-        remaining -= s.digit_above;
-        prefix |= s.digit << lo;
+        find_bin_desc(s, scan, (int)remaining);
+        remaining -= (uint32_t)s.thr_above;
+        prefix |= (uint32_t)s.thr_bin << lo;
         mask |= dmask << lo;
         hi = lo;
+        __syncthreads();                               // thr_* are rewritten by the next pass
     }
     quota = remaining;
-    return prefix;
+    return kmin + prefix;
 }
 
 // N consecutive scores starting at t0 (a multiple of 4); positions >= T read as 0 and are
@@ -208,43 +209,41 @@ __device__ __forceinline__ void load_scores(const float* __restrict__ sc, int t0
     }
 }
 
-__global__ void __launch_bounds__(SEL_THREADS, 1)
-select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
-                   const uint8_t* __restrict__ allowed, int64_t T_host,
-                   const int32_t* __restrict__ T_dev, int64_t M, int sink_in, int window_in,
-                   int sorted, int32_t* __restrict__ list, int64_t list_row_stride,
-                   int32_t* __restrict__ list_len) {
-    extern __shared__ __align__(16) char smem_raw[];
-    SelShared& s = *reinterpret_cast<SelShared*>(smem_raw);
+// Exact top-`need` of the n_cand candidates in shared memory (index order) -> heavy[out_pos..),
+// ties at the cut resolved towards the front (= the smallest indices).  Returns the k-th key.
+__device__ __forceinline__ uint32_t emit_from_candidates(SelShared& s, Scan& scan, int n_cand, int need,
+                                                         int out_pos, int Me, int32_t* __restrict__ heavy) {
+    const int tid = threadIdx.x;
+    uint32_t quota;
+    const uint32_t kth = smem_kth(s, scan, s.cand_key, n_cand, (uint32_t)need, quota);
+    int gt_base = 0, eq_base = 0;
+    for (int base = 0; base < n_cand; base += SEL_THREADS) {
+        const int i = base + tid;
+        uint32_t k = 0;
+        int idx = 0;
+        const bool live = i < n_cand;
+        if (live) {
+            k = s.cand_key[i];
+            idx = s.cand_idx[i];
+        }
+        const int gt = live && k > kth, eq = live && k == kth;
+        int total;
+        const int off = scan.excl(gt | (eq << 16), total, s);
+        const int gt_before = gt_base + (off & 0xffff);
+        const int eq_before = eq_base + (off >> 16);
+        const int dst = out_pos + gt_before + min(eq_before, (int)quota);
+        if ((gt || (eq && eq_before < (int)quota)) && dst < Me) heavy[dst] = idx;
+        gt_base += total & 0xffff;
+        eq_base += total >> 16;
+    }
+    return kth;
+}
+
+// Top-`Me` (0 < Me) of one row of T scores -> heavy[0..Me).  Exact; see the file header.
+__device__ __forceinline__ void select_row(SelShared& s, Scan& scan, const float* __restrict__ sc, int T,
+                                           int Me, int32_t* __restrict__ heavy) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int64_t row = blockIdx.x;
-    const float* sc = scores + row * score_row_stride;
-    const uint8_t* al = allowed ? allowed + row * T_host : nullptr;
-    int32_t* out = list + row * list_row_stride;
-    const int T = effective_len(T_host, T_dev);
     const bool vec = (reinterpret_cast<uintptr_t>(sc) & 15u) == 0;
-    Scan scan;
-
-    if (T <= 0) {
-        if (tid == 0) list_len[row] = 0;
-        return;
-    }
-    // ---- structured part: sink prefix and local window
-    const int sink = max(0, min(sink_in, T));
-    const int window = max(0, min(window_in, T));
-    const int win_start = max(T - window, sink);
-    const int n_win = window > 0 ? T - win_start : 0;
-    int nb = sink + n_win;
-    for (int i = tid; i < sink; i += SEL_THREADS) out[i] = i;
-    for (int i = tid; i < n_win; i += SEL_THREADS) out[sink + i] = win_start + i;
-    if (nb == 0) {
-        if (tid == 0) out[0] = T - 1;
-        nb = 1;
-    }
-    const int Me = (int)(M < (int64_t)T ? M : (int64_t)T);
-    if (tid == 0) list_len[row] = nb + Me;
-    int32_t* heavy = out + nb;
-
     if (Me == T) {
         for (int i = tid; i < T; i += SEL_THREADS) heavy[i] = i;
     } else if (Me > 0) {
@@ -266,18 +265,40 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
             const int stride = T / SEL_SAMPLES;                     // >= 2
             const int64_t rs64 = (2 * (int64_t)Me * SEL_SAMPLES + T - 1) / T + 32;
             if (rs64 <= SEL_SAMPLES / 4 && rs64 * stride <= SEL_CAP / 2) {
-                const uint32_t r_s = (uint32_t)rs64;
-                for (int i = tid; i < SEL_SAMPLES; i += SEL_THREADS)
-                    s.cand_key[i] = order_key(__ldg(sc + (size_t)i * stride));
-                __syncthreads();
-                uint32_t quota;
-                const uint32_t cut_key = smem_kth(s, s.cand_key, SEL_SAMPLES, r_s, quota);
-                const float cut = key_to_float(cut_key);
-                __syncthreads();                                    // samples are consumed
+                // 8 strided samples per thread -> value histogram -> cut with ~r_s samples above
+                float fs[8];
+                uint32_t flo = 0xffffffffu, fhi = 0u;               // order keys of the finite samples
+                // one 32-byte run of 8 consecutive scores per thread, runs spread evenly over the
+                // row: 8192 samples for 1024 memory requests
+                load_scores<8>(sc, (int)(((int64_t)tid * (T - 8) / SEL_THREADS) & ~3), T, vec, fs);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (fs[j] > -INFINITY && fs[j] < INFINITY) {
+                        const uint32_t key = order_key(fs[j]);
+                        flo = min(flo, key);
+                        fhi = max(fhi, key);
+                    }
+                }
+                for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
+                block_minmax(s, flo, fhi);
+                const float fmin = key_to_float(flo), fmax = key_to_float(fhi);
+                float cut = INFINITY;
+                if (flo < fhi) {
+                    const float scale = (float)(SEL_BINS - 2) / (fmax - fmin);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t b = min(__float2uint_rz((fs[j] - fmin) * scale), (uint32_t)(SEL_BINS - 1));
+                        warp_hist_add(s.hist, b, true);
+                    }
+                    __syncthreads();
+                    find_bin_desc(s, scan, (int)rs64);
+                    if (s.thr_bin >= 1) cut = fmin + (float)s.thr_bin / scale;
+                    __syncthreads();
+                }
                 int base_cnt = 0;
                 float cur[SEL_EPT1], nxt[SEL_EPT1];
                 load_scores<SEL_EPT1>(sc, tid * SEL_EPT1, T, vec, cur);
-                for (int base = 0; base < T; base += SEL_CHUNK1) {
+                for (int base = 0; base < T && cut < INFINITY; base += SEL_CHUNK1) {
                     const int t0 = base + tid * SEL_EPT1;
                     if (base + SEL_CHUNK1 < T) load_scores<SEL_EPT1>(sc, t0 + SEL_CHUNK1, T, vec, nxt);
                     unsigned hit = 0;
@@ -360,26 +381,7 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
                         warp_hist_add(s.hist, (uint32_t)bin(order_key(fb[j])), tb + j < T);
                 }
                 __syncthreads();
-                {
-                    int c[4], local = 0;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        c[j] = (int)s.hist[SEL_BINS - 1 - (4 * tid + j)];
-                        local += c[j];
-                    }
-                    int total;
-                    int before = scan.excl(local, total, s);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (before < Me && before + c[j] >= Me) {
-                            s.thr_bin = SEL_BINS - 1 - (4 * tid + j);
-                            s.thr_above = before;
-                            s.thr_inbin = c[j];
-                        }
-                        before += c[j];
-                    }
-                }
-                __syncthreads();
+                find_bin_desc(s, scan, Me);
                 const int thr = s.thr_bin;
                 const int above = s.thr_above;
                 const int inbin = s.thr_inbin;
@@ -440,34 +442,12 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
         }
 
         if (have_cand) {
-            // ---- exact select among the on-chip candidates
-            uint32_t quota;
-            const uint32_t kth = smem_kth(s, s.cand_key, n_cand, (uint32_t)need, quota);
-            int gt_base = 0, eq_base = 0;
-            for (int base = 0; base < n_cand; base += SEL_THREADS) {
-                const int i = base + tid;
-                uint32_t k = 0;
-                int idx = 0;
-                const bool live = i < n_cand;
-                if (live) {
-                    k = s.cand_key[i];
-                    idx = s.cand_idx[i];
-                }
-                const int gt = live && k > kth, eq = live && k == kth;
-                int total;
-                const int off = scan.excl(gt | (eq << 16), total, s);
-                const int gt_before = gt_base + (off & 0xffff);
-                const int eq_before = eq_base + (off >> 16);
-                const int dst = out_pos + gt_before + min(eq_before, (int)quota);
-                if ((gt || (eq && eq_before < (int)quota)) && dst < Me) heavy[dst] = idx;
-                gt_base += total & 0xffff;
-                eq_base += total >> 16;
-            }
+            emit_from_candidates(s, scan, n_cand, need, out_pos, Me, heavy);
         } else if (global_fallback) {
             // ---- fallback: radix select over the whole row in global memory
             uint32_t prefix = 0, mask = 0, remaining = (uint32_t)Me;
             for (int shift = 24; shift >= 0; shift -= 8) {
-                for (int i = tid; i < 256; i += SEL_THREADS) s.hist[i] = 0;
+                for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
                 __syncthreads();
                 for (int base = 0; base < T; base += SEL_THREADS) {
                     const int t = base + tid;
@@ -475,11 +455,11 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
                     warp_hist_add(s.hist, (k >> shift) & 0xffu, t < T && (k & mask) == prefix);
                 }
                 __syncthreads();
-                find_digit(s, remaining);
-                __syncthreads();
-                remaining -= s.digit_above;
-                prefix |= s.digit << shift;
+                find_bin_desc(s, scan, (int)remaining);
+                remaining -= (uint32_t)s.thr_above;
+                prefix |= (uint32_t)s.thr_bin << shift;
                 mask |= 0xffu << shift;
+                __syncthreads();
             }
             int gt_base = 0, eq_base = 0;
             for (int base = 0; base < T; base += SEL_CHUNK) {
@@ -512,8 +492,31 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
             }
         }
     }
-    __syncthreads();
+}
 
+// Structured part of the list ([0..sink) ++ [max(T-window,sink)..T), or [T-1]); returns its length.
+__device__ __forceinline__ int write_base(int32_t* __restrict__ out, int T, int sink_in, int window_in) {
+    const int tid = threadIdx.x;
+    const int sink = max(0, min(sink_in, T));
+    const int window = max(0, min(window_in, T));
+    const int win_start = max(T - window, sink);
+    const int n_win = window > 0 ? T - win_start : 0;
+    int nb = sink + n_win;
+    for (int i = tid; i < sink; i += SEL_THREADS) out[i] = i;
+    for (int i = tid; i < n_win; i += SEL_THREADS) out[sink + i] = win_start + i;
+    if (nb == 0) {
+        if (tid == 0) out[0] = T - 1;
+        nb = 1;
+    }
+    return nb;
+}
+
+// Optional descending-score order of the top-k part, then the -1 masking of the whole list.
+__device__ __forceinline__ void finish_row(SelShared& s, const float* __restrict__ sc,
+                                           const uint8_t* __restrict__ al, int32_t* __restrict__ out,
+                                           int nb, int Me, int sorted) {
+    const int tid = threadIdx.x;
+    int32_t* heavy = out + nb;
     // ---- optional: order the top-k part by descending score (ties: ascending index)
     if (sorted && Me > 1) {
         uint64_t* keys = reinterpret_cast<uint64_t*>(s.cand_key);  // spans cand_key + cand_idx
@@ -558,6 +561,159 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
     }
 }
 
+__global__ void __launch_bounds__(SEL_THREADS, 1)
+select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
+                   const uint8_t* __restrict__ allowed, int64_t T_host,
+                   const int32_t* __restrict__ T_dev, int64_t M, int sink_in, int window_in,
+                   int sorted, int32_t* __restrict__ list, int64_t list_row_stride,
+                   int32_t* __restrict__ list_len) {
+    extern __shared__ __align__(16) char smem_raw[];
+    SelShared& s = *reinterpret_cast<SelShared*>(smem_raw);
+    const int tid = threadIdx.x;
+    const int64_t row = blockIdx.x;
+    const float* sc = scores + row * score_row_stride;
+    const uint8_t* al = allowed ? allowed + row * T_host : nullptr;
+    int32_t* out = list + row * list_row_stride;
+    const int T = effective_len(T_host, T_dev);
+    Scan scan;
+    if (T <= 0) {
+        if (tid == 0) list_len[row] = 0;
+        return;
+    }
+    const int nb = write_base(out, T, sink_in, window_in);
+    const int Me = (int)(M < (int64_t)T ? M : (int64_t)T);
+    if (tid == 0) list_len[row] = nb + Me;
+    if (Me > 0) select_row(s, scan, sc, T, Me, out + nb);
+    __syncthreads();
+    finish_row(s, sc, al, out, nb, Me, sorted);
+}
+
+
+// ------------------------------------------------------------------------------------------
+// Candidate mode: the filtering scorer left, per row, runs of (score, index) pairs in
+// ascending index order plus the cut each chunk used.  Gather them on chip, select exactly,
+// and accept the result only if the k-th key is >= every chunk's cut (then every element of
+// the true top-k was kept by its chunk).  Otherwise rescore the row here and select from the
+// full row.
+// ------------------------------------------------------------------------------------------
+struct CandArgs {
+    const int32_t* cnt;     // [rows][chunks_max][32]
+    const float* cut;       // [rows][chunks_max]
+    const uint2* cand;      // [rows][chunks_max][32][cap_w]
+    float* scratch;         // [rows][score_stride]
+    int32_t* n_fallback;    // statistics: rows that had to be rescored
+    int64_t score_stride;
+    int chunks_max, cap_w;
+    int64_t Tslots, per_cta;
+    // for the rescoring path
+    const float* lut;
+    const uint8_t* codes;
+    const __half* v_norm;
+    int H, Hkv, L, R, ht;
+    int64_t Tcap;
+};
+
+__global__ void __launch_bounds__(SEL_THREADS, 1)
+select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev, int64_t M,
+                   int sink_in, int window_in, int sorted, int32_t* __restrict__ list,
+                   int64_t list_row_stride, int32_t* __restrict__ list_len) {
+    extern __shared__ __align__(16) char smem_raw[];
+    SelShared& s = *reinterpret_cast<SelShared*>(smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t row = blockIdx.x;
+    int32_t* out = list + row * list_row_stride;
+    const int T = effective_len(T_host, T_dev);
+    Scan scan;
+    if (T <= 0) {
+        if (tid == 0) list_len[row] = 0;
+        return;
+    }
+    const int nb = write_base(out, T, sink_in, window_in);
+    const int Me = (int)(M < (int64_t)T ? M : (int64_t)T);
+    if (tid == 0) list_len[row] = nb + Me;
+    int32_t* heavy = out + nb;
+    float* sc = a.scratch + row * a.score_stride;
+
+    // which scorer chunks belong to this row's KV-head group
+    const int rep = a.H / a.Hkv, tiles = rep / a.ht;
+    const int b = (int)(row / a.H), h = (int)(row - (int64_t)b * a.H);
+    const int kvh = h / rep, hj = h - kvh * rep;
+    const int g = (b * a.Hkv + kvh) * tiles + hj / a.ht;
+    const int64_t first_cta = ((int64_t)g * a.Tslots) / a.per_cta;
+    const int64_t last_cta = ((int64_t)(g + 1) * a.Tslots - 1) / a.per_cta;
+    const int n_runs = (int)(last_cta - first_cta + 1) * SC_WARPS;      // <= 1024
+    const int32_t* cnt = a.cnt + row * a.chunks_max * SC_WARPS;
+
+    bool exact = false;
+    if (Me > 0 && Me < T) {
+        // ---- run lengths -> offsets (one run per thread), largest cut
+        int c = 0;
+        if (tid < n_runs) c = cnt[tid];
+        const bool over = c > a.cap_w;
+        float cutv = -INFINITY;
+        if (tid < n_runs / SC_WARPS) cutv = a.cut[row * a.chunks_max + tid];
+        int total;
+        const int off = scan.excl(c, total, s);
+        const int any_over = __syncthreads_or(over);
+        uint32_t clo = 0xffffffffu, chi = order_key(cutv);
+        block_minmax(s, clo, chi);                     // chi = key of the largest cut
+        if (!any_over && total >= Me && total <= SEL_CAP) {
+            // ---- gather: stash (offset, count) per run, then one warp per run, coalesced
+            if (tid < n_runs) {
+                s.hist[2 * tid] = (uint32_t)off;
+                s.hist[2 * tid + 1] = (uint32_t)c;
+            }
+            __syncthreads();
+            const uint2* cand = a.cand + row * a.chunks_max * SC_WARPS * a.cap_w;
+            for (int r = warp; r < n_runs; r += SEL_WARPS) {
+                const int o = (int)s.hist[2 * r], n = (int)s.hist[2 * r + 1];
+                const uint2* src = cand + (size_t)r * a.cap_w;
+                for (int i = lane; i < n; i += 32) {
+                    const uint2 e = __ldg(src + i);
+                    s.cand_key[o + i] = order_key(__uint_as_float(e.x));
+                    s.cand_idx[o + i] = (int32_t)e.y;
+                }
+            }
+            __syncthreads();
+            const uint32_t kth = emit_from_candidates(s, scan, total, Me, 0, Me, heavy);
+            exact = kth >= chi;                        // uniform: kth and chi are block-wide values
+        }
+        if (!exact) {
+            // ---- rescore this row (tables added in ascending order), then the full-row select
+            if (tid == 0) atomicAdd(a.n_fallback, 1);
+            __syncthreads();
+            float* tab = reinterpret_cast<float*>(s.cand_key);           // [L][R] of this head
+            const float* lut_g = a.lut + (size_t)g * a.R * a.L * a.ht;
+            const int j = hj % a.ht;
+            for (int i = tid; i < a.L * a.R; i += SEL_THREADS) {
+                const int l = i / a.R, r = i - l * a.R;
+                tab[i] = lut_g[((size_t)r * a.L + l) * a.ht + j];
+            }
+            __syncthreads();
+            const uint8_t* cg = a.codes + (size_t)(b * a.Hkv + kvh) * a.Tcap * a.L;
+            const __half* vg = a.v_norm + (size_t)(b * a.Hkv + kvh) * a.Tcap;
+            for (int t = tid; t < T; t += SEL_THREADS) {
+                const uint4* cp = reinterpret_cast<const uint4*>(cg + (size_t)t * a.L);
+                float sum = 0.f;
+                for (int v = 0; v < a.L / 16; ++v) {
+                    const uint4 w4 = __ldg(cp + v);
+                    const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
+                        sum += tab[(v * 16 + q) * a.R + ((w[q >> 2] >> (8 * (q & 3))) & 0xffu)];
+                }
+                sc[t] = sum * __half2float(vg[t]);
+            }
+            __syncthreads();
+            select_row(s, scan, sc, T, Me, heavy);
+        }
+    } else if (Me == T) {
+        for (int i = tid; i < T; i += SEL_THREADS) heavy[i] = i;
+    }
+    __syncthreads();
+    finish_row(s, sc, nullptr, out, nb, Me, 0);
+}
+
 }  // namespace
 
 int launch_select_list(const float* scores, int64_t score_row_stride, const uint8_t* allowed,
@@ -577,6 +733,44 @@ int launch_select_list(const float* scores, int64_t score_row_stride, const uint
         scores, score_row_stride, allowed, T, T_dev, M, sink, window, sorted, list, list_row_stride,
         list_len);
     return check_launch("select_list_kernel");
+}
+
+int launch_select_candidates(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
+                             int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
+                             int sink, int window, int sorted, int32_t* list, int64_t list_row_stride,
+                             int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st) {
+    (void)status;
+    if (sorted) return fail(SK_ERR_UNSUPPORTED, "fused score+select: sorted output not supported");
+    const int ht = lut_head_tile(H / Hkv);
+    const ScorePlan plan = make_score_plan(B * Hkv * ((H / Hkv) / ht), T, M);
+    const int64_t rows = (int64_t)B * H;
+    const FusedLayout lay = make_fused_layout(rows, plan, T);
+    char* ws = static_cast<char*>(workspace);
+    CandArgs a;
+    a.cnt = reinterpret_cast<const int32_t*>(ws + lay.cnt);
+    a.cut = reinterpret_cast<const float*>(ws + lay.cut);
+    a.cand = reinterpret_cast<const uint2*>(ws + lay.cand);
+    a.scratch = reinterpret_cast<float*>(ws + lay.scores);
+    a.n_fallback = reinterpret_cast<int32_t*>(ws + lay.stats);
+    a.score_stride = lay.score_stride;
+    a.chunks_max = plan.chunks_max;
+    a.cap_w = plan.cap_w;
+    a.Tslots = plan.Tslots;
+    a.per_cta = plan.per_cta;
+    a.lut = lut;
+    a.codes = codes;
+    a.v_norm = reinterpret_cast<const __half*>(v_norm);
+    a.H = H; a.Hkv = Hkv; a.L = L; a.R = R; a.ht = ht;
+    a.Tcap = Tcap;
+    if ((size_t)L * R * 4 > sizeof(uint32_t) * SEL_CAP)
+        return fail(SK_ERR_UNSUPPORTED, "fused score+select: L*R too large for the rescoring table");
+    const size_t smem = sizeof(SelShared);
+    cudaError_t e = cudaFuncSetAttribute(select_cand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "select_cand_kernel smem attribute: %s", cudaGetErrorString(e));
+    select_cand_kernel<<<(unsigned)rows, SEL_THREADS, smem, st>>>(a, T, T_dev, M, sink, window, sorted, list,
+                                                                 list_row_stride, list_len);
+    return check_launch("select_cand_kernel");
 }
 
 }  // namespace sk

@@ -196,6 +196,32 @@ def select_list(scores: torch.Tensor, T: int, M: int, sink: int, window: int,
     return lst, ln
 
 
+def score_select_applicable(B: int, H: int, Hkv: int, L: int, R: int, T: int, M: int) -> bool:
+    return bool(lib().sk_score_select_applicable(B, H, Hkv, L, R, T, M))
+
+
+def score_select_list(lut: torch.Tensor, codes: torch.Tensor, v_norm: torch.Tensor, n_heads: int, T: int,
+                      M: int, sink: int, window: int, R: int = 256,
+                      T_dev: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None):
+    """Fused scorer + select (`sk_score_select_list`): the list of `score` followed by
+    `select_list`, without the score array.  Returns (sparse_list, sparse_len, workspace); the
+    first int32 of the workspace counts the rows that had to be rescored so far."""
+    _require_cuda(lut, codes, v_norm)
+    B, Hkv, Tcap, L = codes.shape
+    M = min(M, T)
+    Ktot = list_len(T, sink, window, M)
+    lst = torch.empty(B, n_heads, Ktot, dtype=torch.int32, device=codes.device)
+    ln = torch.empty(B, n_heads, dtype=torch.int32, device=codes.device)
+    need = int(lib().sk_score_select_workspace_bytes(B, n_heads, Hkv, L, T, M))
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.zeros(need, dtype=torch.uint8, device=codes.device)
+    check(lib().sk_score_select_list(ptr(lut), ptr(codes), ptr(v_norm), B, n_heads, Hkv, L, R, T, ptr(T_dev),
+                                     Tcap, M, sink, window, ptr(lst), Ktot, ptr(ln), ptr(workspace),
+                                     workspace.numel(), None, stream_ptr(codes.device)),
+          "sk_score_select_list")
+    return lst, ln, workspace
+
+
 def sparse_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   sparse_list: torch.Tensor, sparse_len: torch.Tensor, T: Optional[int] = None,
                   T_dev: Optional[torch.Tensor] = None,

@@ -410,3 +410,68 @@ def test_run_to_run_determinism():
         outs.append((lst.clone(), sc.clone(), o.clone()))
     for a in outs[1:]:
         assert all(torch.equal(x, y) for x, y in zip(a, outs[0]))
+
+
+# ---------------------------------------------------------------------------- fused scorer + select
+def _fused_vs_two_step(B, H, Hkv, T, M, sink, window, v_norm=None, seed=0, Tcap=None):
+    g = torch.Generator().manual_seed(seed)
+    Tcap = Tcap or T
+    q = torch.randn(B, H, 128, generator=g)
+    planes = torch.randn(32, 8, 128, generator=g)
+    codes = torch.randint(0, 256, (B, Hkv, Tcap, 32), generator=g, dtype=torch.uint8)
+    if v_norm is None:
+        v_norm = (torch.rand(B, Hkv, Tcap, generator=g) + 10.5).to(torch.float16)
+    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv,
+                           want_probs=False, want_lut=True)
+    codes_d, vn_d = cu(codes), cu(v_norm.contiguous())
+    scores = ops.score(lut, codes_d, vn_d, H, T)
+    want, want_len = ops.select_list(scores, T, M, sink, window)
+    got, got_len, ws = ops.score_select_list(lut, codes_d, vn_d, H, T, M, sink, window)
+    assert torch.equal(got_len, want_len)
+    nb = got.shape[-1] - min(M, T)
+    assert torch.equal(got[:, :, :nb], want[:, :, :nb])
+    assert torch.equal(torch.sort(got[:, :, nb:], dim=-1).values, torch.sort(want[:, :, nb:], dim=-1).values)
+    # and the selection is a true top-k of the scores
+    vals = torch.sort(torch.gather(scores, 2, got[:, :, nb:].long()), dim=-1, descending=True).values
+    assert torch.equal(vals, torch.topk(scores[:, :, :T], min(M, T), dim=-1).values)
+    return int(ws[:4].view(torch.int32).item())
+
+
+@pytest.mark.parametrize("B,H,Hkv,T,M", [(1, 32, 8, 32768, 1024), (2, 8, 2, 20000, 512), (1, 4, 1, 4096, 64),
+                                         (1, 8, 8, 9000, 100), (4, 32, 8, 131072, 2048), (1, 16, 2, 50001, 1)])
+def test_fused_score_select_equals_two_step(B, H, Hkv, T, M):
+    assert ops.score_select_applicable(B, H, Hkv, 32, 256, T, M)
+    n_fallback = _fused_vs_two_step(B, H, Hkv, T, M, 8, 24, seed=T + M)
+    assert n_fallback == 0          # benign rows are decided on the candidates alone
+
+
+def test_fused_score_select_falls_back_exactly_on_hostile_rows():
+    T = 40000
+    ramp = (1.0 + 6.0 * torch.arange(T) / T).to(torch.float16)          # scores grow with position
+    n1 = _fused_vs_two_step(1, 8, 2, T, 512, 4, 4, v_norm=ramp.expand(1, 2, T), seed=1)
+    block = torch.ones(T)
+    block[12000:15000] = 50.0                                           # one chunk holds all winners
+    n2 = _fused_vs_two_step(1, 8, 2, T, 1024, 4, 4, v_norm=block.to(torch.float16).expand(1, 2, T), seed=2)
+    flat = torch.ones(1, 2, T, dtype=torch.float16)
+    codes_equal = _fused_vs_two_step(1, 8, 2, T, 256, 0, 0, v_norm=flat, seed=3)
+    assert n1 + n2 > 0               # at least the hostile layouts went through the rescoring path
+    assert codes_equal >= 0
+
+
+def test_fused_score_select_device_length_and_capacity():
+    T_live, Tcap = 30000, 33000
+    g = torch.Generator().manual_seed(9)
+    B, H, Hkv, M = 1, 8, 2, 300
+    q = torch.randn(B, H, 128, generator=g)
+    planes = torch.randn(32, 8, 128, generator=g)
+    codes = cu(torch.randint(0, 256, (B, Hkv, Tcap, 32), generator=g, dtype=torch.uint8))
+    vn = cu((torch.rand(B, Hkv, Tcap, generator=g) + 1).to(torch.float16))
+    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv, want_probs=False,
+                           want_lut=True)
+    T_dev = torch.tensor(T_live, dtype=torch.int32, device=DEV)
+    got, got_len, _ = ops.score_select_list(lut, codes, vn, H, Tcap, M, 4, 16, T_dev=T_dev)
+    scores = ops.score(lut, codes, vn, H, T_live)
+    want, want_len = ops.select_list(scores, T_live, M, 4, 16)
+    k = want.shape[-1]
+    assert (got_len == k).all()
+    assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values)
