@@ -81,6 +81,7 @@ inline ScorePlan make_score_plan(int n_groups, int64_t T, int64_t M) {
         int64_t chunks = n_groups >= n_sm ? 1 : n_sm / n_groups;
         const int64_t max_chunks = (T + 1023) / 1024;
         if (chunks > max_chunks) chunks = max_chunks;
+        if (chunks > 32) chunks = 32;   // the candidate select handles at most 32 chunks x 32 runs
         p.per_cta = (T + chunks - 1) / chunks;
         p.per_cta = (p.per_cta + 31) / 32 * 32;
         chunks = (T + p.per_cta - 1) / p.per_cta;
@@ -97,7 +98,8 @@ inline ScorePlan make_score_plan(int n_groups, int64_t T, int64_t M) {
 }
 // The filtering scorer pays off (and its buffers stay small) only for small k / T.
 inline bool fused_filter_applicable(const ScorePlan& p, int64_t T, int64_t M) {
-    return M > 0 && T >= 4096 && 12 * M <= T && 3 * M <= (SEL_CAP * 3) / 4 && p.chunks_max * SC_WARPS <= 1024;
+    return M > 0 && T >= 4096 && 12 * M <= T && 3 * M <= (SEL_CAP * 3) / 4 &&
+           p.chunks_max * SC_WARPS <= 1024 && p.cap_w <= 250;   // run lengths are kept in 8 bits
 }
 
 // Workspace of the fused scorer + select: [fallback counter | cnt | cut | cand | scratch scores]

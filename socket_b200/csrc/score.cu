@@ -219,21 +219,21 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         }
 
         // each warp owns a contiguous run of keys (a multiple of 32 long)
-        const int64_t per_warp = ((t1_raw - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32;
-        const int64_t ws = t0 + (int64_t)warp * per_warp;
-        const int64_t we = min(t1, ws + per_warp);
+        const int per_warp = (int)(((t1_raw - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32);
+        const int ws = (int)t0 + warp * per_warp;
+        const int we = min((int)t1, ws + per_warp);
         const uint4* cg = reinterpret_cast<const uint4*>(codes + (size_t)bk * Tcap * L);
         const __half* vg = v_norm + (size_t)bk * Tcap;
 
         uint4 cur[NV], nxt[NV];
-        int64_t t = ws + lane;
+        int t = ws + lane;
         if (t < we) {
 #pragma unroll
-            for (int i = 0; i < NV; ++i) cur[i] = __ldg(cg + t * NV + i);
+            for (int i = 0; i < NV; ++i) cur[i] = __ldg(cg + (size_t)t * NV + i);
         }
         if (t + 32 < we) {
 #pragma unroll
-            for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (t + 32) * NV + i);
+            for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (size_t)(t + 32) * NV + i);
         }
 
         const bool ok = mbar_wait(bar, phase);
@@ -243,14 +243,13 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             return;
         }
 
-        int cnt[HT];
+        uint32_t cnt4 = 0;            // four 8-bit run lengths, saturating at 255 (cap_w <= 250)
         float cutv[HT];
 #pragma unroll
-        for (int j = 0; j < HT; ++j) {
-            cnt[j] = 0;
-            cutv[j] = -INFINITY;
-        }
+        for (int j = 0; j < HT; ++j) cutv[j] = -INFINITY;
         bool first = true;
+        // this warp's run of head j starts at cand[(((row0 + j) * chunks_max + chunk) * 32 + warp) * cap_w];
+        // the address is formed only when a key is kept (rare), not carried in registers
 
         if (FILTER) {
             // ---- sample = first key of every lane: scores, min / max, histogram, cut
@@ -345,13 +344,14 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             for (int j = 0; j < HT; ++j) {
                 const bool hit = valid && sv[j] >= cutv[j];
                 const unsigned bal = __ballot_sync(FULL, hit);
+                const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
                 if (hit) {
-                    const int pos = cnt[j] + __popc(bal & ((1u << lane) - 1u));
+                    const int pos = have + __popc(bal & ((1u << lane) - 1u));
                     if (pos < fa.cap_w)
                         fa.cand[(((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w + pos] =
                             make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
                 }
-                cnt[j] += __popc(bal);
+                cnt4 += (uint32_t)min(__popc(bal), 255 - have) << (8 * j);
             }
             first = false;
         }
@@ -363,7 +363,7 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
             if (t + 32 < we) {
 #pragma unroll
-                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (t + 32) * NV + i);
+                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (size_t)(t + 32) * NV + i);
             }
         }
         for (; t - lane < we; t += 32) {
@@ -381,13 +381,14 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
                 for (int j = 0; j < HT; ++j) {
                     const bool hit = valid && sv[j] >= cutv[j];
                     const unsigned bal = __ballot_sync(FULL, hit);
+                    const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
                     if (hit) {
-                        const int pos = cnt[j] + __popc(bal & ((1u << lane) - 1u));
+                        const int pos = have + __popc(bal & ((1u << lane) - 1u));
                         if (pos < fa.cap_w)
-                            fa.cand[(((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w + pos] =
-                                make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
+                        fa.cand[(((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w + pos] =
+                            make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
                     }
-                    cnt[j] += __popc(bal);
+                    cnt4 += (uint32_t)min(__popc(bal), 255 - have) << (8 * j);
                 }
             } else if (valid) {
 #pragma unroll
@@ -401,13 +402,13 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
             if (t + 64 < we) {
 #pragma unroll
-                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (t + 64) * NV + i);
+                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (size_t)(t + 64) * NV + i);
             }
         }
         if (FILTER && lane == 0) {
 #pragma unroll
             for (int j = 0; j < HT; ++j)
-                fa.cnt[((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp] = cnt[j];
+                fa.cnt[((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp] = (int32_t)((cnt4 >> (8 * j)) & 0xffu);
         }
     }
 }

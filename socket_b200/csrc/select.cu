@@ -239,6 +239,73 @@ __device__ __forceinline__ uint32_t emit_from_candidates(SelShared& s, Scan& sca
     return kth;
 }
 
+// Same job as emit_from_candidates with fewer block-wide phases, for the common case of a few
+// thousand candidates: one 4096-bin histogram of (key - kmin) finds the bin holding the need-th
+// largest key; everything in higher bins is emitted by one ordered scan (consecutive candidates
+// per thread), and the handful of candidates inside that bin are ranked against each other
+// directly.  hist must be zero on entry.  Returns false (nothing written) if the threshold bin
+// holds more than 1024 candidates; the caller then uses the radix path.
+__device__ __forceinline__ bool emit_candidates_binned(SelShared& s, Scan& scan, int n, int need, int Me,
+                                                       uint32_t kmin, uint32_t kmax,
+                                                       int32_t* __restrict__ heavy, uint32_t& kth_out) {
+    const int tid = threadIdx.x;
+    const uint32_t range = kmax - kmin;
+    const int bits = range == 0 ? 0 : 32 - __clz(range);
+    const int shift = max(0, bits - 12);
+    for (int base = 0; base < n; base += SEL_THREADS) {
+        const int i = base + tid;
+        const uint32_t k = i < n ? s.cand_key[i] : kmin;
+        warp_hist_add(s.hist, (k - kmin) >> shift, i < n);
+    }
+    __syncthreads();
+    find_bin_desc(s, scan, need);
+    const int thr = s.thr_bin, above = s.thr_above, inbin = s.thr_inbin;
+    if (inbin > 1024) return false;
+    __syncthreads();                                   // hist is reused for the tie list below
+    uint32_t* tie_key = s.hist;                        // [1024]
+    int32_t* tie_idx = reinterpret_cast<int32_t*>(s.hist + 1024);
+    const int ept = (n + SEL_THREADS - 1) / SEL_THREADS;
+    const int i0 = tid * ept, i1 = min(n, i0 + ept);
+    int n_gt = 0, n_eq = 0;
+    for (int i = i0; i < i1; ++i) {
+        const int b = (int)((s.cand_key[i] - kmin) >> shift);
+        n_gt += b > thr;
+        n_eq += b == thr;
+    }
+    int total;
+    const int off = scan.excl(n_gt | (n_eq << 16), total, s);
+    int g = off & 0xffff, e = off >> 16;
+    for (int i = i0; i < i1; ++i) {
+        const uint32_t k = s.cand_key[i];
+        const int b = (int)((k - kmin) >> shift);
+        if (b > thr) {
+            if (g < Me) heavy[g] = s.cand_idx[i];
+            ++g;
+        } else if (b == thr) {
+            if (e < 1024) {
+                tie_key[e] = k;
+                tie_idx[e] = s.cand_idx[i];
+            }
+            ++e;
+        }
+    }
+    __syncthreads();
+    const int want = need - above;                     // 1 <= want <= inbin
+    if (tid < inbin) {
+        const uint32_t k = tie_key[tid];
+        int rank = 0;
+        for (int j = 0; j < inbin; ++j) {
+            const uint32_t kj = tie_key[j];
+            rank += (kj > k) || (kj == k && j < tid);
+        }
+        if (rank < want && above + rank < Me) heavy[above + rank] = tie_idx[tid];
+        if (rank == want - 1) s.red_lo[0] = k;
+    }
+    __syncthreads();
+    kth_out = s.red_lo[0];
+    return true;
+}
+
 // Top-`Me` (0 < Me) of one row of T scores -> heavy[0..Me).  Exact; see the file header.
 __device__ __forceinline__ void select_row(SelShared& s, Scan& scan, const float* __restrict__ sc, int T,
                                            int Me, int32_t* __restrict__ heavy) {
@@ -646,36 +713,73 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
 
     bool exact = false;
     if (Me > 0 && Me < T) {
-        // ---- run lengths -> offsets (one run per thread), largest cut
+        // ---- run lengths -> offsets (one run per thread), largest cut, overflow flag
+        if (tid == 0) {
+            s.thr_bin = 0;                             // "some run overflowed"
+            s.red_hi[0] = 0u;                          // key of the largest cut
+        }
+        for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
+        __syncthreads();
         int c = 0;
         if (tid < n_runs) c = cnt[tid];
-        const bool over = c > a.cap_w;
-        float cutv = -INFINITY;
-        if (tid < n_runs / SC_WARPS) cutv = a.cut[row * a.chunks_max + tid];
+        if (c > a.cap_w) s.thr_bin = 1;
+        if (tid < n_runs / SC_WARPS) atomicMax(&s.red_hi[0], order_key(a.cut[row * a.chunks_max + tid]));
         int total;
-        const int off = scan.excl(c, total, s);
-        const int any_over = __syncthreads_or(over);
-        uint32_t clo = 0xffffffffu, chi = order_key(cutv);
-        block_minmax(s, clo, chi);                     // chi = key of the largest cut
+        const int off = scan.excl(c, total, s);        // two barriers: the flags above are visible after it
+        const bool any_over = s.thr_bin != 0;
+        const uint32_t chi = s.red_hi[0];
         if (!any_over && total >= Me && total <= SEL_CAP) {
-            // ---- gather: stash (offset, count) per run, then one warp per run, coalesced
-            if (tid < n_runs) {
-                s.hist[2 * tid] = (uint32_t)off;
-                s.hist[2 * tid + 1] = (uint32_t)c;
-            }
-            __syncthreads();
-            const uint2* cand = a.cand + row * a.chunks_max * SC_WARPS * a.cap_w;
-            for (int r = warp; r < n_runs; r += SEL_WARPS) {
-                const int o = (int)s.hist[2 * r], n = (int)s.hist[2 * r + 1];
-                const uint2* src = cand + (size_t)r * a.cap_w;
-                for (int i = lane; i < n; i += 32) {
-                    const uint2 e = __ldg(src + i);
-                    s.cand_key[o + i] = order_key(__uint_as_float(e.x));
-                    s.cand_idx[o + i] = (int32_t)e.y;
+            // ---- gather: run offsets to shared memory, then one candidate per thread and step
+            // (its run found by binary search), all loads independent
+            int32_t* run_off = s.cand_idx + SEL_CAP - 1024;       // tail of cand_idx, free until total > 15360
+            const bool tail_free = total <= SEL_CAP - 1024;
+            uint32_t kmin = 0xffffffffu, kmax = 0u;
+            if (tail_free) {
+                if (tid < n_runs) run_off[tid] = off;
+                __syncthreads();
+                const uint2* cand = a.cand + row * a.chunks_max * SC_WARPS * a.cap_w;
+                for (int i = tid; i < total; i += SEL_THREADS) {
+                    int lo = 0, hi = n_runs - 1;                  // last run with run_off <= i
+                    while (lo < hi) {
+                        const int mid = (lo + hi + 1) >> 1;
+                        if (run_off[mid] <= i) lo = mid; else hi = mid - 1;
+                    }
+                    const uint2 e = __ldg(cand + (size_t)lo * a.cap_w + (i - run_off[lo]));
+                    const uint32_t k = order_key(__uint_as_float(e.x));
+                    s.cand_key[i] = k;
+                    s.cand_idx[i] = (int32_t)e.y;
+                    kmin = min(kmin, k);
+                    kmax = max(kmax, k);
                 }
+            } else {
+                // nearly full buffer: one warp per run
+                if (tid < n_runs) {
+                    s.hist[2 * tid] = (uint32_t)off;
+                    s.hist[2 * tid + 1] = (uint32_t)c;
+                }
+                __syncthreads();
+                const uint2* cand = a.cand + row * a.chunks_max * SC_WARPS * a.cap_w;
+                for (int r = warp; r < n_runs; r += SEL_WARPS) {
+                    const int o = (int)s.hist[2 * r], n = (int)s.hist[2 * r + 1];
+                    const uint2* src = cand + (size_t)r * a.cap_w;
+                    for (int i = lane; i < n; i += 32) {
+                        const uint2 e = __ldg(src + i);
+                        const uint32_t k = order_key(__uint_as_float(e.x));
+                        s.cand_key[o + i] = k;
+                        s.cand_idx[o + i] = (int32_t)e.y;
+                        kmin = min(kmin, k);
+                        kmax = max(kmax, k);
+                    }
+                }
+                __syncthreads();
+                for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
             }
-            __syncthreads();
-            const uint32_t kth = emit_from_candidates(s, scan, total, Me, 0, Me, heavy);
+            block_minmax(s, kmin, kmax);               // also the barrier after the gather
+            uint32_t kth = 0;
+            if (!emit_candidates_binned(s, scan, total, Me, Me, kmin, kmax, heavy, kth)) {
+                __syncthreads();
+                kth = emit_from_candidates(s, scan, total, Me, 0, Me, heavy);
+            }
             exact = kth >= chi;                        // uniform: kth and chi are block-wide values
         }
         if (!exact) {
