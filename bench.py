@@ -323,45 +323,70 @@ def main():
     a_codes = B * Hkv * T_now * cfg.L
     a_kv = B * H * cfg.ktot * 2 * D * cfg.kv_bytes()
 
-    def time_kernel(fn, n=50):
-        """One kernel per CUDA-graph launch, so the host-side wrapper cost stays outside the
-        bracket; same flush discipline as the whole-step loop."""
-        with torch.cuda.stream(side):
-            fn()
-            side.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
+    REP = 8
+
+    def time_kernel(fn, n=20):
+        """Per-kernel time without launch overhead in the bracket: a CUDA graph holding REP x
+        (L2 flush, kernel) is timed against a graph holding REP x (L2 flush) and the difference
+        is divided by REP."""
+        def build(with_fn):
+            with torch.cuda.stream(side):
                 fn()
-        torch.cuda.synchronize()
-        ts = []
-        for i in range(n + 3):
-            if not args.no_flush:
-                flush.fill_(i & 0xff)
-            e0 = torch.cuda.Event(enable_timing=True)
-            e1 = torch.cuda.Event(enable_timing=True)
-            e0.record()
-            g.replay()
-            e1.record()
-            ts.append((e0, e1))
-        torch.cuda.synchronize()
-        v = sorted(a.elapsed_time(b) for a, b in ts[3:])
-        return sum(v) / len(v) * 1e3    # us
+                side.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for r in range(REP):
+                        if not args.no_flush:
+                            flush.fill_(r)
+                        if with_fn:
+                            fn()
+            torch.cuda.synchronize()
+            return g
+
+        def run(g):
+            ts = []
+            for i in range(n + 2):
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                ts.append((e0, e1))
+            torch.cuda.synchronize()
+            v = sorted(a.elapsed_time(b) for a, b in ts[2:])
+            return v[len(v) // 2] * 1e3
+        return max(0.0, (run(build(True)) - run(build(False))) / REP)    # us
 
     us = {}
     if args.skip_stages:
         return finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, None, {}, None,
                       sampler, step, peak, peak_src)
+    from socket_b200._lib import lib, ptr, stream_ptr
     probs, lut = ops.soft_hash(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv, want_probs=False,
                                want_lut=True)
-    scores = ops.score(lut, cache.k_hard, cache.v_norm, H, T_now)
-    lst, ln = ops.select_list(scores, T_now, cfg.topk, cfg.sink, cfg.window)
+    fused = ops.score_select_applicable(B, H, Hkv, cfg.L, cfg.R, T_now, cfg.topk)
     us["kv_append"] = time_kernel(lambda: cache.append(pos_s, k_s, v_s, attn.planes))
     us["soft_hash"] = time_kernel(lambda: ops.soft_hash(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv,
                                                         want_probs=False, want_lut=True))
-    us["score"] = time_kernel(lambda: ops.score(lut, cache.k_hard, cache.v_norm, H, T_now, out=scores))
-    us["select_list"] = time_kernel(lambda: ops.select_list(scores, T_now, cfg.topk, cfg.sink, cfg.window))
+    if fused:
+        lst, ln, fws = ops.score_select_list(lut, cache.k_hard, cache.v_norm, H, T_now, cfg.topk, cfg.sink,
+                                             cfg.window)
+        ktot = lst.shape[-1]
+        common = (ptr(lut), ptr(cache.k_hard), ptr(cache.v_norm), B, H, Hkv, cfg.L, cfg.R, T_now, None, Tcap,
+                  cfg.topk)
+        us["score_filter"] = time_kernel(lambda: lib().sk_score_filter(
+            *common, ptr(fws), fws.numel(), None, stream_ptr(dev)))
+        us["select_candidates"] = time_kernel(lambda: lib().sk_select_candidates(
+            *common, cfg.sink, cfg.window, ptr(lst), ktot, ptr(ln), ptr(fws), fws.numel(), None, stream_ptr(dev)))
+        score_name, select_name = "score_filter", "select_candidates"
+    else:
+        scores = ops.score(lut, cache.k_hard, cache.v_norm, H, T_now)
+        lst, ln = ops.select_list(scores, T_now, cfg.topk, cfg.sink, cfg.window)
+        us["score"] = time_kernel(lambda: ops.score(lut, cache.k_hard, cache.v_norm, H, T_now, out=scores))
+        us["select_list"] = time_kernel(lambda: ops.select_list(scores, T_now, cfg.topk, cfg.sink, cfg.window))
+        score_name, select_name = "score", "select_list"
     us["sparse_decode"] = time_kernel(lambda: ops.sparse_decode(q_s, cache.k_cache, cache.v_cache, lst, ln, T=T_now))
-    alg = {"kv_append": 0, "soft_hash": 0, "score": a_codes, "select_list": 0, "sparse_decode": a_kv}
+    alg = {"kv_append": 0, "soft_hash": 0, score_name: a_codes, select_name: 0, "sparse_decode": a_kv}
     for name, t_us in us.items():
         gbs = alg[name] / (t_us * 1e-6) / 1e9 if alg[name] else None
         stages[name] = {"us": round(t_us, 2), "algorithmic_bytes": alg[name],
@@ -371,7 +396,7 @@ def main():
     stages["whole_step"] = {"us": round(ms_per_step * 1e3, 2), "algorithmic_bytes": A,
                             "achieved_gbs": round(step_gbs, 1), "frac_of_hbm_peak": round(step_gbs / peak, 4),
                             "frac_of_8tbs": round(step_gbs / 8000.0, 4)}
-    dominant = max(("score", "sparse_decode", "select_list"), key=lambda n: us[n])
+    dominant = max((score_name, "sparse_decode", select_name), key=lambda n: us[n])
     dom_alg = alg[dominant] if alg[dominant] else A
     dom_gbs = dom_alg / (us[dominant] * 1e-6) / 1e9
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": round(dom_gbs, 1), "peak": peak,

@@ -165,6 +165,15 @@ SK_API int sk_select_list(const float* scores, int64_t score_row_stride, const u
  * ---------------------------------------------------------------------------------- */
 SK_API int sk_score_select_applicable(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M);
 SK_API size_t sk_score_select_workspace_bytes(int B, int H, int Hkv, int L, int64_t T, int64_t M);
+/* The two halves of sk_score_select_list, for callers that want to time or overlap them: the
+ * filtering scorer fills the workspace, the candidate select consumes it.  Same arguments. */
+SK_API int sk_score_filter(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H, int Hkv,
+                    int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M, void* workspace,
+                    size_t workspace_bytes, int32_t* status, void* stream);
+SK_API int sk_select_candidates(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H, int Hkv,
+                         int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M, int sink,
+                         int window, int32_t* list, int64_t list_row_stride, int32_t* list_len,
+                         void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 SK_API int sk_score_select_list(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
                          int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
                          int sink, int window, int32_t* list, int64_t list_row_stride, int32_t* list_len,

@@ -60,6 +60,9 @@ SIGNATURES = {
     "sk_select_list": (_i, [_p, _i64, _p, _i64, _i64, _p, _i64, _i, _i, _i, _p, _i64, _p, _p, _p]),
     "sk_score_select_applicable": (_i, [_i, _i, _i, _i, _i, _i64, _i64]),
     "sk_score_select_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i64]),
+    "sk_score_filter": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i64, _p, _i64, _i64, _p, _sz, _p, _p]),
+    "sk_select_candidates": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i64, _p, _i64, _i64, _i, _i, _p, _i64, _p,
+                                  _p, _sz, _p, _p]),
     "sk_score_select_list": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i64, _p, _i64, _i64, _i, _i, _p, _i64, _p,
                                   _p, _sz, _p, _p]),
     "sk_sparse_decode_workspace_bytes": (_sz, [_i, _i, _i, _i64]),

@@ -215,6 +215,38 @@ int sk_score_select_list(const float* lut, const uint8_t* codes, const uint16_t*
                                     list, list_row_stride, list_len, workspace, status, st);
 }
 
+int sk_score_filter(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H, int Hkv,
+                    int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M, void* workspace,
+                    size_t workspace_bytes, int32_t* status, void* stream) {
+    SK_REQUIRE(lut && codes && v_norm && workspace, "sk_score_filter: null pointer");
+    if (!sk_score_select_applicable(B, H, Hkv, L, R, T, M))
+        return fail(SK_ERR_UNSUPPORTED, "sk_score_filter: shape outside the fused path");
+    SK_REQUIRE(T <= Tcap, "sk_score_filter: T exceeds the cache capacity");
+    SK_ALIGNED(lut, 16, "sk_score_filter: lut");
+    SK_ALIGNED(codes, 16, "sk_score_filter: codes");
+    SK_ALIGNED(workspace, 256, "sk_score_filter: workspace");
+    if (workspace_bytes < score_select_workspace_bytes(B, H, Hkv, L, T, M))
+        return fail(SK_ERR_WORKSPACE, "sk_score_filter: workspace too small");
+    return launch_score_filter(lut, codes, v_norm, B, H, Hkv, L, R, T, T_dev, Tcap, M, workspace, status,
+                               (cudaStream_t)stream);
+}
+
+int sk_select_candidates(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H, int Hkv,
+                         int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M, int sink,
+                         int window, int32_t* list, int64_t list_row_stride, int32_t* list_len,
+                         void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+    SK_REQUIRE(lut && codes && v_norm && workspace && list && list_len, "sk_select_candidates: null pointer");
+    if (!sk_score_select_applicable(B, H, Hkv, L, R, T, M))
+        return fail(SK_ERR_UNSUPPORTED, "sk_select_candidates: shape outside the fused path");
+    SK_REQUIRE(list_row_stride >= list_len_host(T, sink, window, M),
+               "sk_select_candidates: list_row_stride smaller than the list length");
+    SK_ALIGNED(workspace, 256, "sk_select_candidates: workspace");
+    if (workspace_bytes < score_select_workspace_bytes(B, H, Hkv, L, T, M))
+        return fail(SK_ERR_WORKSPACE, "sk_select_candidates: workspace too small");
+    return launch_select_candidates(lut, codes, v_norm, B, H, Hkv, L, R, T, T_dev, Tcap, M, sink, window, 0,
+                                    list, list_row_stride, list_len, workspace, status, (cudaStream_t)stream);
+}
+
 size_t sk_sparse_decode_workspace_bytes(int B, int H, int D, int64_t max_list_len) {
     return sparse_decode_workspace_bytes(B, H, D, max_list_len);
 }
