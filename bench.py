@@ -391,6 +391,31 @@ def main():
         gbs = alg[name] / (t_us * 1e-6) / 1e9 if alg[name] else None
         stages[name] = {"us": round(t_us, 2), "algorithmic_bytes": alg[name],
                         "achieved_gbs": None if gbs is None else round(gbs, 1)}
+    # prefill hashing of the whole context on the tensor cores (not part of the decode step)
+    if dt == torch.bfloat16 and D == 128 and cfg.L == 32 and cfg.P == 8:
+        n_rows = B * Hkv * T0
+        keys2d = cache.k_cache[:, :, :T0].reshape(-1, D)
+        for _ in range(2):
+            ops.hash_keys_tc(keys2d, attn.planes)
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            ops.hash_keys_tc(keys2d, attn.planes)
+        e1.record()
+        torch.cuda.synchronize()
+        t_us = e0.elapsed_time(e1) / 5 * 1e3
+        flops = 2.0 * n_rows * D * cfg.L * cfg.P
+        tf_peak = None
+        try:
+            tf_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        except Exception:
+            pass
+        stages["prefill_hash_tc"] = {
+            "us": round(t_us, 1), "rows": n_rows, "tflops": round(flops / t_us / 1e6, 1),
+            "frac_of_bf16_peak": None if tf_peak is None else round(flops / t_us / 1e6 / tf_peak, 4),
+            "gbs": round(n_rows * (D * 2 + cfg.L) / t_us / 1e3, 1),
+            "note": "sk_hash_keys_tc incl. its plane-norm, fix-up and gate launches; not in the step"}
     A = a_codes + a_kv
     step_gbs = A / (ms_per_step * 1e-3) / 1e9
     stages["whole_step"] = {"us": round(ms_per_step * 1e3, 2), "algorithmic_bytes": A,

@@ -85,6 +85,27 @@ SK_API int sk_kv_append(const void* k_new, const void* v_new, int kv_dtype, cons
                  int S, int Hkv, int D, int64_t Tcap, int L, int P, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * The same hashing for bulk (prefill-sized) inputs on the tensor cores: the [N,128]x[128,256]
+ * projection runs as tcgen05 MMAs fed by TMA; projections too close to zero for the fp32
+ * accumulator to decide are decided again exactly, so the codes equal sk_hash_keys' bit for
+ * bit.  bf16 keys and planes, D = 128, L = 32, P = 8; codes are uint8.
+ *   dst_row    NULL, or [N] int64: row n's codes go to codes + dst_row[n] * code_row_stride
+ *              (negative = skip the row); lets a [B,S,Hkv] batch land in a [B,Hkv,Tcap] cache
+ *   workspace  sk_hash_keys_tc_workspace_bytes(N) bytes, 256-byte aligned
+ * sk_kv_append_tc = sk_kv_append for many tokens at once (prefill) on that path.
+ * Replaces the same reference code as sk_hash_keys / sk_kv_append.
+ * ---------------------------------------------------------------------------------- */
+SK_API size_t sk_hash_keys_tc_workspace_bytes(int64_t N);
+SK_API int sk_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* planes, int64_t N, int D, int L, int P,
+                    uint8_t* codes, int64_t code_row_stride, const int64_t* dst_row, void* workspace,
+                    size_t workspace_bytes, int32_t* status, void* stream);
+SK_API size_t sk_kv_append_tc_workspace_bytes(int B, int S, int Hkv);
+SK_API int sk_kv_append_tc(const void* k_new, const void* v_new, int kv_dtype, const int64_t* input_pos,
+                    const void* planes, int plane_dtype, void* k_cache, void* v_cache, uint8_t* codes,
+                    uint16_t* v_norm, int32_t* prefill_len, int32_t* status, int B, int S, int Hkv, int D,
+                    int64_t Tcap, int L, int P, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Query soft hash.  Replaces Attention.soft_hash (GPT-FAST/model.py:392-401):
  * q_probs[b,h,l,:] = softmax_r( (tanh(<q, planes[l,p]>) / sqrt(D)) . protos_T[p,r] / temperature )
  * (temperature 1.0 = the GPT-FAST formula; the HuggingFace variant divides by 0.3,

@@ -51,6 +51,11 @@ SIGNATURES = {
     "sk_last_error": (C.c_char_p, []),
     "sk_hash_keys": (_i, [_p, _i, _i64, _p, _i, _i64, _i, _i, _i, _p, _i, _i64, _p]),
     "sk_kv_append": (_i, [_p, _p, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i64, _i, _i, _p]),
+    "sk_hash_keys_tc_workspace_bytes": (_sz, [_i64]),
+    "sk_hash_keys_tc": (_i, [_p, _i64, _p, _i64, _i, _i, _i, _p, _i64, _p, _p, _sz, _p, _p]),
+    "sk_kv_append_tc_workspace_bytes": (_sz, [_i, _i, _i]),
+    "sk_kv_append_tc": (_i, [_p, _p, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i64, _i, _i,
+                             _p, _sz, _p]),
     "sk_lut_head_tile": (_i, [_i]),
     "sk_soft_hash": (_i, [_p, _i, _p, _i, _p, _f, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p]),
     "sk_lut_from_probs": (_i, [_p, _i, _i, _i, _i, _i, _i, _p, _p]),

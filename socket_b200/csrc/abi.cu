@@ -102,6 +102,61 @@ int sk_kv_append(const void* k_new, const void* v_new, int kv_dtype, const int64
                             (cudaStream_t)stream);
 }
 
+size_t sk_hash_keys_tc_workspace_bytes(int64_t N) { return hash_keys_tc_workspace_bytes(N < 0 ? 0 : N); }
+
+int sk_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* planes, int64_t N, int D, int L, int P,
+                    uint8_t* codes, int64_t code_row_stride, const int64_t* dst_row, void* workspace,
+                    size_t workspace_bytes, int32_t* status, void* stream) {
+    SK_REQUIRE(N >= 0, "sk_hash_keys_tc: N must be non-negative");
+    if (N == 0) return SK_OK;
+    SK_REQUIRE(keys && planes && codes && workspace, "sk_hash_keys_tc: null pointer");
+    if (D != 128 || L * P != 256 || P != 8)
+        return fail(SK_ERR_UNSUPPORTED, "sk_hash_keys_tc: needs head_dim 128, P = 8 and L = 32 (got D=%d L=%d P=%d)", D, L, P);
+    SK_REQUIRE(key_row_stride >= D && code_row_stride >= L, "sk_hash_keys_tc: row stride smaller than row");
+    SK_ALIGNED(keys, 16, "sk_hash_keys_tc: keys");
+    SK_ALIGNED(planes, 16, "sk_hash_keys_tc: planes");
+    SK_ALIGNED(codes, 16, "sk_hash_keys_tc: codes");
+    SK_ALIGNED(workspace, 256, "sk_hash_keys_tc: workspace");
+    if (key_row_stride % 8 || code_row_stride % 16)
+        return fail(SK_ERR_MISALIGNED, "sk_hash_keys_tc: key rows and code rows must start on 16-byte boundaries");
+    return launch_hash_keys_tc(keys, key_row_stride, planes, N, codes, code_row_stride, dst_row, workspace,
+                               workspace_bytes, status, (cudaStream_t)stream);
+}
+
+size_t sk_kv_append_tc_workspace_bytes(int B, int S, int Hkv) {
+    const int64_t N = (int64_t)(B > 0 ? B : 0) * (S > 0 ? S : 0) * (Hkv > 0 ? Hkv : 0);
+    return up256((size_t)N * sizeof(int64_t)) + hash_keys_tc_workspace_bytes(N);
+}
+
+int sk_kv_append_tc(const void* k_new, const void* v_new, int kv_dtype, const int64_t* input_pos,
+                    const void* planes, int plane_dtype, void* k_cache, void* v_cache, uint8_t* codes,
+                    uint16_t* v_norm, int32_t* prefill_len, int32_t* status, int B, int S, int Hkv, int D,
+                    int64_t Tcap, int L, int P, void* workspace, size_t workspace_bytes, void* stream) {
+    SK_REQUIRE(B >= 0 && S >= 0 && Hkv > 0 && Tcap > 0, "sk_kv_append_tc: sizes must be positive");
+    if (B == 0 || S == 0) return SK_OK;
+    SK_REQUIRE(k_new && v_new && input_pos && planes && k_cache && v_cache && codes && v_norm && prefill_len && workspace,
+               "sk_kv_append_tc: null pointer");
+    if (kv_dtype != SK_BF16 || plane_dtype != SK_BF16 || D != 128 || L != 32 || P != 8)
+        return fail(SK_ERR_UNSUPPORTED, "sk_kv_append_tc: bf16 keys and planes, head_dim 128, L = 32, P = 8 only; "
+                                        "use sk_kv_append otherwise");
+    SK_ALIGNED(workspace, 256, "sk_kv_append_tc: workspace");
+    SK_ALIGNED(k_new, 16, "sk_kv_append_tc: k_new");
+    SK_ALIGNED(codes, 16, "sk_kv_append_tc: codes");
+    if (workspace_bytes < sk_kv_append_tc_workspace_bytes(B, S, Hkv))
+        return fail(SK_ERR_WORKSPACE, "sk_kv_append_tc: workspace too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t N = (int64_t)B * S * Hkv;
+    char* ws = static_cast<char*>(workspace);
+    int64_t* dst_row = reinterpret_cast<int64_t*>(ws);
+    const size_t off = up256((size_t)N * sizeof(int64_t));
+    int rc = launch_cache_rows(input_pos, B, S, Hkv, Tcap, dst_row, status, st);
+    if (rc != SK_OK) return rc;
+    rc = launch_kv_copy(k_new, v_new, kv_dtype, input_pos, k_cache, v_cache, v_norm, prefill_len, nullptr, B, S,
+                        Hkv, D, Tcap, st);
+    if (rc != SK_OK) return rc;
+    return launch_hash_keys_tc(k_new, D, planes, N, codes, L, dst_row, ws + off, workspace_bytes - off, status, st);
+}
+
 int sk_lut_head_tile(int rep) { return rep > 0 ? lut_head_tile(rep) : 0; }
 
 int sk_soft_hash(const void* q, int q_dtype, const void* planes, int plane_dtype,

@@ -163,6 +163,17 @@ int launch_select_candidates(const float* lut, const uint8_t* codes, const uint1
                              int sink, int window, int sorted, int32_t* list, int64_t list_row_stride,
                              int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st);
 
+// Tensor-core bulk hashing (bf16, head_dim 128, L*P = 256)
+size_t hash_keys_tc_workspace_bytes(int64_t N);
+int launch_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* planes, int64_t N, uint8_t* codes,
+                        int64_t code_row_stride, const int64_t* dst_row, void* workspace, size_t workspace_bytes,
+                        int32_t* status, cudaStream_t st);
+int launch_cache_rows(const int64_t* input_pos, int B, int S, int Hkv, int64_t Tcap, int64_t* dst_row,
+                      int32_t* status, cudaStream_t st);
+int launch_kv_copy(const void* k_new, const void* v_new, int kv_dtype, const int64_t* input_pos, void* k_cache,
+                   void* v_cache, uint16_t* v_norm, int32_t* prefill_len, int32_t* status, int B, int S,
+                   int Hkv, int D, int64_t Tcap, cudaStream_t st);
+
 int lut_head_tile(int rep);
 int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, int dtype,
                            const int64_t* input_pos, const void* planes, int plane_dtype,

@@ -113,4 +113,21 @@ int launch_kv_append(const void* k_new, const void* v_new, int kv_dtype, const i
                                                       D, Tcap, L, P, st)));
 }
 
+// K/V copy, ||v|| and prefill_len of S new tokens without hashing (the codes are written by the
+// tensor-core hashing path): the append kernel with zero tables.
+int launch_kv_copy(const void* k_new, const void* v_new, int kv_dtype, const int64_t* input_pos, void* k_cache,
+                   void* v_cache, uint16_t* v_norm, int32_t* prefill_len, int32_t* status, int B, int S,
+                   int Hkv, int D, int64_t Tcap, cudaStream_t st) {
+    const int64_t N = (int64_t)B * S * Hkv;
+    if (N == 0) return SK_OK;
+    if (kv_dtype != SK_BF16 || D != 128) return fail(SK_ERR_UNSUPPORTED, "kv copy: bf16 and head_dim 128 only");
+    const int64_t gx = (N + HASH_ROWS - 1) / HASH_ROWS;
+    if (gx > 0x7fffffff) return fail(SK_ERR_UNSUPPORTED, "kv copy: too many rows");
+    kv_append_kernel<__nv_bfloat16, __nv_bfloat16, 4><<<dim3((unsigned)gx, 1), HASH_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, input_pos, (const __nv_bfloat16*)k_new,
+        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nullptr, (__half*)v_norm, prefill_len, status, B, S,
+        Hkv, Tcap, 0, 8);
+    return check_launch("kv_append_kernel (copy only)");
+}
+
 }  // namespace sk

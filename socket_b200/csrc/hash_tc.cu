@@ -1,0 +1,399 @@
+// Bulk key hashing on the 5th-generation tensor cores (prefill: thousands of rows).
+//
+// codes = sign( K[N,128] . planes^T[128, L*P = 256] ) packed 8 planes -> one byte per table.
+// One CTA per 128-row tile of K: TMA (cp.async.bulk.tensor, 128-byte swizzle) brings the K tile
+// and the 256 plane rows into shared memory, one elected thread issues eight
+// tcgen05.mma.kind::f16 (M=128, N=256, K=16) with the fp32 accumulator in tensor memory, a
+// tcgen05.commit signals an mbarrier, and the four warps read their 32 accumulator lanes back
+// with tcgen05.ld (one row per thread), take the signs and write 32 code bytes per row.
+//
+// Exactness.  bf16 x bf16 products are exact in fp32, only the accumulation rounds, so a sign
+// can be wrong only when |acc| is tiny compared with |k|.|p|.  Every projection with
+// |acc| <= 2^-16 |k| |p| (a bound far above the accumulation error of 128 terms) is put on a
+// list and decided again by a second kernel from the exact fp64 dot product, which patches the
+// bit; ~1e-4 of the projections take that path.  Rows of zeros hash to all-ones bytes directly.
+// If the list overflows (adversarial inputs), a third kernel rehashes everything exactly.
+#include <cuda.h>
+
+#include "hash_body.cuh"
+
+namespace sk {
+namespace {
+
+constexpr int TC_ROWS = 128;          // rows of K per CTA (MMA M)
+constexpr int TC_N = 256;             // L * P (MMA N)
+constexpr int TC_D = 128;             // head dim (MMA K total)
+constexpr int TC_KHALF = 64;          // bf16 elements per 128-byte swizzle row
+constexpr uint32_t TC_A_HALF_BYTES = TC_ROWS * 128;   // 16 KiB
+constexpr uint32_t TC_B_HALF_BYTES = TC_N * 128;      // 32 KiB
+constexpr uint32_t TC_SMEM_TILES = 2 * TC_A_HALF_BYTES + 2 * TC_B_HALF_BYTES;   // 96 KiB
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
+constexpr float TC_BAND = 1.52587890625e-05f;         // 2^-16
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_addr(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar))
+        : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows x 128 B
+    d |= (uint64_t)1 << 46;                          // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+
+// kind::f16, A = B = bf16 (K-major), D = fp32, M = 128, N = 256
+constexpr uint32_t TC_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((TC_N >> 3) << 17) | ((TC_ROWS >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(TC_IDESC), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct TcShared {
+    uint64_t tma_bar, mma_bar;
+    uint32_t tmem_base;
+    float plane_norm[TC_N];
+};
+
+// ||plane_n|| for the 256 planes, one warp per plane (grid-stride).
+__global__ void __launch_bounds__(256)
+plane_norm_kernel(const __nv_bfloat16* __restrict__ planes, float* __restrict__ out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int n = warp; n < TC_N; n += 8) {
+        float s = 0.f;
+        for (int d = lane; d < TC_D; d += 32) {
+            const float x = __bfloat162float(planes[(size_t)n * TC_D + d]);
+            s = fmaf(x, x, s);
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(FULL, s, o);
+        if (lane == 0) out[n] = sqrtf(s) * 1.001f;
+    }
+}
+
+__global__ void __launch_bounds__(TC_ROWS)
+hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_p,
+               const __nv_bfloat16* __restrict__ keys, int64_t key_row_stride,
+               const float* __restrict__ plane_norm, int64_t N, uint8_t* __restrict__ codes,
+               int64_t code_row_stride, const int64_t* __restrict__ dst_row, uint32_t* fix_count,
+               uint32_t* __restrict__ fix_list, uint32_t fix_cap, int32_t* status) {
+    extern __shared__ char tc_raw[];
+    __shared__ TcShared ts;
+    char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
+    char* a_half[2] = {tiles, tiles + TC_A_HALF_BYTES};
+    char* b_half[2] = {tiles + 2 * TC_A_HALF_BYTES, tiles + 2 * TC_A_HALF_BYTES + TC_B_HALF_BYTES};
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t row0 = (int64_t)blockIdx.x * TC_ROWS;
+
+    for (int i = tid; i < TC_N; i += TC_ROWS) ts.plane_norm[i] = plane_norm[i];
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&ts.tma_bar)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&ts.mma_bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_addr(&ts.tmem_base)),
+                     "r"((uint32_t)TC_N)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = ts.tmem_base;
+
+    if (tid == 0) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(&ts.tma_bar)),
+                     "r"(TC_SMEM_TILES)
+                     : "memory");
+        tma_load_2d(a_half[0], &map_k, 0, (int)row0, &ts.tma_bar);
+        tma_load_2d(a_half[1], &map_k, TC_KHALF, (int)row0, &ts.tma_bar);
+        tma_load_2d(b_half[0], &map_p, 0, 0, &ts.tma_bar);
+        tma_load_2d(b_half[1], &map_p, TC_KHALF, 0, &ts.tma_bar);
+        if (mbar_wait_bounded(&ts.tma_bar, 0)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int k = 0; k < TC_D / 16; ++k) {
+                const int half = k >> 2, kb = k & 3;       // 16 bf16 = 32 bytes along the swizzled row
+                const uint64_t da = umma_desc_sw128(smem_addr(a_half[half]) + kb * 32);
+                const uint64_t db = umma_desc_sw128(smem_addr(b_half[half]) + kb * 32);
+                umma_bf16(tmem, da, db, k > 0 ? 1u : 0u);
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             smem_addr(&ts.mma_bar))
+                         : "memory");
+        }
+    }
+    const bool ok = mbar_wait_bounded(&ts.mma_bar, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (__syncthreads_and(ok)) {
+        // ---- epilogue: one accumulator row per thread
+        const int64_t row = row0 + tid;
+        const bool valid = row < N;
+        float knorm = 0.f;
+        if (valid) {
+            const uint4* kp = reinterpret_cast<const uint4*>(keys + row * key_row_stride);
+            float ss = 0.f;
+#pragma unroll 4
+            for (int i = 0; i < TC_D / 8; ++i) {
+                const uint4 w = __ldg(kp + i);
+                const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float a = __uint_as_float(u[j] << 16), b = __uint_as_float(u[j] & 0xffff0000u);
+                    ss = fmaf(a, a, fmaf(b, b, ss));
+                }
+            }
+            knorm = sqrtf(ss) * 1.001f;
+        }
+        const float thr = TC_BAND * knorm;
+        uint32_t words[TC_N / 32];
+#pragma unroll
+        for (int c = 0; c < TC_N / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c * 32, r);
+            uint32_t word = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float a = __uint_as_float(r[i]);
+                const int l4 = i >> 3, p = i & 7;
+                if (a >= 0.f) word |= 1u << (8 * l4 + 7 - p);
+                if (valid && fabsf(a) <= thr * ts.plane_norm[c * 32 + i] && knorm > 0.f) {
+                    const uint32_t slot = atomicAdd(fix_count, 1u);
+                    if (slot < fix_cap) fix_list[slot] = ((uint32_t)row << 8) | (uint32_t)(c * 32 + i);
+                }
+            }
+            words[c] = word;
+        }
+        if (valid) {
+            const int64_t dst = dst_row ? dst_row[row] : row;
+            if (dst >= 0) {                                // negative = row not to be written
+                uint4* out = reinterpret_cast<uint4*>(codes + dst * code_row_stride);
+                out[0] = make_uint4(words[0], words[1], words[2], words[3]);
+                out[1] = make_uint4(words[4], words[5], words[6], words[7]);
+            }
+        }
+    } else if (tid == 0 && status != nullptr) {
+        atomicOr(status, SK_DEV_WAIT_TIMEOUT);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TC_N)
+                     : "memory");
+    }
+}
+
+// One warp per listed projection: exact fp64 dot product, then set or clear the code bit.
+__global__ void __launch_bounds__(256)
+hash_fix_kernel(const __nv_bfloat16* __restrict__ keys, int64_t key_row_stride,
+                const __nv_bfloat16* __restrict__ planes, uint8_t* __restrict__ codes,
+                int64_t code_row_stride, const int64_t* __restrict__ dst_row,
+                const uint32_t* __restrict__ fix_count, const uint32_t* __restrict__ fix_list,
+                uint32_t fix_cap) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t n = min(*fix_count, fix_cap);
+    const uint32_t warps = gridDim.x * (blockDim.x >> 5);
+    for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < n; e += warps) {
+        const uint32_t ent = fix_list[e];
+        const int64_t row = ent >> 8;
+        const int col = (int)(ent & 0xffu);               // l * 8 + p
+        const __nv_bfloat16* k = keys + row * key_row_stride;
+        const __nv_bfloat16* p = planes + (size_t)col * TC_D;
+        double s = 0.0;
+#pragma unroll
+        for (int i = 0; i < TC_D / 32; ++i) {
+            const int d = lane * (TC_D / 32) + i;
+            s = fma((double)__bfloat162float(k[d]), (double)__bfloat162float(p[d]), s);
+        }
+        s = warp_sum_f64(s);
+        if (lane == 0) {
+            const int64_t dst = dst_row ? dst_row[row] : row;
+            if (dst < 0) continue;
+            const int l = col >> 3, bit = 7 - (col & 7);
+            uint8_t* byte = codes + dst * code_row_stride + l;
+            uint32_t* word = reinterpret_cast<uint32_t*>(reinterpret_cast<uintptr_t>(byte) & ~(uintptr_t)3);
+            const uint32_t m = 1u << (8 * (int)(reinterpret_cast<uintptr_t>(byte) & 3) + bit);
+            if (s >= 0.0) atomicOr(word, m); else atomicAnd(word, ~m);
+        }
+    }
+}
+
+// Runs only when the list overflowed: exact hashing of every row (the slow, always-right path).
+__global__ void __launch_bounds__(HASH_THREADS)
+hash_exact_if_overflow_kernel(const __nv_bfloat16* __restrict__ keys, int64_t key_row_stride,
+                              const __nv_bfloat16* __restrict__ planes, int64_t N, uint8_t* codes,
+                              int64_t code_row_stride, const int64_t* __restrict__ dst_row,
+                              const uint32_t* __restrict__ fix_count, uint32_t fix_cap) {
+    if (*fix_count <= fix_cap) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int l = blockIdx.y * HASH_WARPS + warp;
+    for (int64_t n0 = (int64_t)blockIdx.x * HASH_ROWS; n0 < N; n0 += (int64_t)gridDim.x * HASH_ROWS) {
+        double kd[HASH_ROWS][4];
+        void* code_ptr[HASH_ROWS];
+#pragma unroll
+        for (int r = 0; r < HASH_ROWS; ++r) {
+            const int64_t n = n0 + r;
+            if (n < N) {
+                load_row_f64<__nv_bfloat16, 4>(keys + n * key_row_stride, lane, kd[r]);
+                const int64_t dst = dst_row ? dst_row[n] : n;
+                code_ptr[r] = dst >= 0 ? codes + dst * code_row_stride : nullptr;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) kd[r][i] = 0.0;
+                code_ptr[r] = nullptr;
+            }
+        }
+        if (l < TC_N / 8) hash_table_rows<__nv_bfloat16, 4>(kd, code_ptr, planes, l, 8, 1, lane);
+    }
+}
+
+// Cache row of every new (b, s, kvh) row; -1 (and a status flag) for positions outside the cache.
+__global__ void __launch_bounds__(256)
+cache_rows_kernel(const int64_t* __restrict__ input_pos, int B, int S, int Hkv, int64_t Tcap,
+                  int64_t* __restrict__ dst_row, int32_t* status) {
+    const int64_t N = (int64_t)B * S * Hkv;
+    for (int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; n < N; n += (int64_t)gridDim.x * blockDim.x) {
+        const int kvh = (int)(n % Hkv);
+        const int s = (int)((n / Hkv) % S);
+        const int b = (int)(n / ((int64_t)Hkv * S));
+        const int64_t pos = input_pos[s];
+        const bool ok = pos >= 0 && pos < Tcap;
+        dst_row[n] = ok ? ((int64_t)b * Hkv + kvh) * Tcap + pos : -1;
+        if (!ok && status != nullptr) atomicOr(status, SK_DEV_POS_OUT_OF_RANGE);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// [rows, 128] bf16 row-major (row stride in elements) -> boxes of 64 columns x box_rows rows
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, int64_t row_stride, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return fail(SK_ERR_CUDA, "sk_hash_keys_tc: cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[2] = {(cuuint64_t)TC_D, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_KHALF, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SK_ERR_CUDA, "sk_hash_keys_tc: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return SK_OK;
+}
+
+constexpr size_t TC_WS_HEADER = 256 + TC_N * sizeof(float);   // list counter | plane norms
+
+}  // namespace
+
+int launch_cache_rows(const int64_t* input_pos, int B, int S, int Hkv, int64_t Tcap, int64_t* dst_row,
+                      int32_t* status, cudaStream_t st) {
+    const int64_t N = (int64_t)B * S * Hkv;
+    int64_t g = (N + 255) / 256;
+    if (g > 148 * 8) g = 148 * 8;
+    cache_rows_kernel<<<(unsigned)g, 256, 0, st>>>(input_pos, B, S, Hkv, Tcap, dst_row, status);
+    return check_launch("cache_rows_kernel");
+}
+
+size_t hash_keys_tc_workspace_bytes(int64_t N) {
+    const int64_t cap = N > 4096 ? N : 4096;
+    return TC_WS_HEADER + (size_t)cap * sizeof(uint32_t);
+}
+
+int launch_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* planes, int64_t N, uint8_t* codes,
+                        int64_t code_row_stride, const int64_t* dst_row, void* workspace, size_t workspace_bytes,
+                        int32_t* status, cudaStream_t st) {
+    if (N == 0) return SK_OK;
+    if (N >= (1 << 24)) return fail(SK_ERR_UNSUPPORTED, "sk_hash_keys_tc: at most 2^24 - 1 rows per call");
+    if (workspace_bytes < TC_WS_HEADER + 1024 * sizeof(uint32_t))
+        return fail(SK_ERR_WORKSPACE, "sk_hash_keys_tc: workspace %zu bytes is too small", workspace_bytes);
+    char* ws = static_cast<char*>(workspace);
+    uint32_t* fix_count = reinterpret_cast<uint32_t*>(ws);
+    float* pnorm = reinterpret_cast<float*>(ws + 256);
+    uint32_t* fix_list = reinterpret_cast<uint32_t*>(ws + TC_WS_HEADER);
+    const uint32_t fix_cap = (uint32_t)((workspace_bytes - TC_WS_HEADER) / sizeof(uint32_t));
+    CUtensorMap map_k, map_p;
+    int rc = make_map(&map_k, keys, (uint64_t)N, key_row_stride, TC_ROWS);
+    if (rc != SK_OK) return rc;
+    rc = make_map(&map_p, planes, TC_N, TC_D, TC_N);
+    if (rc != SK_OK) return rc;
+    cudaError_t e = cudaMemsetAsync(fix_count, 0, sizeof(uint32_t), st);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "sk_hash_keys_tc: cudaMemsetAsync: %s", cudaGetErrorString(e));
+    const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(keys);
+    const __nv_bfloat16* pb = static_cast<const __nv_bfloat16*>(planes);
+    plane_norm_kernel<<<1, 256, 0, st>>>(pb, pnorm);
+    const size_t smem = TC_SMEM_TILES + 1024;
+    e = cudaFuncSetAttribute(hash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_tc_kernel smem attribute: %s", cudaGetErrorString(e));
+    const unsigned tiles = (unsigned)((N + TC_ROWS - 1) / TC_ROWS);
+    hash_tc_kernel<<<tiles, TC_ROWS, smem, st>>>(map_k, map_p, kb, key_row_stride, pnorm, N, codes,
+                                                 code_row_stride, dst_row, fix_count, fix_list, fix_cap, status);
+    rc = check_launch("hash_tc_kernel");
+    if (rc != SK_OK) return rc;
+    hash_fix_kernel<<<148, 256, 0, st>>>(kb, key_row_stride, pb, codes, code_row_stride, dst_row, fix_count,
+                                         fix_list, fix_cap);
+    dim3 grid(148 * 4, TC_N / 8 / HASH_WARPS);
+    hash_exact_if_overflow_kernel<<<grid, HASH_THREADS, 0, st>>>(kb, key_row_stride, pb, N, codes, code_row_stride,
+                                                                 dst_row, fix_count, fix_cap);
+    return check_launch("hash_tc fix-up kernels");
+}
+
+}  // namespace sk

@@ -57,6 +57,26 @@ def hash_keys(keys: torch.Tensor, planes: torch.Tensor, code_dtype=torch.uint8) 
     return codes
 
 
+def hash_keys_tc(keys: torch.Tensor, planes: torch.Tensor) -> torch.Tensor:
+    """Tensor-core bulk hashing: bf16 keys [..., 128], planes [32, 8, 128] -> uint8 codes [..., 32],
+    bit-identical to `hash_keys`."""
+    _require_cuda(keys, planes)
+    L, P, D = planes.shape
+    keys = keys.contiguous()
+    planes = planes.contiguous()
+    N = keys.numel() // D
+    codes = torch.empty(*keys.shape[:-1], L, dtype=torch.uint8, device=keys.device)
+    ws = torch.empty(int(lib().sk_hash_keys_tc_workspace_bytes(N)), dtype=torch.uint8, device=keys.device)
+    if dtype_code(keys) != _lib.SK_BF16 or dtype_code(planes) != _lib.SK_BF16:
+        raise RuntimeError("hash_keys_tc needs bf16 keys and planes")
+    check(lib().sk_hash_keys_tc(ptr(keys), D, ptr(planes), N, D, L, P, ptr(codes), L, None, ptr(ws), ws.numel(),
+                                None, stream_ptr(keys.device)), "sk_hash_keys_tc")
+    return codes
+
+
+TC_APPEND_MIN_ROWS = 1024
+
+
 def kv_append(k_cache, v_cache, codes, v_norm, prefill_len, input_pos, k_new, v_new, planes,
               status: Optional[torch.Tensor] = None) -> None:
     """Write S new tokens (k_new/v_new [B,S,Hkv,D]) at `input_pos` [S] (int64, device) into
@@ -75,6 +95,16 @@ def kv_append(k_cache, v_cache, codes, v_norm, prefill_len, input_pos, k_new, v_
     k_new = k_new.contiguous()
     v_new = v_new.contiguous()
     planes = planes.contiguous()
+    if (B * S * Hkv >= TC_APPEND_MIN_ROWS and k_new.dtype == torch.bfloat16 and planes.dtype == torch.bfloat16
+            and D == 128 and L == 32 and P == 8):
+        # prefill-sized batch: projection on the tensor cores
+        ws = torch.empty(int(lib().sk_kv_append_tc_workspace_bytes(B, S, Hkv)), dtype=torch.uint8,
+                         device=k_cache.device)
+        check(lib().sk_kv_append_tc(ptr(k_new), ptr(v_new), dtype_code(k_new), ptr(input_pos), ptr(planes),
+                                    dtype_code(planes), ptr(k_cache), ptr(v_cache), ptr(codes), ptr(v_norm),
+                                    ptr(prefill_len), ptr(status), B, S, Hkv, D, Tcap, L, P, ptr(ws), ws.numel(),
+                                    stream_ptr(k_cache.device)), "sk_kv_append_tc")
+        return
     check(lib().sk_kv_append(ptr(k_new), ptr(v_new), dtype_code(k_new), ptr(input_pos), ptr(planes),
                              dtype_code(planes), ptr(k_cache), ptr(v_cache), ptr(codes), ptr(v_norm),
                              ptr(prefill_len), ptr(status), B, S, Hkv, D, Tcap, L, P,

@@ -475,3 +475,38 @@ def test_fused_score_select_device_length_and_capacity():
     k = want.shape[-1]
     assert (got_len == k).all()
     assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values)
+
+
+# ---------------------------------------------------------------------------- tensor-core bulk hashing
+def test_tensor_core_hashing_is_bit_exact():
+    g = torch.Generator().manual_seed(31)
+    N = 5000 + 37
+    planes = torch.randn(32, 8, 128, generator=g).bfloat16()
+    keys = (torch.randn(N, 128, generator=g) * torch.exp(torch.randn(128, generator=g))).bfloat16()
+    keys[5] = 0                                            # a zero row: every projection is exactly 0
+    keys[6] = 0
+    keys[6, 0], keys[6, 1] = planes[3, 2, 1], -planes[3, 2, 0]   # exactly orthogonal to plane (3,2)
+    keys[7] = planes[10, 4] * 1e-3                         # tiny but parallel to a plane
+    keys[8] = -planes[10, 4]
+    keys[100:200] *= 1e-20                                 # very small magnitudes
+    keys[200:300] *= 1e18
+    want, _ = orc.hard_hash_keys_exact(keys.float()[None, :, None, :], planes.float())
+    want = want[0, :, 0].to(torch.uint8)
+    got = ops.hash_keys_tc(cu(keys), cu(planes)).cpu()
+    assert torch.equal(got, want)
+    assert torch.equal(ops.hash_keys(cu(keys), cu(planes)).cpu(), want)
+    assert (got[5] == 255).all()
+
+
+def test_tensor_core_hashing_overflow_path_is_exact():
+    # every key exactly orthogonal to many planes: the near-zero list overflows and the exact
+    # rehash takes over
+    g = torch.Generator().manual_seed(32)
+    planes = torch.randn(32, 8, 128, generator=g).bfloat16()
+    planes[:, :, 64:] = 0
+    N = 6000
+    keys = torch.zeros(N, 128)
+    keys[:, 64:] = torch.randn(N, 64, generator=g)         # support disjoint from the planes: all dots are 0
+    keys = keys.bfloat16()
+    got = ops.hash_keys_tc(cu(keys), cu(planes)).cpu()
+    assert (got == 255).all()
