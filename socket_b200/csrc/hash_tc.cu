@@ -28,6 +28,7 @@ constexpr uint32_t TC_A_HALF_BYTES = TC_ROWS * 128;   // 16 KiB
 constexpr uint32_t TC_B_HALF_BYTES = TC_N * 128;      // 32 KiB
 constexpr uint32_t TC_SMEM_TILES = 2 * TC_A_HALF_BYTES + 2 * TC_B_HALF_BYTES;   // 96 KiB
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
+constexpr int TC_THREADS = 256;       // two threads per accumulator row, 128 columns each
 constexpr float TC_BAND = 1.52587890625e-05f;         // 2^-16
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -95,7 +96,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 struct TcShared {
     uint64_t tma_bar, mma_bar;
     uint32_t tmem_base;
-    float plane_norm[TC_N];
+    float plane_norm[TC_N + 1];       // [TC_N] = the largest norm
 };
 
 // ||plane_n|| for the 256 planes, one warp per plane (grid-stride).
@@ -112,9 +113,15 @@ plane_norm_kernel(const __nv_bfloat16* __restrict__ planes, float* __restrict__ 
         for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(FULL, s, o);
         if (lane == 0) out[n] = sqrtf(s) * 1.001f;
     }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float mx = 0.f;
+        for (int n = 0; n < TC_N; ++n) mx = fmaxf(mx, out[n]);
+        out[TC_N] = mx;
+    }
 }
 
-__global__ void __launch_bounds__(TC_ROWS)
+__global__ void __launch_bounds__(TC_THREADS)
 hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_p,
                const __nv_bfloat16* __restrict__ keys, int64_t key_row_stride,
                const float* __restrict__ plane_norm, int64_t N, uint8_t* __restrict__ codes,
@@ -128,7 +135,7 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t row0 = (int64_t)blockIdx.x * TC_ROWS;
 
-    for (int i = tid; i < TC_N; i += TC_ROWS) ts.plane_norm[i] = plane_norm[i];
+    for (int i = tid; i <= TC_N; i += TC_THREADS) ts.plane_norm[i] = plane_norm[i];
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&ts.tma_bar)));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&ts.mma_bar)));
@@ -171,8 +178,10 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const bool ok = mbar_wait_bounded(&ts.mma_bar, 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (__syncthreads_and(ok)) {
-        // ---- epilogue: one accumulator row per thread
-        const int64_t row = row0 + tid;
+        // ---- epilogue: warps w and w+4 share the 32 accumulator lanes 32*(w%4).., half the
+        // columns each; a thread owns one row and 128 columns = 16 tables = 16 code bytes
+        const int quad = warp & 3, chalf = warp >> 2;
+        const int64_t row = row0 + quad * 32 + lane;
         const bool valid = row < N;
         float knorm = 0.f;
         if (valid) {
@@ -191,31 +200,32 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             knorm = sqrtf(ss) * 1.001f;
         }
         const float thr = TC_BAND * knorm;
-        uint32_t words[TC_N / 32];
+        const float thr_max = valid ? thr * ts.plane_norm[TC_N] : -1.f;      // cheap first test, exact test inside
+        uint32_t words[4];
 #pragma unroll
-        for (int c = 0; c < TC_N / 32; ++c) {
+        for (int c4 = 0; c4 < 4; ++c4) {
+            const int c = chalf * 4 + c4;
             uint32_t r[32];
-            tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c * 32, r);
+            tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + c * 32, r);
             uint32_t word = 0;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float a = __uint_as_float(r[i]);
-                const int l4 = i >> 3, p = i & 7;
-                if (a >= 0.f) word |= 1u << (8 * l4 + 7 - p);
-                if (valid && fabsf(a) <= thr * ts.plane_norm[c * 32 + i] && knorm > 0.f) {
-                    const uint32_t slot = atomicAdd(fix_count, 1u);
-                    if (slot < fix_cap) fix_list[slot] = ((uint32_t)row << 8) | (uint32_t)(c * 32 + i);
+                if (a >= 0.f) word |= 1u << (8 * (i >> 3) + 7 - (i & 7));
+                if (fabsf(a) <= thr_max) {
+                    if (fabsf(a) <= thr * ts.plane_norm[c * 32 + i] && knorm > 0.f) {
+                        const uint32_t slot = atomicAdd(fix_count, 1u);
+                        if (slot < fix_cap) fix_list[slot] = ((uint32_t)row << 8) | (uint32_t)(c * 32 + i);
+                    }
                 }
             }
-            words[c] = word;
+            words[c4] = word;
         }
         if (valid) {
             const int64_t dst = dst_row ? dst_row[row] : row;
-            if (dst >= 0) {                                // negative = row not to be written
-                uint4* out = reinterpret_cast<uint4*>(codes + dst * code_row_stride);
-                out[0] = make_uint4(words[0], words[1], words[2], words[3]);
-                out[1] = make_uint4(words[4], words[5], words[6], words[7]);
-            }
+            if (dst >= 0)                                  // negative = row not to be written
+                reinterpret_cast<uint4*>(codes + dst * code_row_stride)[chalf] =
+                    make_uint4(words[0], words[1], words[2], words[3]);
         }
     } else if (tid == 0 && status != nullptr) {
         atomicOr(status, SK_DEV_WAIT_TIMEOUT);
@@ -340,7 +350,7 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, int64_t row_stri
     return SK_OK;
 }
 
-constexpr size_t TC_WS_HEADER = 256 + TC_N * sizeof(float);   // list counter | plane norms
+constexpr size_t TC_WS_HEADER = 256 + (TC_N + 16) * sizeof(float);   // list counter | plane norms + max
 
 }  // namespace
 
@@ -384,7 +394,7 @@ int launch_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* pl
     e = cudaFuncSetAttribute(hash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_tc_kernel smem attribute: %s", cudaGetErrorString(e));
     const unsigned tiles = (unsigned)((N + TC_ROWS - 1) / TC_ROWS);
-    hash_tc_kernel<<<tiles, TC_ROWS, smem, st>>>(map_k, map_p, kb, key_row_stride, pnorm, N, codes,
+    hash_tc_kernel<<<tiles, TC_THREADS, smem, st>>>(map_k, map_p, kb, key_row_stride, pnorm, N, codes,
                                                  code_row_stride, dst_row, fix_count, fix_list, fix_cap, status);
     rc = check_launch("hash_tc_kernel");
     if (rc != SK_OK) return rc;
