@@ -238,6 +238,8 @@ int sk_score_select_applicable(int B, int H, int Hkv, int L, int R, int64_t T, i
     if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || L != 32 || R > 256 || T <= 0) return 0;
     const int ht = lut_head_tile(H / Hkv);
     const ScorePlan plan = make_score_plan(B * Hkv * ((H / Hkv) / ht), T, M);
+    // the scorer addresses the candidate buffer with 32-bit entry indices
+    if ((int64_t)B * H * plan.chunks_max * SC_WARPS * plan.cap_w >= (int64_t)1 << 31) return 0;
     return fused_filter_applicable(plan, T, M) ? 1 : 0;
 }
 

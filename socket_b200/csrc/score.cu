@@ -248,8 +248,10 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
 #pragma unroll
         for (int j = 0; j < HT; ++j) cutv[j] = -INFINITY;
         bool first = true;
-        // this warp's run of head j starts at cand[(((row0 + j) * chunks_max + chunk) * 32 + warp) * cap_w];
-        // the address is formed only when a key is kept (rare), not carried in registers
+        // this warp's run of head j starts at entry run_index0 + j * run_stride of the candidate buffer
+        // (32-bit entry indices: the buffer holds far fewer than 2^31 entries)
+        const int run_stride = fa.chunks_max * SC_WARPS * fa.cap_w;
+        const int run_index0 = FILTER ? (((int)row0 * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w : 0;
 
         if (FILTER) {
             // ---- sample = first key of every lane: scores, min / max, histogram, cut
@@ -344,14 +346,14 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             for (int j = 0; j < HT; ++j) {
                 const bool hit = valid && sv[j] >= cutv[j];
                 const unsigned bal = __ballot_sync(FULL, hit);
-                const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
-                if (hit) {
+                if (bal != 0u) {                              // warp-uniform
+                    const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
                     const int pos = have + __popc(bal & ((1u << lane) - 1u));
-                    if (pos < fa.cap_w)
-                        fa.cand[(((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w + pos] =
+                    if (hit && pos < fa.cap_w)
+                        fa.cand[(size_t)(run_index0 + j * run_stride + pos)] =
                             make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
+                    cnt4 += (uint32_t)min(__popc(bal), 255 - have) << (8 * j);
                 }
-                cnt4 += (uint32_t)min(__popc(bal), 255 - have) << (8 * j);
             }
             first = false;
         }
@@ -381,14 +383,14 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
                 for (int j = 0; j < HT; ++j) {
                     const bool hit = valid && sv[j] >= cutv[j];
                     const unsigned bal = __ballot_sync(FULL, hit);
-                    const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
-                    if (hit) {
+                    if (bal != 0u) {                              // warp-uniform
+                        const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
                         const int pos = have + __popc(bal & ((1u << lane) - 1u));
-                        if (pos < fa.cap_w)
-                        fa.cand[(((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w + pos] =
-                            make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
+                        if (hit && pos < fa.cap_w)
+                            fa.cand[(size_t)(run_index0 + j * run_stride + pos)] =
+                                make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
+                        cnt4 += (uint32_t)min(__popc(bal), 255 - have) << (8 * j);
                     }
-                    cnt4 += (uint32_t)min(__popc(bal), 255 - have) << (8 * j);
                 }
             } else if (valid) {
 #pragma unroll
