@@ -11,7 +11,7 @@
 // lookups are arranged to be bank-conflict free for ht = 4: the table is stored
 // [bucket][table][head], which puts table l in 16-byte bank group l mod 8, and the 8 lanes
 // of a quarter warp walk the tables of each group of 8 in a different order
-// (table = j ^ (lane & 7)), so that at every step they hit 8 distinct bank groups whatever
+// (table = j ^ (key index & 7)), so that at every step they hit 8 distinct bank groups whatever
 // the bucket values are.  The permutation is applied to the code bytes with two PRMTs per
 // 8 bytes.  Consequence: the L terms of a score are added in a lane-dependent order; the
 // result differs from the ascending-order sum by fp32 rounding only (~1e-7 relative).
@@ -130,6 +130,88 @@ __device__ __forceinline__ void warp_hist_add256(uint32_t* hist, uint32_t bin, b
     }
 }
 
+// Per-head cut from one sample score per thread (sv[j], `valid`): block-wide min / max, a
+// 256-bin value histogram, and the bin boundary that about frac of the sample exceeds.  The cuts
+// end up in fs.cut[] (all threads read them after the trailing barrier) and, for the select
+// kernel's check, in cut_out[j * cut_stride].  Must be called by the whole CTA.
+template <int HT>
+__device__ __forceinline__ void filter_cuts(FilterShared& fs, const float (&sv)[HT], bool valid, float frac,
+                                            float* __restrict__ cut_out, size_t cut_stride) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int j = 0; j < HT; ++j) {
+        const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
+        float lo = fin ? sv[j] : INFINITY, hi = fin ? sv[j] : -INFINITY;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            lo = fminf(lo, __shfl_xor_sync(FULL, lo, o));
+            hi = fmaxf(hi, __shfl_xor_sync(FULL, hi, o));
+        }
+        if (lane == 0) {
+            fs.red_min[j][warp] = lo;
+            fs.red_max[j][warp] = hi;
+        }
+    }
+    __syncthreads();
+    if (warp < HT) {
+        float lo = fs.red_min[warp][lane], hi = fs.red_max[warp][lane];
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            lo = fminf(lo, __shfl_xor_sync(FULL, lo, o));
+            hi = fmaxf(hi, __shfl_xor_sync(FULL, hi, o));
+        }
+        if (lane == 0) {
+            fs.fmin[warp] = lo;
+            fs.scale[warp] = hi > lo ? 254.0f / (hi - lo) : 0.f;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < HT; ++j) {
+        const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
+        const uint32_t bin = min(__float2uint_rz((sv[j] - fs.fmin[j]) * fs.scale[j]), 255u);
+        warp_hist_add256(fs.hist[j], fin ? bin : 0u, fin);
+    }
+    __syncthreads();
+    if (warp < HT) {
+        // bins in descending order, 8 per lane
+        uint32_t c[8], local = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            c[i] = fs.hist[warp][255 - (8 * lane + i)];
+            local += c[i];
+        }
+        uint32_t inc = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t n = __shfl_up_sync(FULL, inc, o);
+            if (lane >= o) inc += n;
+        }
+        const uint32_t n_samp = __shfl_sync(FULL, inc, 31);
+        uint32_t target = (uint32_t)ceilf(frac * (float)n_samp) + 4u;
+        if (target > n_samp) target = n_samp;
+        uint32_t before = inc - local;
+        int found = -1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (target > 0 && before < target && before + c[i] >= target) found = 255 - (8 * lane + i);
+            before += c[i];
+        }
+        // exactly one lane finds the bin (none if the sample is empty)
+        const unsigned who = __ballot_sync(FULL, found >= 0);
+        float cut = -INFINITY;       // empty or degenerate sample: keep everything
+        if (who) {
+            const int bin = __shfl_sync(FULL, found, __ffs(who) - 1);
+            if (fs.scale[warp] > 0.f && bin >= 1) cut = fs.fmin[warp] + (float)bin / fs.scale[warp];
+        }
+        if (lane == 0) {
+            fs.cut[warp] = cut;
+            cut_out[(size_t)warp * cut_stride] = cut;
+        }
+    }
+    __syncthreads();
+}
+
 // L: tables per key (bytes per key), HT: query heads per table word.
 // FILTER = false: every score is written to `scores`.
 // FILTER = true:  nothing is written for most keys.  Each CTA estimates, per head, a cut from
@@ -162,11 +244,6 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
     const int tiles = rep / HT;
     const int Teff = effective_len(T, T_dev);
     const uint32_t lut_bytes = (uint32_t)R * CODE_STRIDE;
-
-    const int m = lane & 7;
-    const uint32_t sel_lo = 0x3210u ^ (0x1111u * m);
-    const uint32_t sel_hi = 0x7654u ^ (0x1111u * m);
-    const uint32_t mL = (uint32_t)m * L_STRIDE;
 
     if (threadIdx.x == 0) mbar_init(bar, 1);
     __syncthreads();
@@ -222,6 +299,13 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         const int per_warp = (int)(((t1_raw - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32);
         const int ws = (int)t0 + warp * per_warp;
         const int we = min((int)t1, ws + per_warp);
+        // table order of a key depends on its index only: table = j ^ (t & 7) inside each group of
+        // 8, so that any 8 consecutive keys (a quarter warp) hit 8 distinct bank groups; the lane's
+        // keys are 32 apart, hence one permutation per lane and segment
+        const int m = (ws + lane) & 7;
+        const uint32_t sel_lo = 0x3210u ^ (0x1111u * m);
+        const uint32_t sel_hi = 0x7654u ^ (0x1111u * m);
+        const uint32_t mL = (uint32_t)m * L_STRIDE;
         const uint4* cg = reinterpret_cast<const uint4*>(codes + (size_t)bk * Tcap * L);
         const __half* vg = v_norm + (size_t)bk * Tcap;
 
@@ -267,78 +351,7 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
 #pragma unroll
                 for (int j = 0; j < HT; ++j) sv[j] = 0.f;
             }
-#pragma unroll
-            for (int j = 0; j < HT; ++j) {
-                const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
-                float lo = fin ? sv[j] : INFINITY, hi = fin ? sv[j] : -INFINITY;
-#pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) {
-                    lo = fminf(lo, __shfl_xor_sync(FULL, lo, o));
-                    hi = fmaxf(hi, __shfl_xor_sync(FULL, hi, o));
-                }
-                if (lane == 0) {
-                    fs.red_min[j][warp] = lo;
-                    fs.red_max[j][warp] = hi;
-                }
-            }
-            __syncthreads();
-            if (warp < HT) {
-                float lo = fs.red_min[warp][lane], hi = fs.red_max[warp][lane];
-#pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) {
-                    lo = fminf(lo, __shfl_xor_sync(FULL, lo, o));
-                    hi = fmaxf(hi, __shfl_xor_sync(FULL, hi, o));
-                }
-                if (lane == 0) {
-                    fs.fmin[warp] = lo;
-                    fs.scale[warp] = hi > lo ? 254.0f / (hi - lo) : 0.f;
-                }
-            }
-            __syncthreads();
-#pragma unroll
-            for (int j = 0; j < HT; ++j) {
-                const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
-                const uint32_t bin = min(__float2uint_rz((sv[j] - fs.fmin[j]) * fs.scale[j]), 255u);
-                warp_hist_add256(fs.hist[j], fin ? bin : 0u, fin);
-            }
-            __syncthreads();
-            if (warp < HT) {
-                // bins in descending order, 8 per lane
-                uint32_t c[8], local = 0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    c[i] = fs.hist[warp][255 - (8 * lane + i)];
-                    local += c[i];
-                }
-                uint32_t inc = local;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t n = __shfl_up_sync(FULL, inc, o);
-                    if (lane >= o) inc += n;
-                }
-                const uint32_t n_samp = __shfl_sync(FULL, inc, 31);
-                uint32_t target = (uint32_t)ceilf(fa.frac * (float)n_samp) + 4u;
-                if (target > n_samp) target = n_samp;
-                uint32_t before = inc - local;
-                int found = -1;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (target > 0 && before < target && before + c[i] >= target) found = 255 - (8 * lane + i);
-                    before += c[i];
-                }
-                // exactly one lane finds the bin (none if the sample is empty)
-                const unsigned who = __ballot_sync(FULL, found >= 0);
-                float cut = -INFINITY;       // empty or degenerate sample: keep everything
-                if (who) {
-                    const int bin = __shfl_sync(FULL, found, __ffs(who) - 1);
-                    if (fs.scale[warp] > 0.f && bin >= 1) cut = fs.fmin[warp] + (float)bin / fs.scale[warp];
-                }
-                if (lane == 0) {
-                    fs.cut[warp] = cut;
-                    fa.cut[(row0 + warp) * fa.chunks_max + chunk] = cut;
-                }
-            }
-            __syncthreads();
+            filter_cuts<HT>(fs, sv, valid, fa.frac, fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max);
 #pragma unroll
             for (int j = 0; j < HT; ++j) cutv[j] = fs.cut[j];
             // the sample keys themselves
