@@ -416,6 +416,31 @@ def main():
             "frac_of_bf16_peak": None if tf_peak is None else round(flops / t_us / 1e6 / tf_peak, 4),
             "gbs": round(n_rows * (D * 2 + cfg.L) / t_us / 1e3, 1),
             "note": "sk_hash_keys_tc incl. its plane-norm, fix-up and gate launches; not in the step"}
+        # the whole prefill cache write (copy K/V + v_norm + codes) of S tokens; the tokens are the
+        # cache's own first S rows, so the cache is left unchanged
+        S_pf = min(T0, 8192)
+        k_pf = cache.k_cache[:, :, :S_pf].transpose(1, 2).contiguous()
+        v_pf = cache.v_cache[:, :, :S_pf].transpose(1, 2).contiguous()
+        pos_pf = torch.arange(S_pf, device=dev, dtype=torch.int64)
+
+        def _append():
+            ops.kv_append(cache.k_cache, cache.v_cache, cache.k_hard, cache.v_norm, cache.prefill_len,
+                          pos_pf, k_pf, v_pf, attn.planes)
+        for _ in range(2):
+            _append()
+        e0.record()
+        for _ in range(5):
+            _append()
+        e1.record()
+        torch.cuda.synchronize()
+        t_us = e0.elapsed_time(e1) / 5 * 1e3
+        rows_pf = B * Hkv * S_pf
+        bytes_pf = rows_pf * (4 * D * 2 + cfg.L + 2)      # K and V read + written, codes, v_norm
+        stages["prefill_kv_append"] = {
+            "us": round(t_us, 1), "rows": rows_pf, "gbs": round(bytes_pf / t_us / 1e3, 1),
+            "frac_of_hbm_peak": round(bytes_pf / t_us / 1e3 / peak, 4),
+            "note": "sk_kv_append_tc: copy + v_norm kernel, then tensor-core hashing; not in the step"}
+        del k_pf, v_pf
     A = a_codes + a_kv
     step_gbs = A / (ms_per_step * 1e-3) / 1e9
     stages["whole_step"] = {"us": round(ms_per_step * 1e3, 2), "algorithmic_bytes": A,

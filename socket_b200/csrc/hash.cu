@@ -47,6 +47,54 @@ kv_append_kernel(const KT* __restrict__ k_new, const KT* __restrict__ v_new,
                                 (int64_t)blockIdx.x * HASH_ROWS, blockIdx.y * HASH_WARPS);
 }
 
+// Bulk cache write without hashing (the tensor-core path hashes separately): one warp per new
+// (b, s, kvh) row of 128 bf16; lanes 0-15 move the key, lanes 16-31 the value (16 bytes each)
+// and accumulate ||v||^2 in fp64, so v_norm is the same number the fused append stores.
+__global__ void __launch_bounds__(256)
+kv_copy_kernel(const uint4* __restrict__ k_new, const uint4* __restrict__ v_new,
+               const int64_t* __restrict__ input_pos, uint4* __restrict__ k_cache,
+               uint4* __restrict__ v_cache, __half* __restrict__ v_norm, int32_t* prefill_len,
+               int32_t* status, int64_t N, int S, int Hkv, int64_t Tcap) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    bool bad = false;
+    int32_t max_len = 0;
+    for (int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); n < N; n += warps) {
+        const int kvh = (int)(n % Hkv);
+        const int s = (int)((n / Hkv) % S);
+        const int64_t b = n / ((int64_t)Hkv * S);
+        const int64_t pos = __ldg(input_pos + s);
+        if (pos < 0 || pos >= Tcap) {
+            bad = true;
+            continue;
+        }
+        const int64_t row = (b * Hkv + kvh) * Tcap + pos;
+        if (pos + 1 > max_len) max_len = (int32_t)(pos + 1);
+        if (lane < 16) {
+            k_cache[row * 16 + lane] = __ldg(k_new + n * 16 + lane);
+        } else {
+            const uint4 x = __ldg(v_new + n * 16 + (lane - 16));
+            v_cache[row * 16 + (lane - 16)] = x;
+            const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+            double ss = 0.0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const double lo = (double)__uint_as_float(w[i] << 16);
+                const double hi = (double)__uint_as_float(w[i] & 0xffff0000u);
+                ss = fma(lo, lo, ss);
+                ss = fma(hi, hi, ss);
+            }
+#pragma unroll
+            for (int o = 8; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffff0000u, ss, o);
+            if (lane == 16) v_norm[row] = __float2half_rn((float)sqrt(ss));
+        }
+    }
+    if (lane == 0) {
+        if (bad && status != nullptr) atomicOr(status, SK_DEV_POS_OUT_OF_RANGE);
+        if (max_len > 0) atomicMax(prefill_len, max_len);
+    }
+}
+
 template <typename KT, typename PT>
 int hash_keys_dispatch(const void* keys, int64_t krs, const void* planes, int64_t N, int D, int L,
                        int P, void* codes, int cb, int64_t crs, cudaStream_t st) {
@@ -121,13 +169,14 @@ int launch_kv_copy(const void* k_new, const void* v_new, int kv_dtype, const int
     const int64_t N = (int64_t)B * S * Hkv;
     if (N == 0) return SK_OK;
     if (kv_dtype != SK_BF16 || D != 128) return fail(SK_ERR_UNSUPPORTED, "kv copy: bf16 and head_dim 128 only");
-    const int64_t gx = (N + HASH_ROWS - 1) / HASH_ROWS;
-    if (gx > 0x7fffffff) return fail(SK_ERR_UNSUPPORTED, "kv copy: too many rows");
-    kv_append_kernel<__nv_bfloat16, __nv_bfloat16, 4><<<dim3((unsigned)gx, 1), HASH_THREADS, 0, st>>>(
-        (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, input_pos, (const __nv_bfloat16*)k_new,
-        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nullptr, (__half*)v_norm, prefill_len, status, B, S,
-        Hkv, Tcap, 0, 8);
-    return check_launch("kv_append_kernel (copy only)");
+    if ((((uintptr_t)k_new | (uintptr_t)v_new | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) != 0)
+        return fail(SK_ERR_MISALIGNED, "kv copy: K/V pointers must be 16-byte aligned");
+    int64_t gx = (N + 7) / 8;
+    if (gx > 148 * 16) gx = 148 * 16;
+    kv_copy_kernel<<<(unsigned)gx, 256, 0, st>>>((const uint4*)k_new, (const uint4*)v_new, input_pos, (uint4*)k_cache,
+                                                 (uint4*)v_cache, (__half*)v_norm, prefill_len, status, N, S, Hkv,
+                                                 Tcap);
+    return check_launch("kv_copy_kernel");
 }
 
 }  // namespace sk

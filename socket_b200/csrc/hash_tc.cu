@@ -99,25 +99,36 @@ struct TcShared {
     float plane_norm[TC_N + 1];       // [TC_N] = the largest norm
 };
 
-// ||plane_n|| for the 256 planes, one warp per plane (grid-stride).
-__global__ void __launch_bounds__(256)
+// ||plane_n|| * 1.001 for the 256 planes and their maximum.  One CTA of 1024 threads: warp w owns
+// planes 8w .. 8w+7 and issues all its loads before the first use.
+__global__ void __launch_bounds__(1024)
 plane_norm_kernel(const __nv_bfloat16* __restrict__ planes, float* __restrict__ out) {
+    static_assert(TC_N == 256 && TC_D == 128, "one warp per 8 planes, one 8-byte load per lane and plane");
+    __shared__ float wmax[32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int n = warp; n < TC_N; n += 8) {
-        float s = 0.f;
-        for (int d = lane; d < TC_D; d += 32) {
-            const float x = __bfloat162float(planes[(size_t)n * TC_D + d]);
-            s = fmaf(x, x, s);
-        }
+    uint2 raw[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        raw[i] = __ldg(reinterpret_cast<const uint2*>(planes + (size_t)(warp * 8 + i) * TC_D) + lane);
+    float mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float x0 = __uint_as_float(raw[i].x << 16), x1 = __uint_as_float(raw[i].x & 0xffff0000u);
+        const float x2 = __uint_as_float(raw[i].y << 16), x3 = __uint_as_float(raw[i].y & 0xffff0000u);
+        float s = fmaf(x0, x0, fmaf(x1, x1, fmaf(x2, x2, x3 * x3)));
 #pragma unroll
         for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(FULL, s, o);
-        if (lane == 0) out[n] = sqrtf(s) * 1.001f;
+        const float nrm = sqrtf(s) * 1.001f;
+        if (lane == 0) out[warp * 8 + i] = nrm;
+        mx = fmaxf(mx, nrm);
     }
+    if (lane == 0) wmax[warp] = mx;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float mx = 0.f;
-        for (int n = 0; n < TC_N; ++n) mx = fmaxf(mx, out[n]);
-        out[TC_N] = mx;
+    if (warp == 0) {
+        float v = wmax[lane];
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULL, v, o));
+        if (lane == 0) out[TC_N] = v;
     }
 }
 
@@ -389,7 +400,7 @@ int launch_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* pl
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "sk_hash_keys_tc: cudaMemsetAsync: %s", cudaGetErrorString(e));
     const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(keys);
     const __nv_bfloat16* pb = static_cast<const __nv_bfloat16*>(planes);
-    plane_norm_kernel<<<1, 256, 0, st>>>(pb, pnorm);
+    plane_norm_kernel<<<1, 1024, 0, st>>>(pb, pnorm);
     const size_t smem = TC_SMEM_TILES + 1024;
     e = cudaFuncSetAttribute(hash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_tc_kernel smem attribute: %s", cudaGetErrorString(e));
