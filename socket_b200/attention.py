@@ -145,3 +145,68 @@ class SocketAttention(nn.Module):
             self._step = (key, step)
         self._step[1].run()
         return out
+
+    def host_decoder(self, batch: int) -> "HostDecodeStep":
+        """A decode step fed from, and answering into, pinned host memory (see HostDecodeStep)."""
+        return HostDecodeStep(self, batch)
+
+
+class HostDecodeStep:
+    """One decode step whose inputs live in host memory: a single pinned staging block
+    `[input_pos | q | k_new | v_new]` goes to the device in one copy, the four kernels of
+    `sk_decode_step` run, and the output comes back into pinned memory — all of it one CUDA
+    graph, so a step costs one launch call.  Write the inputs through `h_q`, `h_k`, `h_v`,
+    `h_pos` (views of the staging block), call `launch()` and, once `wait()` returns, read
+    `h_out`.  `__call__` does the three for host tensors.  Build it after the cache is
+    allocated; the graph holds the cache's addresses."""
+
+    def __init__(self, attn: SocketAttention, batch: int):
+        cache = attn.kv_cache
+        assert cache is not None, "Call setup_cache() first so kv_cache exists"
+        dev, dt = cache.k_cache.device, cache.k_cache.dtype
+        B, H, Hkv, D = batch, attn.n_head, attn.n_local_heads, attn.head_dim
+        assert B == cache.k_cache.shape[0]
+        es = torch.empty((), dtype=dt).element_size()
+        nq, nkv = B * H * D * es, B * Hkv * D * es
+        total = 16 + nq + 2 * nkv
+        self.h_in = torch.zeros(total, dtype=torch.uint8).pin_memory()
+        self.d_in = torch.zeros(total, dtype=torch.uint8, device=dev)
+
+        def views(buf):
+            pos = buf[:8].view(torch.int64)
+            q = buf[16:16 + nq].view(dt).view(B, H, D)
+            k = buf[16 + nq:16 + nq + nkv].view(dt).view(B, 1, Hkv, D)
+            v = buf[16 + nq + nkv:].view(dt).view(B, 1, Hkv, D)
+            return pos, q, k, v
+
+        self.h_pos, self.h_q, self.h_k, self.h_v = views(self.h_in)
+        d_pos, d_q, d_k, d_v = views(self.d_in)
+        self.d_out = torch.empty(B, H, D, dtype=dt, device=dev)
+        self.h_out = torch.empty(B, H, D, dtype=dt).pin_memory()
+        self.h2d_bytes, self.d2h_bytes = total, self.h_out.numel() * es
+        self.step = ops.DecodeStep(cache, d_q, d_k, d_v, d_pos, attn.planes, attn.protos_T, self.d_out,
+                                   topk=attn.heavy_const, sink=attn.sink_size, window=attn.window_size,
+                                   T_max=cache.k_cache.shape[2], temperature=attn.temperature)
+        self.done = torch.cuda.Event()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.d_in.copy_(self.h_in, non_blocking=True)
+            self.step.run()
+            self.h_out.copy_(self.d_out, non_blocking=True)
+
+    def launch(self) -> None:
+        self.graph.replay()
+        self.done.record()
+
+    def wait(self) -> Tensor:
+        self.done.synchronize()
+        return self.h_out
+
+    @torch.no_grad()
+    def __call__(self, q: Tensor, k_new: Tensor, v_new: Tensor, pos: int) -> Tensor:
+        self.h_q.copy_(q)
+        self.h_k.copy_(k_new)
+        self.h_v.copy_(v_new)
+        self.h_pos[0] = pos
+        self.launch()
+        return self.wait()

@@ -351,6 +351,35 @@ def test_model_flow_decode_step_matches_reference():
     assert int(step.status) == 0
 
 
+def test_host_decoder_equals_device_path():
+    """The host-memory entry (pinned staging -> graph of copy, step, copy back) gives the same
+    bits as the device-tensor call on the same cache, and advances the cache the same way."""
+    B, H, Hkv, T, M, sink, window = 2, 8, 2, 5000, 128, 8, 24
+    inp = make_decode_inputs(B, H, Hkv, T + 2, seed=33, dtype=torch.bfloat16)
+    k_bshd = inp.k.permute(0, 2, 1, 3).contiguous()
+    v_bshd = inp.v.permute(0, 2, 1, 3).contiguous()
+    outs = []
+    for mode in ("device", "host"):
+        attn = SocketAttention(H, Hkv, 128, heavy_const=M, sink_size=sink, window_size=window,
+                               planes=inp.planes, protos_T=inp.protos_T, dtype=torch.bfloat16, device=DEV)
+        cache = attn.setup_cache(B, T + 64, dtype=torch.bfloat16)
+        cache.append(torch.arange(T, device=DEV), cu(k_bshd[:, :T]), cu(v_bshd[:, :T]), attn.planes)
+        got = []
+        hd = attn.host_decoder(B) if mode == "host" else None
+        for i in range(2):
+            kn, vn = k_bshd[:, T + i:T + i + 1].contiguous(), v_bshd[:, T + i:T + i + 1].contiguous()
+            if mode == "host":
+                o = hd(inp.q, kn, vn, T + i).clone()
+            else:
+                o = attn.sparse_decode(cu(inp.q), cu(kn), cu(vn), torch.tensor([T + i], device=DEV)).cpu()
+            got.append(o)
+        assert int(cache.prefill_len) == T + 2
+        outs.append((got, cache.k_hard[:, :, :T + 2].cpu(), cache.v_norm[:, :, :T + 2].cpu()))
+    for a, b in zip(outs[0][0], outs[1][0]):
+        assert torch.equal(a, b)
+    assert torch.equal(outs[0][1], outs[1][1]) and torch.equal(outs[0][2], outs[1][2])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_fused_decode_step_against_chained_oracle(dtype):
     B, H, Hkv, T, M, sink, window = 2, 8, 2, 3000, 96, 8, 24
