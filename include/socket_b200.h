@@ -201,6 +201,23 @@ SK_API int sk_score_select_list(const float* lut, const uint8_t* codes, const ui
                          void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Scorer and select in ONE launch on thread-block clusters: a cluster of up to 16 CTAs per KV
+ * head scores its keys for the four query heads of a table word, keeps all scores on chip and
+ * finds the exact top-M with a radix select whose histograms are combined through distributed
+ * shared memory.  Same list as sk_score followed by sk_select_list (sorted == 0, no mask), the
+ * top-M part in ascending index order.  No workspace.  Replaces the same reference code as
+ * sk_score_select_list.
+ *   sk_score_select_cluster_size(...) -> the cluster size used for the shape on the current
+ *   device, or 0 when the shape is outside this path (needs L = 32, R = 256, 4 | H/Hkv,
+ *   ceil(T / cluster size) <= 5120 keys per CTA and all B*Hkv*(H/Hkv/4) clusters resident at once).
+ * ---------------------------------------------------------------------------------- */
+SK_API int sk_score_select_cluster_size(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M);
+SK_API int sk_score_select_cluster(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
+                            int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
+                            int sink, int window, int32_t* list, int64_t list_row_stride, int32_t* list_len,
+                            int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * GQA sparse flash-decode.  Replaces sparse_attention_fwd and its two Triton kernels
  * (GPT-FAST/kernels/sparse.py:309-329, 102-235):
  *   out[b,h,:] = sum_j softmax_j(<q[b,h], K[b,h/rep,idx_j]>/sqrt(D)) V[b,h/rep,idx_j],
@@ -260,6 +277,13 @@ SK_API int sk_sparse_decode_static(const void* q, int q_dtype, const void* k_cac
  * select, attend.  Graph-capturable: the live length is read from `prefill_len` on the
  * device, grids are sized from `T_max`.
  * ---------------------------------------------------------------------------------- */
+enum sk_select_path {
+    SK_SELECT_AUTO = 0,
+    SK_SELECT_TWO_LAUNCH = 1,   /* sk_score + sk_select_list (score matrix in the workspace) */
+    SK_SELECT_FILTER = 2,       /* sk_score_filter + sk_select_candidates                   */
+    SK_SELECT_CLUSTER = 3       /* sk_score_select_cluster                                   */
+};
+
 typedef struct sk_decode_params {
     /* new token */
     const void* q;         /* [B,H,D]      q_dtype                                   */
@@ -292,6 +316,9 @@ typedef struct sk_decode_params {
     int64_t T_max;         /* upper bound of the live length during this call */
     int64_t M;
     int sink, window;
+    /* how the list is built: SK_SELECT_AUTO picks the fastest path the shape allows; the others pin
+     * one (SK_ERR_UNSUPPORTED if the shape is outside it).  All give the same list. */
+    int select_path;
 } sk_decode_params;
 
 SK_API size_t sk_decode_step_workspace_bytes(int B, int H, int Hkv, int D, int L, int R, int64_t T_max,

@@ -38,7 +38,7 @@ class DecodeParams(C.Structure):
         ("B", C.c_int), ("H", C.c_int), ("Hkv", C.c_int), ("D", C.c_int), ("L", C.c_int),
         ("P", C.c_int), ("R", C.c_int),
         ("Tcap", C.c_int64), ("T_max", C.c_int64), ("M", C.c_int64),
-        ("sink", C.c_int), ("window", C.c_int),
+        ("sink", C.c_int), ("window", C.c_int), ("select_path", C.c_int),
     ]
 
 
@@ -70,6 +70,9 @@ SIGNATURES = {
                                   _p, _sz, _p, _p]),
     "sk_score_select_list": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i64, _p, _i64, _i64, _i, _i, _p, _i64, _p,
                                   _p, _sz, _p, _p]),
+    "sk_score_select_cluster_size": (_i, [_i, _i, _i, _i, _i, _i64, _i64]),
+    "sk_score_select_cluster": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i64, _p, _i64, _i64, _i, _i, _p, _i64, _p,
+                                     _p, _p]),
     "sk_sparse_decode_workspace_bytes": (_sz, [_i, _i, _i, _i64]),
     "sk_sparse_decode": (_i, [_p, _i, _p, _p, _i, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _i, _i,
                               _i, _i, _i64, _p, _p, _sz, _p, _p]),

@@ -272,6 +272,32 @@ int sk_score_select_list(const float* lut, const uint8_t* codes, const uint16_t*
                                     list, list_row_stride, list_len, workspace, status, st);
 }
 
+int sk_score_select_cluster_size(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M) {
+    return score_select_cluster_size(B, H, Hkv, L, R, T, M);
+}
+
+int sk_score_select_cluster(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
+                            int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
+                            int sink, int window, int32_t* list, int64_t list_row_stride, int32_t* list_len,
+                            int32_t* status, void* stream) {
+    SK_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && L > 0 && R > 0 && T > 0 && M >= 0,
+               "sk_score_select_cluster: sizes must be positive");
+    if (B == 0) return SK_OK;
+    SK_REQUIRE(H % Hkv == 0, "sk_score_select_cluster: H=%d not a multiple of Hkv=%d", H, Hkv);
+    SK_REQUIRE(lut && codes && v_norm && list && list_len, "sk_score_select_cluster: null pointer");
+    SK_REQUIRE(T <= Tcap, "sk_score_select_cluster: T exceeds the cache capacity");
+    SK_REQUIRE(list_row_stride >= list_len_host(T, sink, window, M),
+               "sk_score_select_cluster: list_row_stride smaller than the list length");
+    SK_ALIGNED(lut, 16, "sk_score_select_cluster: lut");
+    SK_ALIGNED(codes, 16, "sk_score_select_cluster: codes");
+    if (score_select_cluster_size(B, H, Hkv, L, R, T, M) == 0)
+        return fail(SK_ERR_UNSUPPORTED,
+                    "sk_score_select_cluster: shape outside the one-launch path (needs L=32, R=256, 4 | H/Hkv, "
+                    "T <= 16 * 5120 and every cluster resident); use sk_score_select_list or sk_score + sk_select_list");
+    return launch_score_select_cluster(lut, codes, v_norm, B, H, Hkv, L, R, T, T_dev, Tcap, M, sink, window, list,
+                                       list_row_stride, list_len, status, (cudaStream_t)stream);
+}
+
 int sk_score_filter(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H, int Hkv,
                     int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M, void* workspace,
                     size_t workspace_bytes, int32_t* status, void* stream) {
@@ -413,7 +439,25 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
                           p->H, p->Hkv, p->D, p->L, p->P, p->R, nullptr, lut, stream);
         if (rc != SK_OK) return rc;
     }
-    if (lay.fused) {
+    SK_REQUIRE(p->select_path >= SK_SELECT_AUTO && p->select_path <= SK_SELECT_CLUSTER,
+               "sk_decode_step: select_path %d is not an sk_select_path", p->select_path);
+    const bool can_cluster = score_select_cluster_size(p->B, p->H, p->Hkv, p->L, p->R, p->T_max, p->M) != 0;
+    int path = p->select_path;
+    if (path == SK_SELECT_AUTO) path = lay.fused ? SK_SELECT_FILTER : (can_cluster ? SK_SELECT_CLUSTER : SK_SELECT_TWO_LAUNCH);
+    if (path == SK_SELECT_CLUSTER && !can_cluster)
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the one-launch scorer + select");
+    if (path == SK_SELECT_FILTER && !lay.fused)
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the filtering scorer + candidate select");
+    if (path == SK_SELECT_TWO_LAUNCH && lay.fused)
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: the workspace of this shape holds no score matrix; "
+                                        "use SK_SELECT_FILTER or SK_SELECT_AUTO");
+    if (path == SK_SELECT_CLUSTER) {
+        // one launch: scores stay in shared memory, select across the cluster
+        rc = launch_score_select_cluster(lut, p->codes, p->v_norm, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
+                                         p->prefill_len, p->Tcap, p->M, p->sink, p->window, list, list_stride,
+                                         list_len, p->status, st);
+        if (rc != SK_OK) return rc;
+    } else if (path == SK_SELECT_FILTER) {
         // filtering scorer + candidate select: no score array is written or re-read
         rc = launch_score_filter(lut, p->codes, p->v_norm, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
                                  p->prefill_len, p->Tcap, p->M, ws + lay.scores, p->status, st);

@@ -49,6 +49,30 @@ __device__ __forceinline__ int effective_len(int64_t T, const int32_t* T_dev) {
     return t < 0 ? 0 : (int)t;
 }
 
+// ---------------------------------------------------------------- shared-memory histograms
+// Histogram increment by all 32 lanes of a warp.  The lanes that hit the same bin as the first
+// active lane are merged into one atomic (score keys cluster, so one dominant bin per warp is the
+// common way thousands of atomics end up serialised on one address); the others add on their own.
+// Two warp collectives; match.any, which costs a round per distinct value, is kept for
+// hist_add_match() below.
+__device__ __forceinline__ void warp_hist_add(uint32_t* hist, uint32_t bin, bool active) {
+    const unsigned live = __ballot_sync(FULL, active);
+    if (live == 0u) return;
+    const int leader = __ffs(live) - 1;
+    const uint32_t first = __shfl_sync(FULL, bin, leader);
+    const unsigned same = __ballot_sync(FULL, active && bin == first);
+    if ((int)(threadIdx.x & 31) == leader) atomicAdd(&hist[first], (uint32_t)__popc(same));
+    else if (active && bin != first) atomicAdd(&hist[bin], 1u);
+}
+// Every group of equal bins merged into one atomic: for digits with very few distinct values.
+__device__ __forceinline__ void warp_hist_add_match(uint32_t* hist, uint32_t bin, bool active) {
+    const unsigned live = __ballot_sync(FULL, active);
+    if (active) {
+        const unsigned peers = __match_any_sync(live, bin);
+        if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
+    }
+}
+
 // ---------------------------------------------------------------- scorer work split
 // How the flat (KV-head group, key) space is cut into CTAs; shared by the scorer, which writes
 // per-(row, chunk, warp) candidate runs in its filtering mode, and the select kernel, which
@@ -162,6 +186,13 @@ int launch_select_candidates(const float* lut, const uint8_t* codes, const uint1
                              int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
                              int sink, int window, int sorted, int32_t* list, int64_t list_row_stride,
                              int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st);
+
+// One-launch scorer + exact select on thread-block clusters (score_cluster.cu)
+int score_select_cluster_size(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M);
+int launch_score_select_cluster(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
+                                int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
+                                int sink, int window, int32_t* list, int64_t list_row_stride, int32_t* list_len,
+                                int32_t* status, cudaStream_t st);
 
 // Tensor-core bulk hashing (bf16, head_dim 128, L*P = 256)
 size_t hash_keys_tc_workspace_bytes(int64_t N);

@@ -88,17 +88,6 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
     return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
 }
 
-// Histogram increment with the lanes of a warp that hit the same bin merged into one atomic
-// (score keys share their high bits, so without this thousands of atomics would serialise on
-// one address).  Must be called by all 32 lanes.
-__device__ __forceinline__ void warp_hist_add(uint32_t* hist, uint32_t bin, bool active) {
-    const unsigned live = __ballot_sync(FULL, active);
-    if (active) {
-        const unsigned peers = __match_any_sync(live, bin);
-        if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
-    }
-}
-
 // Block-wide min / max of one uint32 per thread; every thread gets the result.
 __device__ __forceinline__ void block_minmax(SelShared& s, uint32_t& lo, uint32_t& hi) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -519,7 +508,7 @@ __device__ __forceinline__ void select_row(SelShared& s, Scan& scan, const float
                 for (int base = 0; base < T; base += SEL_THREADS) {
                     const int t = base + tid;
                     const uint32_t k = t < T ? order_key(sc[t]) : 0u;
-                    warp_hist_add(s.hist, (k >> shift) & 0xffu, t < T && (k & mask) == prefix);
+                    warp_hist_add_match(s.hist, (k >> shift) & 0xffu, t < T && (k & mask) == prefix);
                 }
                 __syncthreads();
                 find_bin_desc(s, scan, (int)remaining);

@@ -252,6 +252,30 @@ def score_select_list(lut: torch.Tensor, codes: torch.Tensor, v_norm: torch.Tens
     return lst, ln, workspace
 
 
+def score_select_cluster_size(B: int, H: int, Hkv: int, L: int, R: int, T: int, M: int) -> int:
+    """Cluster size (2..16) of the one-launch scorer + select for this shape on the current
+    device, 0 when the shape is outside it."""
+    return int(lib().sk_score_select_cluster_size(B, H, Hkv, L, R, T, M))
+
+
+def score_select_cluster(lut: torch.Tensor, codes: torch.Tensor, v_norm: torch.Tensor, n_heads: int, T: int,
+                         M: int, sink: int, window: int, R: int = 256, T_dev: Optional[torch.Tensor] = None,
+                         status: Optional[torch.Tensor] = None):
+    """Scorer + exact select in one launch on thread-block clusters (`sk_score_select_cluster`):
+    the list of `score` followed by `select_list`, scores never leave the chip.  Returns
+    (sparse_list, sparse_len)."""
+    _require_cuda(lut, codes, v_norm)
+    B, Hkv, Tcap, L = codes.shape
+    M = min(M, T)
+    Ktot = list_len(T, sink, window, M)
+    lst = torch.empty(B, n_heads, Ktot, dtype=torch.int32, device=codes.device)
+    ln = torch.empty(B, n_heads, dtype=torch.int32, device=codes.device)
+    check(lib().sk_score_select_cluster(ptr(lut), ptr(codes), ptr(v_norm), B, n_heads, Hkv, L, R, T, ptr(T_dev),
+                                        Tcap, M, sink, window, ptr(lst), Ktot, ptr(ln), ptr(status),
+                                        stream_ptr(codes.device)), "sk_score_select_cluster")
+    return lst, ln
+
+
 def sparse_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   sparse_list: torch.Tensor, sparse_len: torch.Tensor, T: Optional[int] = None,
                   T_dev: Optional[torch.Tensor] = None,
@@ -284,6 +308,10 @@ def sparse_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return out
 
 
+# sk_select_path: how the decode step builds its list (all paths give the same list)
+SELECT_PATHS = {"auto": 0, "two_launch": 1, "filter": 2, "cluster": 3}
+
+
 class DecodeStep:
     """One fused decode step of one layer (`sk_decode_step`): append+hash the new token,
     soft-hash the query, score, select, attend — four launches on the current stream, no
@@ -295,7 +323,7 @@ class DecodeStep:
                  v_new: Optional[torch.Tensor], input_pos: Optional[torch.Tensor],
                  planes: torch.Tensor, protos_T: torch.Tensor, out: torch.Tensor, *, topk: int,
                  sink: int, window: int, T_max: int, temperature: float = 1.0,
-                 keep_list: bool = False):
+                 keep_list: bool = False, select_path: str = "auto"):
         B, Hkv, Tcap, D = cache.k_cache.shape
         H = q.shape[1]
         L, P, _ = planes.shape
@@ -321,11 +349,16 @@ class DecodeStep:
         p.q_dtype, p.kv_dtype, p.plane_dtype = dtype_code(q), dtype_code(cache.k_cache), dtype_code(planes)
         p.B, p.H, p.Hkv, p.D, p.L, p.P, p.R = B, H, Hkv, D, L, P, R
         p.Tcap, p.T_max, p.M, p.sink, p.window = Tcap, T_max, topk, sink, window
+        p.select_path = SELECT_PATHS[select_path]
         self.params = p
         self.device = dev
         # prologue (append + soft hash in one launch when q and the cache share a dtype), score,
         # select, decode
         self.n_launches = 4 if (k_new is None or q.dtype == cache.k_cache.dtype) else 5
+        fused = bool(lib().sk_score_select_applicable(B, H, Hkv, L, R, T_max, topk))
+        cluster = bool(lib().sk_score_select_cluster_size(B, H, Hkv, L, R, T_max, topk))
+        if select_path == "cluster" or (select_path == "auto" and cluster and not fused):
+            self.n_launches -= 1          # scorer and select are one launch
 
     def run(self) -> None:
         check(lib().sk_decode_step(C.byref(self.params), stream_ptr(self.device)), "sk_decode_step")

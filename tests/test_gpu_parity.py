@@ -506,6 +506,83 @@ def test_fused_score_select_device_length_and_capacity():
     assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values)
 
 
+# ---------------------------------------------------------------------------- one-launch scorer + select (clusters)
+def _cluster_vs_two_step(B, H, Hkv, T, M, sink, window, v_norm=None, codes=None, seed=0, Tcap=None, T_live=None):
+    g = torch.Generator().manual_seed(seed)
+    Tcap = Tcap or T
+    q = torch.randn(B, H, 128, generator=g)
+    planes = torch.randn(32, 8, 128, generator=g)
+    if codes is None:
+        codes = torch.randint(0, 256, (B, Hkv, Tcap, 32), generator=g, dtype=torch.uint8)
+    if v_norm is None:
+        v_norm = (torch.rand(B, Hkv, Tcap, generator=g) + 10.5).to(torch.float16)
+    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv,
+                           want_probs=False, want_lut=True)
+    codes_d, vn_d = cu(codes.contiguous()), cu(v_norm.contiguous())
+    T_eff = T if T_live is None else T_live
+    T_dev = None if T_live is None else torch.tensor(T_live, dtype=torch.int32, device=DEV)
+    scores = ops.score(lut, codes_d, vn_d, H, T_eff)
+    want, want_len = ops.select_list(scores, T_eff, M, sink, window)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got, got_len = ops.score_select_cluster(lut, codes_d, vn_d, H, T, M, sink, window, T_dev=T_dev, status=status)
+    assert int(status) == 0
+    assert torch.equal(got_len, want_len)
+    k = want.shape[-1]
+    Me = min(M, T_eff)
+    nb = k - Me
+    assert torch.equal(got[:, :, :nb], want[:, :, :nb])
+    heavy = got[:, :, nb:k]
+    # exactly the two-step selection (ties included), and in ascending index order
+    assert torch.equal(heavy, torch.sort(want[:, :, nb:], dim=-1).values)
+
+
+@pytest.mark.parametrize("B,H,Hkv,T,M", [(1, 32, 8, 32768, 1024), (1, 32, 8, 33801, 1024), (2, 8, 2, 20000, 512),
+                                         (1, 4, 1, 4096, 64), (1, 8, 2, 1000, 100), (1, 8, 2, 77, 200),
+                                         (1, 16, 2, 50001, 1), (1, 8, 1, 81920, 4096), (1, 8, 2, 40, 40), (2, 32, 8, 20000, 512)])
+def test_cluster_score_select_equals_two_step(B, H, Hkv, T, M):
+    assert 2 <= ops.score_select_cluster_size(B, H, Hkv, 32, 256, T, M) <= 16
+    _cluster_vs_two_step(B, H, Hkv, T, M, 8, 24, seed=T + M)
+
+
+def test_cluster_score_select_ties_and_hostile_rows():
+    T = 40000
+    ramp = (1.0 + 6.0 * torch.arange(T) / T).to(torch.float16)          # scores grow with position
+    _cluster_vs_two_step(1, 8, 2, T, 512, 4, 4, v_norm=ramp.expand(1, 2, T), seed=1)
+    block = torch.ones(T)
+    block[12000:15000] = 50.0                                           # one CTA holds all winners
+    _cluster_vs_two_step(1, 8, 2, T, 1024, 4, 4, v_norm=block.to(torch.float16).expand(1, 2, T), seed=2)
+    # all keys share their codes: every score of a row is equal, the lowest indices must win
+    flat = torch.ones(1, 2, T, dtype=torch.float16)
+    same = torch.randint(0, 256, (1, 2, 1, 32), dtype=torch.uint8).expand(1, 2, T, 32)
+    _cluster_vs_two_step(1, 8, 2, T, 256, 0, 0, v_norm=flat, codes=same, seed=3)
+    # a few distinct score levels with thousands of keys each: the boundary bin overflows the pairwise
+    # ranking and is refined level by level down to exact ties
+    few = torch.randint(0, 256, (1, 2, 4, 32), dtype=torch.uint8)
+    pick = torch.randint(0, 4, (T,))
+    _cluster_vs_two_step(1, 8, 2, T, 3000, 2, 2, v_norm=flat, codes=few[:, :, pick], seed=4)
+    # zero value norms (score 0) mixed with live keys, fewer live keys than the budget
+    vz = torch.zeros(1, 2, T, dtype=torch.float16)
+    vz[:, :, ::97] = 2.0
+    _cluster_vs_two_step(1, 8, 2, T, 1024, 4, 4, v_norm=vz, seed=5)
+
+
+def test_cluster_score_select_device_length():
+    _cluster_vs_two_step(1, 8, 2, 33000, 300, 4, 16, seed=9, T_live=30000)
+    _cluster_vs_two_step(1, 8, 2, 33000, 300, 4, 16, seed=10, T_live=1)
+    _cluster_vs_two_step(1, 8, 2, 33000, 300, 4, 16, seed=11, T_live=257)
+
+
+def test_cluster_score_select_rejects_shapes_outside_its_range():
+    assert ops.score_select_cluster_size(4, 32, 8, 32, 256, 131072, 2048) == 0      # keys per CTA
+    assert ops.score_select_cluster_size(1, 8, 8, 32, 256, 8192, 100) == 0          # one head per KV head
+    assert ops.score_select_cluster_size(1, 32, 8, 16, 256, 8192, 100) == 0         # L
+    lut = torch.zeros(8 * 32 * 256, device=DEV)
+    codes = torch.zeros(1, 8, 8192, 32, dtype=torch.uint8, device=DEV)
+    vn = torch.ones(1, 8, 8192, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError, match="outside the one-launch path"):
+        ops.score_select_cluster(lut, codes, vn, 8, 8192, 100, 4, 4)
+
+
 # ---------------------------------------------------------------------------- tensor-core bulk hashing
 def test_tensor_core_hashing_is_bit_exact():
     g = torch.Generator().manual_seed(31)
