@@ -1,6 +1,7 @@
 // extern "C" entry points: argument validation, workspace carving, kernel launches.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -8,6 +9,14 @@
 namespace sk {
 
 static thread_local char g_err[512] = "";
+static thread_local int g_pdl_depth = 0;
+
+bool pdl_chain_active() {
+    static const bool off = getenv("SOCKET_B200_NO_PDL") != nullptr;   // debugging aid: launch the step's kernels unchained
+    return g_pdl_depth > 0 && !off;
+}
+PdlChain::PdlChain() { ++g_pdl_depth; }
+PdlChain::~PdlChain() { --g_pdl_depth; }
 
 int fail(int status, const char* fmt, ...) {
     va_list ap;
@@ -411,6 +420,18 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
         return fail(SK_ERR_WORKSPACE, "sk_decode_step: workspace %zu < %zu bytes", p->workspace_bytes, lay.total);
     SK_REQUIRE(p->list == nullptr || p->list_row_stride >= lay.list_stride,
                "sk_decode_step: list_row_stride smaller than the list length %lld", (long long)lay.list_stride);
+    SK_REQUIRE(p->select_path >= SK_SELECT_AUTO && p->select_path <= SK_SELECT_CLUSTER,
+               "sk_decode_step: select_path %d is not an sk_select_path", p->select_path);
+    const bool can_cluster = score_select_cluster_size(p->B, p->H, p->Hkv, p->L, p->R, p->T_max, p->M) != 0;
+    int path = p->select_path;
+    if (path == SK_SELECT_AUTO) path = lay.fused ? SK_SELECT_FILTER : (can_cluster ? SK_SELECT_CLUSTER : SK_SELECT_TWO_LAUNCH);
+    if (path == SK_SELECT_CLUSTER && !can_cluster)
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the one-launch scorer + select");
+    if (path == SK_SELECT_FILTER && !lay.fused)
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the filtering scorer + candidate select");
+    if (path == SK_SELECT_TWO_LAUNCH && lay.fused)
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: the workspace of this shape holds no score matrix; "
+                                        "use SK_SELECT_FILTER or SK_SELECT_AUTO");
     cudaStream_t st = (cudaStream_t)stream;
     char* ws = static_cast<char*>(p->workspace);
     float* lut = reinterpret_cast<float*>(ws + lay.lut);
@@ -439,18 +460,8 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
                           p->H, p->Hkv, p->D, p->L, p->P, p->R, nullptr, lut, stream);
         if (rc != SK_OK) return rc;
     }
-    SK_REQUIRE(p->select_path >= SK_SELECT_AUTO && p->select_path <= SK_SELECT_CLUSTER,
-               "sk_decode_step: select_path %d is not an sk_select_path", p->select_path);
-    const bool can_cluster = score_select_cluster_size(p->B, p->H, p->Hkv, p->L, p->R, p->T_max, p->M) != 0;
-    int path = p->select_path;
-    if (path == SK_SELECT_AUTO) path = lay.fused ? SK_SELECT_FILTER : (can_cluster ? SK_SELECT_CLUSTER : SK_SELECT_TWO_LAUNCH);
-    if (path == SK_SELECT_CLUSTER && !can_cluster)
-        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the one-launch scorer + select");
-    if (path == SK_SELECT_FILTER && !lay.fused)
-        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the filtering scorer + candidate select");
-    if (path == SK_SELECT_TWO_LAUNCH && lay.fused)
-        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: the workspace of this shape holds no score matrix; "
-                                        "use SK_SELECT_FILTER or SK_SELECT_AUTO");
+    // from here on every launch may start while its predecessor drains (see pdl_wait in the kernels)
+    PdlChain chain;
     if (path == SK_SELECT_CLUSTER) {
         // one launch: scores stay in shared memory, select across the cluster
         rc = launch_score_select_cluster(lut, p->codes, p->v_norm, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,

@@ -43,10 +43,43 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 __device__ __forceinline__ int effective_len(int64_t T, const int32_t* T_dev) {
     int64_t t = T;
     if (T_dev != nullptr) {
-        int64_t d = (int64_t)(*T_dev);
+        int64_t d = (int64_t)__ldcg(T_dev);   // written by a kernel this one may overlap: no cached copy
         t = d < t ? d : t;
     }
     return t < 0 ? 0 : (int)t;
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// The kernels of one decode step are chained with programmatic stream serialisation: a kernel
+// lets its successor start launching right away (launch_dependents) and the successor does its
+// set-up that needs no input, then waits (pdl_wait) until the predecessor has completed and its
+// writes are visible before it touches anything the predecessor produces.  Both instructions do
+// nothing in a kernel that was launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Host side: true while sk_decode_step chains its launches (thread-local); launch_chained() adds
+// the attribute exactly then.
+bool pdl_chain_active();
+struct PdlChain {
+    PdlChain();
+    ~PdlChain();
+};
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    const bool chained = pdl_chain_active();
+    cfg.attrs = chained ? &attr : nullptr;
+    cfg.numAttrs = chained ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 // ---------------------------------------------------------------- shared-memory histograms

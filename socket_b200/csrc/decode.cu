@@ -119,9 +119,19 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
     const int kvh = h / (H / Hkv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hw = tid >> 4, hw2 = lane >> 4, hl = tid & 15;
+    pdl_launch_dependents();
+
+    // the query is an input of the whole step, so it can be fetched before the list exists
+    float qf[8];
+    cvt8(q + (size_t)row * DEC_D + hl * 8, qf);
+    const float qscale = rsqrtf((float)DEC_D) * LOG2E;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qf[i] *= qscale;
+
+    pdl_wait();                               // list, list_len, the live length and the newest K/V row
     const int Teff = effective_len(T, T_dev);
 
-    int len = list_len[row];
+    int len = __ldcg(list_len + row);
     if (len > max_len) len = (int)max_len;
     const int chunk = (int)((max_len + splits - 1) / splits);
     const int c0 = split * chunk;
@@ -131,12 +141,6 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
     const int w0 = c0 + warp * per_warp;
     const int w1 = min(c1, w0 + per_warp);
     const int n_stage = w1 > w0 ? (w1 - w0 + DEC_G - 1) / DEC_G : 0;
-
-    float qf[8];
-    cvt8(q + (size_t)row * DEC_D + hl * 8, qf);
-    const float qscale = rsqrtf((float)DEC_D) * LOG2E;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) qf[i] *= qscale;
 
     const KT* kb = k_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs;
     const KT* vb = v_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs;
@@ -150,7 +154,7 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
         const int e = w0 + batch * 32 + lane;
         int idx = -1;
         if (e < w1) {
-            idx = __ldg(lst + e);
+            idx = __ldcg(lst + e);
             if (idx >= Teff) {
                 bad_index = true;
                 idx = -1;
@@ -312,9 +316,10 @@ int decode_launch(dim3 grid, cudaStream_t st, const void* q, const void* k_cache
         if (e != cudaSuccess)
             return fail(SK_ERR_CUDA, "sparse_decode_kernel smem attribute: %s", cudaGetErrorString(e));
     }
-    kern<<<grid, DEC_THREADS, smem, st>>>((const QT*)q, (const KT*)k_cache, (const KT*)v_cache, kv_bs,
-                                          kv_hs, kv_rs, list, list_rs, list_len, max_list_len, (QT*)out,
-                                          H, Hkv, T, T_dev, tickets, ws_ml, ws_acc, status);
+    cudaError_t e = launch_chained(kern, grid, dim3(DEC_THREADS), (size_t)smem, st, (const QT*)q, (const KT*)k_cache,
+                                   (const KT*)v_cache, kv_bs, kv_hs, kv_rs, list, list_rs, list_len, max_list_len,
+                                   (QT*)out, H, Hkv, T, T_dev, tickets, ws_ml, ws_acc, status);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "sparse_decode_kernel: %s", cudaGetErrorString(e));
     return check_launch("sparse_decode_kernel");
 }
 

@@ -19,6 +19,7 @@ decode_prologue_kernel(const T* __restrict__ q, const T* __restrict__ k_new, con
                        int Hkv, int64_t Tcap, int L, int P, int R, int ht, int append_gx, int append_gy,
                        int sh_gx) {
     extern __shared__ __align__(16) float pro_smem[];
+    pdl_launch_dependents();
     const int n_append = append_gx * append_gy;
     if ((int)blockIdx.x < n_append) {
         const int bx = blockIdx.x % append_gx, by = blockIdx.x / append_gx;

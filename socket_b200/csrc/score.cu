@@ -148,11 +148,13 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rep = H / Hkv;
     const int tiles = rep / HT;
-    const int Teff = effective_len(T, T_dev);
     const uint32_t lut_bytes = (uint32_t)R * CODE_STRIDE;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) mbar_init(bar, 1);
     __syncthreads();
+    pdl_wait();                                // the table, the live length and the newest codes come from the predecessor
+    const int Teff = effective_len(T, T_dev);
 
     const int64_t total = (int64_t)n_groups * Tslots;
     int64_t slot = (int64_t)blockIdx.x * slots_per_cta;
@@ -219,11 +221,11 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         int t = ws + lane;
         if (t < we) {
 #pragma unroll
-            for (int i = 0; i < NV; ++i) cur[i] = __ldg(cg + (size_t)t * NV + i);
+            for (int i = 0; i < NV; ++i) cur[i] = __ldcg(cg + (size_t)t * NV + i);
         }
         if (t + 32 < we) {
 #pragma unroll
-            for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (size_t)(t + 32) * NV + i);
+            for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cg + (size_t)(t + 32) * NV + i);
         }
 
         const bool ok = mbar_wait(bar, phase);
@@ -250,7 +252,7 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             if (valid) {
                 float acc[HT];
                 score_key<L, HT>(cur, lut_s, sel_lo, sel_hi, mL, acc);
-                const float vn = __half2float(vg[t]);
+                const float vn = __half2float(__ldcg(vg + t));
 #pragma unroll
                 for (int j = 0; j < HT; ++j) sv[j] = acc[j] * vn;
             } else {
@@ -284,7 +286,7 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
             if (t + 32 < we) {
 #pragma unroll
-                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (size_t)(t + 32) * NV + i);
+                for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cg + (size_t)(t + 32) * NV + i);
             }
         }
         for (; t - lane < we; t += 32) {
@@ -293,7 +295,7 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             if (valid) {
                 float acc[HT];
                 score_key<L, HT>(cur, lut_s, sel_lo, sel_hi, mL, acc);
-                const float vn = __half2float(vg[t]);
+                const float vn = __half2float(__ldcg(vg + t));
 #pragma unroll
                 for (int j = 0; j < HT; ++j) sv[j] = acc[j] * vn;
             }
@@ -323,7 +325,7 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
             if (t + 64 < we) {
 #pragma unroll
-                for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cg + (size_t)(t + 64) * NV + i);
+                for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cg + (size_t)(t + 64) * NV + i);
             }
         }
         if (FILTER && lane == 0) {
@@ -374,9 +376,10 @@ int score_launch(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
     auto kern = score_kernel<L, HT, FILTER>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "score_kernel smem attribute: %s", cudaGetErrorString(e));
-    kern<<<(unsigned)plan.grid, SC_THREADS, smem, st>>>(lut, codes, (const __half*)v_norm, allowed, scores,
+    e = launch_chained(kern, dim3((unsigned)plan.grid), dim3(SC_THREADS), smem, st, lut, codes, (const __half*)v_norm, allowed, scores,
                                                         srs, H, Hkv, R, T, T_dev, Tcap, plan.Tslots,
                                                         plan.per_cta, n_groups, status, fa);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "score_kernel: %s", cudaGetErrorString(e));
     return check_launch("score_kernel");
 }
 

@@ -126,6 +126,8 @@ score_select_cluster_kernel(ClusterArgs a) {
     const int b = bk / a.Hkv, kvh = bk - b * a.Hkv;
     const size_t row0 = (size_t)b * a.H + kvh * rep + tile * CS_HT;
 
+    pdl_launch_dependents();
+    pdl_wait();                               // the table, the live length and the newest codes come from the predecessor
     const int T = effective_len(a.T, a.T_dev);
     if (T <= 0) {   // uniform over the grid
         if (rank == 0 && tid < CS_HT) a.list_len[row0 + tid] = 0;
@@ -192,13 +194,13 @@ score_select_cluster_kernel(ClusterArgs a) {
     float vcur = 0.f, vnxt = 0.f;
     if (live(0)) {
 #pragma unroll
-        for (int i = 0; i < NV; ++i) cur[i] = __ldg(cgp + (size_t)(t_lo + local_of(0)) * NV + i);
-        vcur = __half2float(vg[t_lo + local_of(0)]);
+        for (int i = 0; i < NV; ++i) cur[i] = __ldcg(cgp + (size_t)(t_lo + local_of(0)) * NV + i);
+        vcur = __half2float(__ldcg(vg + t_lo + local_of(0)));
     }
     if (live(1)) {
 #pragma unroll
-        for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cgp + (size_t)(t_lo + local_of(1)) * NV + i);
-        vnxt = __half2float(vg[t_lo + local_of(1)]);
+        for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cgp + (size_t)(t_lo + local_of(1)) * NV + i);
+        vnxt = __half2float(__ldcg(vg + t_lo + local_of(1)));
     }
     const bool ok = mbar_wait(bar, 0);
     if (!__syncthreads_and(ok)) {
@@ -228,8 +230,8 @@ score_select_cluster_kernel(ClusterArgs a) {
         vcur = vnxt;
         if (live(k + 2)) {
 #pragma unroll
-            for (int i = 0; i < NV; ++i) nxt[i] = __ldg(cgp + (size_t)(t_lo + local_of(k + 2)) * NV + i);
-            vnxt = __half2float(vg[t_lo + local_of(k + 2)]);
+            for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cgp + (size_t)(t_lo + local_of(k + 2)) * NV + i);
+            vnxt = __half2float(__ldcg(vg + t_lo + local_of(k + 2)));
         }
     }
     // shared-memory slot of (k, lane): conflict free, 32 * iters slots per warp

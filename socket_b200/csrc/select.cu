@@ -189,12 +189,12 @@ __device__ __forceinline__ void load_scores(const float* __restrict__ sc, int t0
     if (vec && t0 + N <= T) {
 #pragma unroll
         for (int v = 0; v < N / 4; ++v) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(sc + t0) + v);
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(sc + t0) + v);
             f[4 * v] = a.x; f[4 * v + 1] = a.y; f[4 * v + 2] = a.z; f[4 * v + 3] = a.w;
         }
     } else {
 #pragma unroll
-        for (int j = 0; j < N; ++j) f[j] = (t0 + j < T) ? __ldg(sc + t0 + j) : 0.f;
+        for (int j = 0; j < N; ++j) f[j] = (t0 + j < T) ? __ldcg(sc + t0 + j) : 0.f;
     }
 }
 
@@ -627,6 +627,8 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
     SelShared& s = *reinterpret_cast<SelShared*>(smem_raw);
     const int tid = threadIdx.x;
     const int64_t row = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const float* sc = scores + row * score_row_stride;
     const uint8_t* al = allowed ? allowed + row * T_host : nullptr;
     int32_t* out = list + row * list_row_stride;
@@ -678,6 +680,22 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t row = blockIdx.x;
     int32_t* out = list + row * list_row_stride;
+
+    // which scorer chunks belong to this row's KV-head group
+    const int rep = a.H / a.Hkv, tiles = rep / a.ht;
+    const int b = (int)(row / a.H), h = (int)(row - (int64_t)b * a.H);
+    const int kvh = h / rep, hj = h - kvh * rep;
+    const int g = (b * a.Hkv + kvh) * tiles + hj / a.ht;
+    const int64_t first_cta = ((int64_t)g * a.Tslots) / a.per_cta;
+    const int64_t last_cta = ((int64_t)(g + 1) * a.Tslots - 1) / a.per_cta;
+    const int n_runs = (int)(last_cta - first_cta + 1) * SC_WARPS;      // <= 1024
+    const int32_t* cnt = a.cnt + row * a.chunks_max * SC_WARPS;
+    pdl_launch_dependents();
+    pdl_wait();                               // the runs, their lengths and the cuts come from the scorer
+    // run length and chunk cut of this thread: issued before anything waits on the live length
+    const int c_run = tid < n_runs ? __ldcg(cnt + tid) : 0;
+    const float cut_chunk = tid < n_runs / SC_WARPS ? __ldcg(a.cut + row * a.chunks_max + tid) : -INFINITY;
+
     const int T = effective_len(T_host, T_dev);
     Scan scan;
     if (T <= 0) {
@@ -690,16 +708,6 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
     int32_t* heavy = out + nb;
     float* sc = a.scratch + row * a.score_stride;
 
-    // which scorer chunks belong to this row's KV-head group
-    const int rep = a.H / a.Hkv, tiles = rep / a.ht;
-    const int b = (int)(row / a.H), h = (int)(row - (int64_t)b * a.H);
-    const int kvh = h / rep, hj = h - kvh * rep;
-    const int g = (b * a.Hkv + kvh) * tiles + hj / a.ht;
-    const int64_t first_cta = ((int64_t)g * a.Tslots) / a.per_cta;
-    const int64_t last_cta = ((int64_t)(g + 1) * a.Tslots - 1) / a.per_cta;
-    const int n_runs = (int)(last_cta - first_cta + 1) * SC_WARPS;      // <= 1024
-    const int32_t* cnt = a.cnt + row * a.chunks_max * SC_WARPS;
-
     bool exact = false;
     if (Me > 0 && Me < T) {
         // ---- run lengths -> offsets (one run per thread), largest cut, overflow flag
@@ -709,10 +717,9 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
         }
         for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
         __syncthreads();
-        int c = 0;
-        if (tid < n_runs) c = cnt[tid];
+        const int c = c_run;
         if (c > a.cap_w) s.thr_bin = 1;
-        if (tid < n_runs / SC_WARPS) atomicMax(&s.red_hi[0], order_key(a.cut[row * a.chunks_max + tid]));
+        if (tid < n_runs / SC_WARPS) atomicMax(&s.red_hi[0], order_key(cut_chunk));
         int total;
         const int off = scan.excl(c, total, s);        // two barriers: the flags above are visible after it
         const bool any_over = s.thr_bin != 0;
@@ -727,18 +734,32 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                 if (tid < n_runs) run_off[tid] = off;
                 __syncthreads();
                 const uint2* cand = a.cand + row * a.chunks_max * SC_WARPS * a.cap_w;
-                for (int i = tid; i < total; i += SEL_THREADS) {
-                    int lo = 0, hi = n_runs - 1;                  // last run with run_off <= i
-                    while (lo < hi) {
-                        const int mid = (lo + hi + 1) >> 1;
-                        if (run_off[mid] <= i) lo = mid; else hi = mid - 1;
+                // four candidates per thread and pass: the searches first, then the four loads in
+                // flight together
+                for (int base = 0; base < total; base += 4 * SEL_THREADS) {
+                    uint2 e[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int i = base + u * SEL_THREADS + tid;
+                        int lo = 0, hi = n_runs - 1;              // last run with run_off <= i
+                        while (lo < hi) {
+                            const int mid = (lo + hi + 1) >> 1;
+                            if (run_off[mid] <= i) lo = mid; else hi = mid - 1;
+                        }
+                        e[u] = make_uint2(0u, 0u);
+                        if (i < total) e[u] = __ldcg(cand + (size_t)lo * a.cap_w + (i - run_off[lo]));
                     }
-                    const uint2 e = __ldg(cand + (size_t)lo * a.cap_w + (i - run_off[lo]));
-                    const uint32_t k = order_key(__uint_as_float(e.x));
-                    s.cand_key[i] = k;
-                    s.cand_idx[i] = (int32_t)e.y;
-                    kmin = min(kmin, k);
-                    kmax = max(kmax, k);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int i = base + u * SEL_THREADS + tid;
+                        if (i < total) {
+                            const uint32_t k = order_key(__uint_as_float(e[u].x));
+                            s.cand_key[i] = k;
+                            s.cand_idx[i] = (int32_t)e[u].y;
+                            kmin = min(kmin, k);
+                            kmax = max(kmax, k);
+                        }
+                    }
                 }
             } else {
                 // nearly full buffer: one warp per run
@@ -752,7 +773,7 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                     const int o = (int)s.hist[2 * r], n = (int)s.hist[2 * r + 1];
                     const uint2* src = cand + (size_t)r * a.cap_w;
                     for (int i = lane; i < n; i += 32) {
-                        const uint2 e = __ldg(src + i);
+                        const uint2 e = __ldcg(src + i);
                         const uint32_t k = order_key(__uint_as_float(e.x));
                         s.cand_key[o + i] = k;
                         s.cand_idx[o + i] = (int32_t)e.y;
@@ -780,7 +801,7 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
             const int j = hj % a.ht;
             for (int i = tid; i < a.L * a.R; i += SEL_THREADS) {
                 const int l = i / a.R, r = i - l * a.R;
-                tab[i] = lut_g[((size_t)r * a.L + l) * a.ht + j];
+                tab[i] = __ldcg(lut_g + ((size_t)r * a.L + l) * a.ht + j);
             }
             __syncthreads();
             const uint8_t* cg = a.codes + (size_t)(b * a.Hkv + kvh) * a.Tcap * a.L;
@@ -789,13 +810,13 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                 const uint4* cp = reinterpret_cast<const uint4*>(cg + (size_t)t * a.L);
                 float sum = 0.f;
                 for (int v = 0; v < a.L / 16; ++v) {
-                    const uint4 w4 = __ldg(cp + v);
+                    const uint4 w4 = __ldcg(cp + v);
                     const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                     for (int q = 0; q < 16; ++q)
                         sum += tab[(v * 16 + q) * a.R + ((w[q >> 2] >> (8 * (q & 3))) & 0xffu)];
                 }
-                sc[t] = sum * __half2float(vg[t]);
+                sc[t] = sum * __half2float(__ldcg(vg + t));
             }
             __syncthreads();
             select_row(s, scan, sc, T, Me, heavy);
@@ -822,6 +843,7 @@ int launch_select_list(const float* scores, int64_t score_row_stride, const uint
     cudaError_t e = cudaFuncSetAttribute(select_list_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "select_list_kernel smem attribute: %s", cudaGetErrorString(e));
+    // not chained to its predecessor: this kernel reads the score matrix through the read-only cache
     select_list_kernel<<<(unsigned)rows, SEL_THREADS, smem, st>>>(
         scores, score_row_stride, allowed, T, T_dev, M, sink, window, sorted, list, list_row_stride,
         list_len);
@@ -861,8 +883,9 @@ int launch_select_candidates(const float* lut, const uint8_t* codes, const uint1
     cudaError_t e = cudaFuncSetAttribute(select_cand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "select_cand_kernel smem attribute: %s", cudaGetErrorString(e));
-    select_cand_kernel<<<(unsigned)rows, SEL_THREADS, smem, st>>>(a, T, T_dev, M, sink, window, sorted, list,
-                                                                 list_row_stride, list_len);
+    e = launch_chained(select_cand_kernel, dim3((unsigned)rows), dim3(SEL_THREADS), smem, st, a, T, T_dev, M, sink,
+                       window, sorted, list, list_row_stride, list_len);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "select_cand_kernel: %s", cudaGetErrorString(e));
     return check_launch("select_cand_kernel");
 }
 

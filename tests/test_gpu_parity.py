@@ -351,6 +351,54 @@ def test_model_flow_decode_step_matches_reference():
     assert int(step.status) == 0
 
 
+def test_graph_replayed_steps_see_the_newest_token():
+    """The step's kernels are chained so that each may start while its predecessor drains.  Replayed
+    from a CUDA graph they do overlap, and every replay must still score and attend over the token
+    its own first kernel appended: compare each replay with separate, unchained calls."""
+    B, H, Hkv, T, M, sink, window = 2, 8, 2, 5000, 128, 8, 24
+    inp = make_decode_inputs(B, H, Hkv, T + 4, seed=33, dtype=torch.bfloat16)
+    k_bshd = cu(inp.k.permute(0, 2, 1, 3).contiguous())
+    v_bshd = cu(inp.v.permute(0, 2, 1, 3).contiguous())
+    attn = SocketAttention(H, Hkv, 128, heavy_const=M, sink_size=sink, window_size=window,
+                           planes=inp.planes, protos_T=inp.protos_T, dtype=torch.bfloat16, device=DEV)
+    cache = attn.setup_cache(B, T + 64, dtype=torch.bfloat16)
+    cache.append(torch.arange(T, device=DEV), k_bshd[:, :T].contiguous(), v_bshd[:, :T].contiguous(), attn.planes)
+    q = cu(inp.q)
+    kn = torch.empty(B, 1, Hkv, 128, dtype=torch.bfloat16, device=DEV)
+    vn = torch.empty_like(kn)
+    pos = torch.zeros(1, dtype=torch.int64, device=DEV)
+    out = torch.empty_like(q)
+    step = ops.DecodeStep(cache, q, kn, vn, pos, attn.planes, attn.protos_T, out, topk=M, sink=sink,
+                          window=window, T_max=T + 64, keep_list=True)
+    kn.copy_(k_bshd[:, T:T + 1]); vn.copy_(v_bshd[:, T:T + 1]); pos.fill_(T)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        step.run()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step.run()
+    for i in range(4):
+        kn.copy_(k_bshd[:, T + i:T + i + 1]); vn.copy_(v_bshd[:, T + i:T + i + 1]); pos.fill_(T + i)
+        q.copy_(cu(inp.q) * (1.0 + 0.25 * i))                      # a different table every replay
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        Tn = T + i + 1
+        assert int(step.status) == 0 and int(cache.prefill_len) == Tn
+        _, lut = ops.soft_hash(q, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv, want_probs=False, want_lut=True)
+        sc = ops.score(lut, cache.k_hard, cache.v_norm, H, Tn)
+        lst, ln = ops.select_list(sc, Tn, M, sink, window)
+        ref = ops.sparse_decode(q, cache.k_cache, cache.v_cache, lst, ln, T=Tn)
+        ktot = lst.shape[-1]
+        assert torch.equal(step.list_len, ln)
+        assert torch.equal(torch.sort(step.list[:, :, :ktot], -1).values, torch.sort(lst, -1).values), i
+        assert (lst == Tn - 1).any(dim=-1).all()                   # the window holds the newest token
+        got = ops.sparse_decode(q, cache.k_cache, cache.v_cache, step.list[:, :, :ktot].contiguous(),
+                                step.list_len, T=Tn)
+        assert torch.equal(out, got), i
+
+
 def test_host_decoder_equals_device_path():
     """The host-memory entry (pinned staging -> graph of copy, step, copy back) gives the same
     bits as the device-tensor call on the same cache, and advances the cache the same way."""
