@@ -549,7 +549,7 @@ def finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, roofline,
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "higher_is_better": True,
             "scaling": args.shard, "vs_baseline": None, "dtype": cfg.kv_dtype, "data": "synthetic",
-            "config": workload_config(args, cfg, world), "roofline": roofline, "stages": stages,
+            "config": workload_config(args, cfg_full, world), "roofline": roofline, "stages": stages,
             "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": clocks,
             "gpu_launches": K * step.n_launches,
         }
