@@ -1,8 +1,8 @@
 // GQA sparse flash-decode: exact softmax attention of one query per head over the K/V rows
 // named by that head's sparse list, read in place from the KV cache.
 //
-// Work split: grid (splits, B*H), sized so that every CTA is resident at once.  A CTA owns a
-// contiguous slice of one row's list, each of its 4 warps a contiguous part of that slice.
+// Work split: grid (splits, B*H), sized so that every CTA is resident at once (two per SM).  A CTA owns a
+// contiguous slice of one row's list, each of its 8 warps a contiguous part of that slice.
 // A warp streams its rows through a private two-stage ring in shared memory with 16-byte
 // asynchronous copies (cp.async): a stage is 8 list entries = 8 K rows + 8 V rows (4 KiB for
 // bf16), the next stage is in flight while the current one is consumed, and the list indices
@@ -24,7 +24,7 @@ static __device__ __align__(256) unsigned char g_static_decode_scratch[SK_SPARSE
 namespace sk {
 namespace {
 
-constexpr int DEC_THREADS = 128;
+constexpr int DEC_THREADS = 256;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int DEC_HW = DEC_THREADS / 16;   // half-warps per CTA
 constexpr int DEC_G = 8;                   // list entries per stage and warp
@@ -41,8 +41,12 @@ constexpr int64_t DEC_MAX_ROWS = 65536;
 constexpr size_t DEC_TICKET_BYTES = DEC_MAX_ROWS * sizeof(int32_t);
 
 inline int decode_splits(int64_t rows, int64_t max_len) {
-    int64_t s = (148 * 6) / rows;                       // all CTAs resident: <= 6 per SM
-    const int64_t cap = (max_len + 31) / 32;            // at least 8 entries per warp
+    // Few fat CTAs rather than many thin ones: the block scheduler starts roughly 150 CTAs per
+    // microsecond, so a grid of 900 small CTAs spends more time ramping up than gathering.
+    int64_t s = (148 * 2) / rows;                       // all CTAs resident: 2 per SM
+    // long lists are bandwidth work: a third CTA per SM keeps more rows in flight
+    if (s >= 1 && max_len / s > 64 * DEC_WARPS) s = (148 * 3) / rows;
+    const int64_t cap = (max_len + DEC_G * DEC_WARPS - 1) / (DEC_G * DEC_WARPS);   // at least one stage per warp
     if (s > cap) s = cap;
     if (s < 1) s = 1;
     if (s > 256) s = 256;
@@ -129,22 +133,28 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
     for (int i = 0; i < 8; ++i) qf[i] *= qscale;
 
     pdl_wait();                               // list, list_len, the live length and the newest K/V row
-    const int Teff = effective_len(T, T_dev);
-
-    int len = __ldcg(list_len + row);
-    if (len > max_len) len = (int)max_len;
+    // The slice bounds come from max_len alone, so the first two index batches are requested
+    // together with the row's length and the live length (the list row has max_len slots; entries
+    // at or beyond the length are masked once it has arrived).
     const int chunk = (int)((max_len + splits - 1) / splits);
     const int c0 = split * chunk;
-    const int c1 = min(len, c0 + chunk);
-    // this warp's part of the slice, a multiple of the stage size
     const int per_warp = ((chunk + DEC_WARPS - 1) / DEC_WARPS + DEC_G - 1) / DEC_G * DEC_G;
     const int w0 = c0 + warp * per_warp;
+    const int w1_cap = (int)min((int64_t)min(c0 + chunk, w0 + per_warp), max_len);
+    const int32_t* lst = list + (size_t)row * list_rs;
+    int raw0 = -1, raw1 = -1;
+    if (w0 + lane < w1_cap) raw0 = __ldcg(lst + w0 + lane);
+    if (w0 + 32 + lane < w1_cap) raw1 = __ldcg(lst + w0 + 32 + lane);
+    int len = __ldcg(list_len + row);         // requested before the live length is consumed
+    const int Teff = effective_len(T, T_dev);
+    if (len > max_len) len = (int)max_len;
+    const int c1 = min(len, c0 + chunk);
+    // this warp's part of the slice, a multiple of the stage size
     const int w1 = min(c1, w0 + per_warp);
     const int n_stage = w1 > w0 ? (w1 - w0 + DEC_G - 1) / DEC_G : 0;
 
     const KT* kb = k_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs;
     const KT* vb = v_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs;
-    const int32_t* lst = list + (size_t)row * list_rs;
     char* ring = smem + (size_t)warp * DEC_STAGES * S::STAGE;
     int32_t* sidx = sidx_all + warp * DEC_STAGES * DEC_G;
     bool bad_index = false;
@@ -162,7 +172,16 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
         }
         return idx;
     };
-    int idx0 = load_batch(0), idx1 = load_batch(1);
+    auto check_batch = [&](int batch, int raw) -> int {   // the same validation for a batch fetched early
+        const int e = w0 + batch * 32 + lane;
+        if (e >= w1) return -1;
+        if (raw >= Teff) {
+            bad_index = true;
+            return -1;
+        }
+        return raw;
+    };
+    int idx0 = check_batch(0, raw0), idx1 = check_batch(1, raw1);
 
     auto issue = [&](int s) {
         if (s < n_stage) {
@@ -259,7 +278,7 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc_s[hw * DEC_D + hl * 8 + i] = acc[i];
     __syncthreads();
-    {
+    if (tid < DEC_D) {                     // one output element per thread
         float mm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < DEC_HW; ++w) mm = fmaxf(mm, m_s[w]);
@@ -287,17 +306,22 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
         *is_last = (t == splits - 1);
     }
     __syncthreads();
-    if (!*is_last) return;
+    if (!*is_last || tid >= DEC_D) return;
     __threadfence();
-    float mm = -INFINITY;
-    for (int i = 0; i < splits; ++i) mm = fmaxf(mm, __ldcg(ws_ml + ((size_t)row * splits + i) * 2));
-    float ll = 0.f, a = 0.f;
-    if (mm > -INFINITY) {
-        for (int i = 0; i < splits; ++i) {
-            const size_t slot = (size_t)row * splits + i;
-            const float f = exp2f(__ldcg(ws_ml + slot * 2) - mm);
-            ll += __ldcg(ws_ml + slot * 2 + 1) * f;
-            a += __ldcg(ws_acc + slot * DEC_D + tid) * f;
+    // one pass, all loads independent of each other: running maximum with rescaling, splits in
+    // ascending order (so the result does not depend on which CTA came last)
+    float mm = -INFINITY, ll = 0.f, a = 0.f;
+#pragma unroll 4
+    for (int i = 0; i < splits; ++i) {
+        const size_t slot = (size_t)row * splits + i;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(ws_ml + slot * 2));
+        const float av = __ldcg(ws_acc + slot * DEC_D + tid);
+        if (ml.x > -INFINITY) {
+            const float mn = fmaxf(mm, ml.x);
+            const float fo = exp2f(mm - mn), fn = exp2f(ml.x - mn);
+            ll = ll * fo + ml.y * fn;
+            a = a * fo + av * fn;
+            mm = mn;
         }
     }
     out[(size_t)row * DEC_D + tid] = from_f32<QT>(ll > 0.f ? a / ll : 0.f);

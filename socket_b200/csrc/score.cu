@@ -154,12 +154,24 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
     if (threadIdx.x == 0) mbar_init(bar, 1);
     __syncthreads();
     pdl_wait();                                // the table, the live length and the newest codes come from the predecessor
-    const int Teff = effective_len(T, T_dev);
 
     const int64_t total = (int64_t)n_groups * Tslots;
     int64_t slot = (int64_t)blockIdx.x * slots_per_cta;
     const int64_t slot_end = min(slot + slots_per_cta, total);
     uint32_t phase = 0;
+    auto request_table = [&](int g) {          // one thread: bulk copies of group g's table, completing on `bar`
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(bar, lut_bytes);
+        const char* src = reinterpret_cast<const char*>(lut) + (size_t)g * lut_bytes;
+        for (uint32_t off = 0; off < lut_bytes; off += SC_COPY_CHUNK) {
+            const uint32_t n = min((uint32_t)SC_COPY_CHUNK, lut_bytes - off);
+            bulk_g2s(lut_s + off, src + off, n, bar);
+        }
+    };
+    // the table of the first segment is requested before the live length has arrived
+    bool in_flight = slot < slot_end;
+    if (in_flight && threadIdx.x == 0) request_table((int)(slot / Tslots));
+    const int Teff = effective_len(T, T_dev);
 
     while (slot < slot_end) {
         const int g = (int)(slot / Tslots);
@@ -185,20 +197,24 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
                 }
                 if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
             }
+            if (in_flight) {   // its table was requested all the same: let the copy land before the barrier is reused
+                const bool landed = mbar_wait(bar, phase);
+                phase ^= 1u;
+                in_flight = false;
+                if (!__syncthreads_and(landed)) {
+                    if (threadIdx.x == 0 && status != nullptr) atomicOr(status, SK_DEV_WAIT_TIMEOUT);
+                    return;
+                }
+            }
             continue;
         }
 
-        // previous segment's lookups are done before the table is overwritten
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(bar, lut_bytes);
-            const char* src = reinterpret_cast<const char*>(lut) + (size_t)g * lut_bytes;
-            for (uint32_t off = 0; off < lut_bytes; off += SC_COPY_CHUNK) {
-                const uint32_t n = min((uint32_t)SC_COPY_CHUNK, lut_bytes - off);
-                bulk_g2s(lut_s + off, src + off, n, bar);
-            }
+        if (!in_flight) {
+            // previous segment's lookups are done before the table is overwritten
+            __syncthreads();
+            if (threadIdx.x == 0) request_table(g);
         }
+        in_flight = false;
         if (FILTER) {
             for (int i = threadIdx.x; i < 4 * 256; i += SC_THREADS) (&fs.hist[0][0])[i] = 0;
         }
