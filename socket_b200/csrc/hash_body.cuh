@@ -133,11 +133,30 @@ __device__ __forceinline__ void kv_append_body(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t N = (int64_t)B * S * Hkv;
     const int l = l0 + warp;
-    // the plane loads do not depend on anything: issue them first, so that they overlap the
-    // input_pos -> key dependent loads below
-    double pd[8][EPL];
+    // Every global load is issued before the first one is consumed, so the append costs one memory
+    // round trip: the new K rows and this warp's V row (their addresses do not depend on
+    // input_pos), the positions, and the planes.
     const bool fast = (P == 8) && (l < L);
+    const bool mover = l0 == 0 && warp < HASH_ROWS && n0 + warp < N;      // warp r moves row r
+    KT kraw[HASH_ROWS][EPL], vraw[EPL];
+    int64_t posv[HASH_ROWS];
+#pragma unroll
+    for (int r = 0; r < HASH_ROWS; ++r) {
+        const int64_t n = n0 + r;
+        posv[r] = -1;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) kraw[r][i] = from_f32<KT>(0.f);
+        if (n < N) {
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) kraw[r][i] = k_new[n * D + lane * EPL + i];
+            posv[r] = input_pos[(int)((n / Hkv) % S)];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) vraw[i] = mover ? v_new[(n0 + warp) * D + lane * EPL + i] : from_f32<KT>(0.f);
+    double pd[8][EPL];
     if (fast) load_planes8<PT, EPL>(planes, l, lane, pd);
+
     double kd[HASH_ROWS][EPL];
     void* code_ptr[HASH_ROWS];
     int64_t cache_row[HASH_ROWS];
@@ -150,39 +169,35 @@ __device__ __forceinline__ void kv_append_body(
         for (int i = 0; i < EPL; ++i) kd[r][i] = 0.0;
         if (n < N) {
             const int kvh = (int)(n % Hkv);
-            const int s = (int)((n / Hkv) % S);
             const int b = (int)(n / ((int64_t)Hkv * S));
-            const int64_t pos = input_pos[s];
+            const int64_t pos = posv[r];
             if (pos < 0 || pos >= Tcap) {
                 if (status != nullptr && threadIdx.x == 0 && l0 == 0) atomicOr(status, SK_DEV_POS_OUT_OF_RANGE);
             } else {
                 cache_row[r] = ((int64_t)b * Hkv + kvh) * Tcap + pos;
                 code_ptr[r] = codes + cache_row[r] * L;
-                load_row_f64<KT, EPL>(k_new + n * D, lane, kd[r]);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) kd[r][i] = (double)to_f32(kraw[r][i]);
                 if (threadIdx.x == 0 && l0 == 0 && kvh == 0 && b == 0) atomicMax(prefill_len, (int32_t)(pos + 1));
             }
         }
     }
     if (fast) hash_rows_planes8<EPL>(kd, pd, code_ptr, l, 1, lane);
     else if (l < L) hash_rows_generic<PT, EPL>(kd, code_ptr, planes, l, P, 1, lane);
-    if (l0 == 0 && warp < HASH_ROWS) {
-        // warp r moves row r (static indexing of the per-row arrays)
+    if (mover) {
+        // static indexing of the per-row arrays
 #pragma unroll
         for (int r = 0; r < HASH_ROWS; ++r) {
             if (warp != r || cache_row[r] < 0) continue;
-            const int64_t n = n0 + r;
-            const KT* ks = k_new + n * D;
-            const KT* vs = v_new + n * D;
             KT* kdst = k_cache + cache_row[r] * D;
             KT* vdst = v_cache + cache_row[r] * D;
             double ss = 0.0;
 #pragma unroll
             for (int i = 0; i < EPL; ++i) {
                 const int d = lane * EPL + i;
-                kdst[d] = ks[d];
-                const KT x = vs[d];
-                vdst[d] = x;
-                const double xf = (double)to_f32(x);
+                kdst[d] = kraw[r][i];
+                vdst[d] = vraw[i];
+                const double xf = (double)to_f32(vraw[i]);
                 ss = fma(xf, xf, ss);
             }
             ss = warp_sum_f64(ss);

@@ -50,10 +50,12 @@ int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, 
     const int ht = lut_head_tile(rep);
     const int tiles = rep / ht;
     const int tpc = SH_WARPS / ht;
-    const int sh_gx = (L + tpc - 1) / tpc;
-    const int sh_total = sh_gx * B * Hkv * tiles;
     const int append_gx = (B * Hkv + HASH_ROWS - 1) / HASH_ROWS;
     const int append_gy = (L + HASH_WARPS - 1) / HASH_WARPS;
+    // (taking several table groups per CTA to fit the grid into one wave was tried: slower)
+    const int sh_gx = (L + tpc - 1) / tpc;
+    const int n_tiles = B * Hkv * tiles;
+    const int sh_total = sh_gx * n_tiles;
     const size_t smem = soft_hash_smem_bytes(P, R, ht);
     if (smem > 200 * 1024) return SK_OK;
     const float inv_t = 1.0f / temperature;

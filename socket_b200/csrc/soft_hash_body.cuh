@@ -48,7 +48,14 @@ __device__ __forceinline__ void soft_hash_body(
     float* t_s = pr_s + (size_t)P * R;            // [SH_WARPS][16]
     float* stage = t_s + SH_WARPS * 16;           // [tpc][R][ht]
 
-    // issue the plane / query loads first, then the protos copy, then reduce
+    // every global load of the CTA is issued before the first one is consumed: the protos (kept in
+    // registers until the dot products are done) together with the plane / query rows
+    const bool fast = (P == 8 && R == 256);
+    float prr[8];
+    if (fast) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) prr[i] = protos_T[threadIdx.x + i * SH_THREADS];
+    }
     float part[16];
 #pragma unroll
     for (int p = 0; p < 16; ++p) part[p] = 0.f;
@@ -77,7 +84,12 @@ __device__ __forceinline__ void soft_hash_body(
             }
         }
     }
-    for (int i = threadIdx.x; i < P * R; i += SH_THREADS) pr_s[i] = protos_T[i];
+    if (fast) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pr_s[threadIdx.x + i * SH_THREADS] = prr[i];
+    } else {
+        for (int i = threadIdx.x; i < P * R; i += SH_THREADS) pr_s[i] = protos_T[i];
+    }
     const float inv_sqrt_d = 1.0f / fmaxf(sqrtf((float)D), 1e-6f);
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
@@ -95,12 +107,26 @@ __device__ __forceinline__ void soft_hash_body(
             // 8 buckets per lane, logits kept in registers
             float lg[8];
             float mx = -INFINITY;
+            if (P == 8) {
+                float tv[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float a = 0.f;
-                for (int p = 0; p < P; ++p) a = fmaf(t[p], pr_s[p * 256 + lane + 32 * i], a);
-                lg[i] = a * inv_temperature;
-                mx = fmaxf(mx, lg[i]);
+                for (int p = 0; p < 8; ++p) tv[p] = t[p];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int p = 0; p < 8; ++p) a = fmaf(tv[p], pr_s[p * 256 + lane + 32 * i], a);   // same order as below
+                    lg[i] = a * inv_temperature;
+                    mx = fmaxf(mx, lg[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float a = 0.f;
+                    for (int p = 0; p < P; ++p) a = fmaf(t[p], pr_s[p * 256 + lane + 32 * i], a);
+                    lg[i] = a * inv_temperature;
+                    mx = fmaxf(mx, lg[i]);
+                }
             }
             mx = warp_max_f(mx);
             float se = 0.f;
