@@ -1,11 +1,12 @@
 // Bulk key hashing on the 5th-generation tensor cores (prefill: thousands of rows).
 //
 // codes = sign( K[N,128] . planes^T[128, L*P = 256] ) packed 8 planes -> one byte per table.
-// One CTA per 128-row tile of K: TMA (cp.async.bulk.tensor, 128-byte swizzle) brings the K tile
-// and the 256 plane rows into shared memory, one elected thread issues eight
-// tcgen05.mma.kind::f16 (M=128, N=256, K=16) with the fp32 accumulator in tensor memory, a
-// tcgen05.commit signals an mbarrier, and the four warps read their 32 accumulator lanes back
-// with tcgen05.ld (one row per thread), take the signs and write 32 code bytes per row.
+// Persistent CTAs, one per SM, walk the 128-row tiles of K.  The 256 plane rows stay in shared
+// memory; TMA (cp.async.bulk.tensor, 128-byte swizzle) feeds a two-stage ring of K tiles, one
+// elected thread issues eight tcgen05.mma.kind::f16 (M=128, N=256, K=16) per tile into one of two
+// fp32 accumulators in tensor memory, and eight epilogue warps read the other accumulator back
+// with tcgen05.ld (two threads per row), take the signs and write 32 code bytes per row, so
+// loading, multiplying and the epilogue of consecutive tiles overlap.
 //
 // Exactness.  bf16 x bf16 products are exact in fp32, only the accumulation rounds, so a sign
 // can be wrong only when |acc| is tiny compared with |k|.|p|.  Every projection with
@@ -26,9 +27,8 @@ constexpr int TC_D = 128;             // head dim (MMA K total)
 constexpr int TC_KHALF = 64;          // bf16 elements per 128-byte swizzle row
 constexpr uint32_t TC_A_HALF_BYTES = TC_ROWS * 128;   // 16 KiB
 constexpr uint32_t TC_B_HALF_BYTES = TC_N * 128;      // 32 KiB
-constexpr uint32_t TC_SMEM_TILES = 2 * TC_A_HALF_BYTES + 2 * TC_B_HALF_BYTES;   // 96 KiB
+constexpr uint32_t TC_PIPE_SMEM = 2 * TC_B_HALF_BYTES + 2 * 2 * TC_A_HALF_BYTES;   // planes + two K tiles: 128 KiB
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
-constexpr int TC_THREADS = 256;       // two threads per accumulator row, 128 columns each
 constexpr float TC_BAND = 1.52587890625e-05f;         // 2^-16
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -93,10 +93,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+constexpr int TC_STAGES = 2;          // K tiles in flight and accumulators in tensor memory
+constexpr int TC_NORM_WARPS = 4;      // one thread per row of the K tile
+constexpr int TC_EPI_WARPS = 16;      // four threads per accumulator row, 64 columns each
+constexpr int TC_PIPE_THREADS = 32 * (2 + TC_NORM_WARPS + TC_EPI_WARPS);   // TMA warp, MMA warp, norm warps, epilogue warps
+
 struct TcShared {
-    uint64_t tma_bar, mma_bar;
+    uint64_t b_full;                   // planes have landed (once)
+    uint64_t a_full[TC_STAGES];        // K tile of the stage has landed
+    uint64_t a_empty[TC_STAGES];       // MMAs and the norm warps are done with the stage's K tile
+    uint64_t norm_full[TC_STAGES];     // row norms of the stage's K tile are in knorm[]
+    uint64_t acc_full[TC_STAGES];      // accumulator is complete
+    uint64_t acc_empty[TC_STAGES];     // accumulator has been read back
     uint32_t tmem_base;
-    float plane_norm[TC_N + 1];       // [TC_N] = the largest norm
+    int failed;                        // some bounded wait ran out
+    float plane_norm[TC_N + 1];        // [TC_N] = the largest norm
+    float knorm[TC_STAGES][TC_ROWS];   // |k| * 1.001 of the rows of the stage's tile (inf: decide every bit exactly)
 };
 
 // ||plane_n|| * 1.001 for the 256 planes and their maximum.  One CTA of 1024 threads: warp w owns
@@ -132,30 +144,78 @@ plane_norm_kernel(const __nv_bfloat16* __restrict__ planes, float* __restrict__ 
     }
 }
 
-__global__ void __launch_bounds__(TC_THREADS)
+__device__ __forceinline__ void mbar_init_count(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+                 : "memory");
+}
+
+// The careful version of one 32-column chunk of one accumulator row (see the epilogue).
+__device__ __noinline__ uint32_t slow_chunk(uint32_t taddr, int c, int64_t row, float thr, float knorm,
+                                            const float* plane_norm_s, uint32_t* fix_count,
+                                            uint32_t* __restrict__ fix_list, uint32_t fix_cap) {
+    uint32_t r[32];
+    tmem_ld32(taddr, r);
+    uint32_t word = 0;
+#pragma unroll 1
+    for (int k = 0; k < 32; ++k) {
+        const float acc = __uint_as_float(r[k]);
+        if (acc >= 0.f) word |= 1u << (8 * (k >> 3) + 7 - (k & 7));
+        if (fabsf(acc) <= thr * plane_norm_s[c * 32 + k] && knorm > 0.f) {
+            const uint32_t slot = atomicAdd(fix_count, 1u);
+            if (slot < fix_cap) fix_list[slot] = ((uint32_t)row << 8) | (uint32_t)(c * 32 + k);
+        }
+    }
+    return word;
+}
+
+// Persistent, warp-specialised: every CTA keeps the 256 plane rows in shared memory and walks the
+// K tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Warp 0 feeds a two-stage ring of K tiles by
+// TMA, warp 1 issues the MMAs into one of two accumulators in tensor memory, warps 6-21 read the
+// other accumulator back (tcgen05.ld), take the signs, apply the near-zero test and write the code
+// bytes; warps 2-5 compute the row norms that test needs from the K tile in shared memory - so the
+// load of tile i+1, the MMAs of tile i+1 and the epilogue of tile i overlap.  Every wait is bounded; a wait that runs out
+// raises `failed`, which makes every role leave its loop, and the status flag.
+__global__ void __launch_bounds__(TC_PIPE_THREADS, 1)
 hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_p,
-               const __nv_bfloat16* __restrict__ keys, int64_t key_row_stride,
                const float* __restrict__ plane_norm, int64_t N, uint8_t* __restrict__ codes,
                int64_t code_row_stride, const int64_t* __restrict__ dst_row, uint32_t* fix_count,
                uint32_t* __restrict__ fix_list, uint32_t fix_cap, int32_t* status) {
     extern __shared__ char tc_raw[];
     __shared__ TcShared ts;
     char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
-    char* a_half[2] = {tiles, tiles + TC_A_HALF_BYTES};
-    char* b_half[2] = {tiles + 2 * TC_A_HALF_BYTES, tiles + 2 * TC_A_HALF_BYTES + TC_B_HALF_BYTES};
+    char* b_half[2] = {tiles, tiles + TC_B_HALF_BYTES};
+    char* a_base = tiles + 2 * TC_B_HALF_BYTES;                 // [stage][half][16 KiB]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int64_t row0 = (int64_t)blockIdx.x * TC_ROWS;
+    const int64_t n_tiles = (N + TC_ROWS - 1) / TC_ROWS;
+    const int64_t my_tiles = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;     // >= 1: grid <= n_tiles
 
-    for (int i = tid; i <= TC_N; i += TC_THREADS) ts.plane_norm[i] = plane_norm[i];
+    for (int i = tid; i <= TC_N; i += TC_PIPE_THREADS) ts.plane_norm[i] = plane_norm[i];
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&ts.tma_bar)));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&ts.mma_bar)));
+        mbar_init_count(&ts.b_full, 1);
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init_count(&ts.a_full[s], 1);
+            mbar_init_count(&ts.a_empty[s], 1 + TC_NORM_WARPS); // MMA commit + one arrival per norm warp
+            mbar_init_count(&ts.norm_full[s], TC_NORM_WARPS);
+            mbar_init_count(&ts.acc_full[s], 1);
+            mbar_init_count(&ts.acc_empty[s], TC_EPI_WARPS);
+        }
+        ts.failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_addr(&ts.tmem_base)),
-                     "r"((uint32_t)TC_N)
+                     "r"((uint32_t)(TC_STAGES * TC_N))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -163,88 +223,161 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = ts.tmem_base;
+    volatile int* failed = &ts.failed;
 
-    if (tid == 0) {
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(&ts.tma_bar)),
-                     "r"(TC_SMEM_TILES)
-                     : "memory");
-        tma_load_2d(a_half[0], &map_k, 0, (int)row0, &ts.tma_bar);
-        tma_load_2d(a_half[1], &map_k, TC_KHALF, (int)row0, &ts.tma_bar);
-        tma_load_2d(b_half[0], &map_p, 0, 0, &ts.tma_bar);
-        tma_load_2d(b_half[1], &map_p, TC_KHALF, 0, &ts.tma_bar);
-        if (mbar_wait_bounded(&ts.tma_bar, 0)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int k = 0; k < TC_D / 16; ++k) {
-                const int half = k >> 2, kb = k & 3;       // 16 bf16 = 32 bytes along the swizzled row
-                const uint64_t da = umma_desc_sw128(smem_addr(a_half[half]) + kb * 32);
-                const uint64_t db = umma_desc_sw128(smem_addr(b_half[half]) + kb * 32);
-                umma_bf16(tmem, da, db, k > 0 ? 1u : 0u);
-            }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                             smem_addr(&ts.mma_bar))
-                         : "memory");
-        }
-    }
-    const bool ok = mbar_wait_bounded(&ts.mma_bar, 0);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (__syncthreads_and(ok)) {
-        // ---- epilogue: warps w and w+4 share the 32 accumulator lanes 32*(w%4).., half the
-        // columns each; a thread owns one row and 128 columns = 16 tables = 16 code bytes
-        const int quad = warp & 3, chalf = warp >> 2;
-        const int64_t row = row0 + quad * 32 + lane;
-        const bool valid = row < N;
-        float knorm = 0.f;
-        if (valid) {
-            const uint4* kp = reinterpret_cast<const uint4*>(keys + row * key_row_stride);
-            float ss = 0.f;
-#pragma unroll 4
-            for (int i = 0; i < TC_D / 8; ++i) {
-                const uint4 w = __ldg(kp + i);
-                const uint32_t u[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float a = __uint_as_float(u[j] << 16), b = __uint_as_float(u[j] & 0xffff0000u);
-                    ss = fmaf(a, a, fmaf(b, b, ss));
+    if (warp == 0) {
+        // ---- TMA producer
+        if (lane == 0) {
+            mbar_expect(&ts.b_full, 2 * TC_B_HALF_BYTES);
+            tma_load_2d(b_half[0], &map_p, 0, 0, &ts.b_full);
+            tma_load_2d(b_half[1], &map_p, TC_KHALF, 0, &ts.b_full);
+            for (int64_t i = 0; i < my_tiles && !*failed; ++i) {
+                const int s = (int)(i & 1);
+                if (i >= TC_STAGES && !mbar_wait_bounded(&ts.a_empty[s], (uint32_t)(((i >> 1) - 1) & 1))) {
+                    *failed = 1;
+                    break;
                 }
+                const int row0 = (int)((blockIdx.x + i * gridDim.x) * TC_ROWS);
+                char* a = a_base + (size_t)s * 2 * TC_A_HALF_BYTES;
+                mbar_expect(&ts.a_full[s], 2 * TC_A_HALF_BYTES);
+                tma_load_2d(a, &map_k, 0, row0, &ts.a_full[s]);
+                tma_load_2d(a + TC_A_HALF_BYTES, &map_k, TC_KHALF, row0, &ts.a_full[s]);
             }
-            knorm = sqrtf(ss) * 1.001f;
         }
-        const float thr = TC_BAND * knorm;
-        const float thr_max = valid ? thr * ts.plane_norm[TC_N] : -1.f;      // cheap first test, exact test inside
-        uint32_t words[4];
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            if (!mbar_wait_bounded(&ts.b_full, 0)) *failed = 1;
+            for (int64_t i = 0; i < my_tiles && !*failed; ++i) {
+                const int s = (int)(i & 1);
+                const uint32_t par = (uint32_t)((i >> 1) & 1);
+                if (!mbar_wait_bounded(&ts.a_full[s], par) ||
+                    (i >= TC_STAGES && !mbar_wait_bounded(&ts.acc_empty[s], par ^ 1u))) {
+                    *failed = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_addr(a_base + (size_t)s * 2 * TC_A_HALF_BYTES);
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-            const int c = chalf * 4 + c4;
-            uint32_t r[32];
-            tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + c * 32, r);
-            uint32_t word = 0;
+                for (int k = 0; k < TC_D / 16; ++k) {
+                    const int half = k >> 2, kb = k & 3;           // 16 bf16 = 32 bytes along the swizzled row
+                    const uint64_t da = umma_desc_sw128(a_addr + half * TC_A_HALF_BYTES + kb * 32);
+                    const uint64_t db = umma_desc_sw128(smem_addr(b_half[half]) + kb * 32);
+                    umma_bf16(tmem + (uint32_t)s * TC_N, da, db, k > 0 ? 1u : 0u);
+                }
+                umma_commit(&ts.acc_full[s]);                       // accumulator complete ...
+                umma_commit(&ts.a_empty[s]);                        // ... and the K tile no longer read by the MMAs
+            }
+        }
+    } else if (warp < 2 + TC_NORM_WARPS) {
+        // ---- row norms: one thread per row of the K tile, read from the swizzled tile in shared memory
+        // (16-byte chunk c of row r sits at chunk c ^ (r & 7))
+        const int r_in_tile = (warp - 2) * 32 + lane;
+        for (int64_t i = 0; i < my_tiles; ++i) {
+            if (__any_sync(FULL, *failed != 0)) break;                 // warp-uniform
+            const int s = (int)(i & 1);
+            const uint32_t par = (uint32_t)((i >> 1) & 1);
+            // the tile has landed, and the epilogue of the tile before last has read its norms
+            if (!__all_sync(FULL, mbar_wait_bounded(&ts.a_full[s], par)) ||
+                (i >= TC_STAGES && !__all_sync(FULL, mbar_wait_bounded(&ts.acc_empty[s], par ^ 1u)))) {
+                *failed = 1;
+                break;
+            }
+            float ss = 0.f;
+            const char* a = a_base + (size_t)s * 2 * TC_A_HALF_BYTES + (size_t)r_in_tile * 128;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float a = __uint_as_float(r[i]);
-                if (a >= 0.f) word |= 1u << (8 * (i >> 3) + 7 - (i & 7));
-                if (fabsf(a) <= thr_max) {
-                    if (fabsf(a) <= thr * ts.plane_norm[c * 32 + i] && knorm > 0.f) {
-                        const uint32_t slot = atomicAdd(fix_count, 1u);
-                        if (slot < fix_cap) fix_list[slot] = ((uint32_t)row << 8) | (uint32_t)(c * 32 + i);
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(a + h * TC_A_HALF_BYTES + ((c ^ (r_in_tile & 7)) << 4));
+                    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float x = __uint_as_float(u[j] << 16), y = __uint_as_float(u[j] & 0xffff0000u);
+                        ss = fmaf(x, x, fmaf(y, y, ss));
                     }
                 }
             }
-            words[c4] = word;
+            float kn = sqrtf(ss) * 1.001f;
+            // a row whose products could overflow fp32 gets an infinite norm: every projection of it is
+            // then listed for the exact kernel (a NaN norm stays NaN and is handled in the epilogue)
+            if (kn * ts.plane_norm[TC_N] >= 1e38f) kn = INFINITY;
+            ts.knorm[s][r_in_tile] = kn;
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&ts.norm_full[s]);
+                mbar_arrive(&ts.a_empty[s]);
+            }
         }
-        if (valid) {
-            const int64_t dst = dst_row ? dst_row[row] : row;
-            if (dst >= 0)                                  // negative = row not to be written
-                reinterpret_cast<uint4*>(codes + dst * code_row_stride)[chalf] =
-                    make_uint4(words[0], words[1], words[2], words[3]);
+    } else {
+        // ---- epilogue: the four warps with the same (warp % 4) share the 32 accumulator lanes of that
+        // quarter, a quarter of the columns each; a thread owns one row and 64 columns = 8 tables
+        const int quad = warp & 3, cq = (warp - 2 - TC_NORM_WARPS) >> 2;
+        const int r_in_tile = quad * 32 + lane;
+        for (int64_t i = 0; i < my_tiles; ++i) {
+            if (__any_sync(FULL, *failed != 0)) break;                 // warp-uniform
+            const int s = (int)(i & 1);
+            const uint32_t par = (uint32_t)((i >> 1) & 1);
+            const int64_t row = (blockIdx.x + i * gridDim.x) * TC_ROWS + r_in_tile;
+            const bool valid = row < N;
+            int64_t dst = valid ? row : -1;
+            if (valid && dst_row != nullptr) dst = dst_row[row];    // requested before the waits below
+            if (!__all_sync(FULL, mbar_wait_bounded(&ts.norm_full[s], par))) {  // warp-uniform decision
+                *failed = 1;
+                break;
+            }
+            const float knorm = valid ? ts.knorm[s][r_in_tile] : 0.f;
+            const float thr = TC_BAND * knorm;
+            const float thr_max = valid ? thr * ts.plane_norm[TC_N] : -1.f;  // cheap first test, exact test inside
+            if (!__all_sync(FULL, mbar_wait_bounded(&ts.acc_full[s], par))) {
+                *failed = 1;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t words[2];
+#pragma unroll
+            for (int c4 = 0; c4 < 2; ++c4) {
+                const int c = cq * 2 + c4;
+                uint32_t r[32];
+                tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)s * TC_N + c * 32, r);
+                // Fast path, two instructions per projection and no branch: the sign bits are shifted
+                // into one register per table (first plane = most significant bit) and the smallest
+                // |acc| of the chunk decides whether anything needs the near-zero treatment.  A finite
+                // norm below the overflow guard means every accumulator is finite.
+                uint32_t neg[4] = {0u, 0u, 0u, 0u};
+                float mn[4] = {INFINITY, INFINITY, INFINITY, INFINITY};
+#pragma unroll
+                for (int k = 0; k < 32; ++k) {
+                    neg[k >> 3] = __funnelshift_l(r[k], neg[k >> 3], 1);
+                    mn[k & 3] = fminf(mn[k & 3], fabsf(__uint_as_float(r[k])));
+                }
+                uint32_t word = ~(neg[0] | (neg[1] << 8) | (neg[2] << 16) | (neg[3] << 24));
+                const float m = fminf(fminf(mn[0], mn[1]), fminf(mn[2], mn[3]));
+                // warp-uniform: the reload in the careful path is a warp-wide instruction
+                if (__any_sync(FULL, m <= thr_max || !(knorm < INFINITY) || knorm == 0.f)) {
+                    // rare: a projection near zero (listed for the exact kernel; this also settles -0),
+                    // a row that may overflow or holds NaN, or a row of zeros - decide every bit the plain way.
+                    // Kept small on purpose (a rolled loop over a second copy of the chunk): unrolled,
+                    // this path made the kernel wait on instruction fetch more than on anything else.
+                    word = slow_chunk(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)s * TC_N + c * 32, c, row, thr,
+                                      knorm, ts.plane_norm, fix_count, fix_list, fix_cap);
+                }
+                words[c4] = word;
+            }
+            // accumulator and K tile of this stage are free again
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ts.acc_empty[s]);
+            if (dst >= 0)                                          // negative = row not to be written
+                reinterpret_cast<uint2*>(codes + dst * code_row_stride)[cq] = make_uint2(words[0], words[1]);
         }
-    } else if (tid == 0 && status != nullptr) {
-        atomicOr(status, SK_DEV_WAIT_TIMEOUT);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TC_N)
+    if (tid == 0 && ts.failed && status != nullptr) atomicOr(status, SK_DEV_WAIT_TIMEOUT);
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                     "r"((uint32_t)(TC_STAGES * TC_N))
                      : "memory");
     }
 }
@@ -401,12 +534,13 @@ int launch_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* pl
     const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(keys);
     const __nv_bfloat16* pb = static_cast<const __nv_bfloat16*>(planes);
     plane_norm_kernel<<<1, 1024, 0, st>>>(pb, pnorm);
-    const size_t smem = TC_SMEM_TILES + 1024;
+    const size_t smem = TC_PIPE_SMEM + 1024;
     e = cudaFuncSetAttribute(hash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_tc_kernel smem attribute: %s", cudaGetErrorString(e));
-    const unsigned tiles = (unsigned)((N + TC_ROWS - 1) / TC_ROWS);
-    hash_tc_kernel<<<tiles, TC_THREADS, smem, st>>>(map_k, map_p, kb, key_row_stride, pnorm, N, codes,
-                                                 code_row_stride, dst_row, fix_count, fix_list, fix_cap, status);
+    const int64_t tiles = (N + TC_ROWS - 1) / TC_ROWS;
+    const unsigned n_cta = (unsigned)(tiles < 148 ? tiles : 148);     // one persistent CTA per SM
+    hash_tc_kernel<<<n_cta, TC_PIPE_THREADS, smem, st>>>(map_k, map_p, pnorm, N, codes, code_row_stride, dst_row,
+                                                        fix_count, fix_list, fix_cap, status);
     rc = check_launch("hash_tc_kernel");
     if (rc != SK_OK) return rc;
     hash_fix_kernel<<<148, 256, 0, st>>>(kb, key_row_stride, pb, codes, code_row_stride, dst_row, fix_count,
