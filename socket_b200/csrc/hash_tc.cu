@@ -111,39 +111,6 @@ struct TcShared {
     float knorm[TC_STAGES][TC_ROWS];   // |k| * 1.001 of the rows of the stage's tile (inf: decide every bit exactly)
 };
 
-// ||plane_n|| * 1.001 for the 256 planes and their maximum.  One CTA of 1024 threads: warp w owns
-// planes 8w .. 8w+7 and issues all its loads before the first use.
-__global__ void __launch_bounds__(1024)
-plane_norm_kernel(const __nv_bfloat16* __restrict__ planes, float* __restrict__ out) {
-    static_assert(TC_N == 256 && TC_D == 128, "one warp per 8 planes, one 8-byte load per lane and plane");
-    __shared__ float wmax[32];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint2 raw[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-        raw[i] = __ldg(reinterpret_cast<const uint2*>(planes + (size_t)(warp * 8 + i) * TC_D) + lane);
-    float mx = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const float x0 = __uint_as_float(raw[i].x << 16), x1 = __uint_as_float(raw[i].x & 0xffff0000u);
-        const float x2 = __uint_as_float(raw[i].y << 16), x3 = __uint_as_float(raw[i].y & 0xffff0000u);
-        float s = fmaf(x0, x0, fmaf(x1, x1, fmaf(x2, x2, x3 * x3)));
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(FULL, s, o);
-        const float nrm = sqrtf(s) * 1.001f;
-        if (lane == 0) out[warp * 8 + i] = nrm;
-        mx = fmaxf(mx, nrm);
-    }
-    if (lane == 0) wmax[warp] = mx;
-    __syncthreads();
-    if (warp == 0) {
-        float v = wmax[lane];
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULL, v, o));
-        if (lane == 0) out[TC_N] = v;
-    }
-}
-
 __device__ __forceinline__ void mbar_init_count(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
 }
@@ -157,6 +124,15 @@ __device__ __forceinline__ void mbar_expect(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
                  : "memory");
+}
+
+// One projection inside the cheap near-zero band: apply the exact band of its plane and list it.
+__device__ __noinline__ void list_near_zero(float acc, int col, int64_t row, float thr, const float* plane_norm_s,
+                                            uint32_t* fix_count, uint32_t* __restrict__ fix_list, uint32_t fix_cap) {
+    if (fabsf(acc) <= thr * plane_norm_s[col]) {
+        const uint32_t slot = atomicAdd(fix_count, 1u);
+        if (slot < fix_cap) fix_list[slot] = ((uint32_t)row << 8) | (uint32_t)col;
+    }
 }
 
 // The careful version of one 32-column chunk of one accumulator row (see the epilogue).
@@ -187,7 +163,7 @@ __device__ __noinline__ uint32_t slow_chunk(uint32_t taddr, int c, int64_t row, 
 // raises `failed`, which makes every role leave its loop, and the status flag.
 __global__ void __launch_bounds__(TC_PIPE_THREADS, 1)
 hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_p,
-               const float* __restrict__ plane_norm, int64_t N, uint8_t* __restrict__ codes,
+               const __nv_bfloat16* __restrict__ planes, int64_t N, uint8_t* __restrict__ codes,
                int64_t code_row_stride, const int64_t* __restrict__ dst_row, uint32_t* fix_count,
                uint32_t* __restrict__ fix_list, uint32_t fix_cap, int32_t* status) {
     extern __shared__ char tc_raw[];
@@ -199,7 +175,17 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     const int64_t n_tiles = (N + TC_ROWS - 1) / TC_ROWS;
     const int64_t my_tiles = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;     // >= 1: grid <= n_tiles
 
-    for (int i = tid; i <= TC_N; i += TC_PIPE_THREADS) ts.plane_norm[i] = plane_norm[i];
+    // |plane| * 1.001 of the 256 planes, one warp per plane (every CTA computes them for itself:
+    // 64 KiB from L2, cheaper than a launch of its own)
+    for (int n = warp; n < TC_N; n += TC_PIPE_THREADS / 32) {
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(planes + (size_t)n * TC_D) + lane);
+        const float x0 = __uint_as_float(raw.x << 16), x1 = __uint_as_float(raw.x & 0xffff0000u);
+        const float x2 = __uint_as_float(raw.y << 16), x3 = __uint_as_float(raw.y & 0xffff0000u);
+        float sq = fmaf(x0, x0, fmaf(x1, x1, fmaf(x2, x2, x3 * x3)));
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) sq += __shfl_xor_sync(FULL, sq, o);
+        if (lane == 0) ts.plane_norm[n] = sqrtf(sq) * 1.001f;
+    }
     if (tid == 0) {
         mbar_init_count(&ts.b_full, 1);
         for (int s = 0; s < TC_STAGES; ++s) {
@@ -224,6 +210,14 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = ts.tmem_base;
     volatile int* failed = &ts.failed;
+    if (warp == 2) {                          // the largest plane norm, for the cheap first test
+        float v = 0.f;
+        for (int n = lane; n < TC_N; n += 32) v = fmaxf(v, ts.plane_norm[n]);
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(FULL, v, o));
+        if (lane == 0) ts.plane_norm[TC_N] = v;
+    }
+    __syncthreads();
 
     if (warp == 0) {
         // ---- TMA producer
@@ -353,14 +347,29 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                 }
                 uint32_t word = ~(neg[0] | (neg[1] << 8) | (neg[2] << 16) | (neg[3] << 24));
                 const float m = fminf(fminf(mn[0], mn[1]), fminf(mn[2], mn[3]));
+                if (m <= thr_max && knorm < INFINITY && knorm > 0.f) {
+                    // some projection of this row is near zero (about one chunk in seven has one): list
+                    // it for the exact kernel.  The bits above stay as they are - the only value whose
+                    // sign bit disagrees with (acc >= 0) is -0, and that one is always listed.  Only the
+                    // eight columns of a residue class whose minimum fell inside the band are looked at.
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (mn[q] <= thr_max) {
+#pragma unroll
+                            for (int k = q; k < 32; k += 4)
+                                if (fabsf(__uint_as_float(r[k])) <= thr_max)
+                                    list_near_zero(__uint_as_float(r[k]), c * 32 + k, row, thr, ts.plane_norm, fix_count,
+                                                   fix_list, fix_cap);
+                        }
+                    }
+                }
                 // warp-uniform: the reload in the careful path is a warp-wide instruction
-                if (__any_sync(FULL, m <= thr_max || !(knorm < INFINITY) || knorm == 0.f)) {
-                    // rare: a projection near zero (listed for the exact kernel; this also settles -0),
-                    // a row that may overflow or holds NaN, or a row of zeros - decide every bit the plain way.
-                    // Kept small on purpose (a rolled loop over a second copy of the chunk): unrolled,
-                    // this path made the kernel wait on instruction fetch more than on anything else.
-                    word = slow_chunk(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)s * TC_N + c * 32, c, row, thr,
-                                      knorm, ts.plane_norm, fix_count, fix_list, fix_cap);
+                if (__any_sync(FULL, !(knorm < INFINITY) || knorm == 0.f)) {
+                    // rare: a row that may overflow or holds NaN, or a row of zeros - decide every bit
+                    // the plain way (a rolled loop over a second copy of the chunk, out of line)
+                    const uint32_t w2 = slow_chunk(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)s * TC_N + c * 32, c,
+                                                   row, thr, knorm, ts.plane_norm, fix_count, fix_list, fix_cap);
+                    if (!(knorm < INFINITY) || knorm == 0.f) word = w2;
                 }
                 words[c4] = word;
             }
@@ -521,7 +530,6 @@ int launch_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* pl
         return fail(SK_ERR_WORKSPACE, "sk_hash_keys_tc: workspace %zu bytes is too small", workspace_bytes);
     char* ws = static_cast<char*>(workspace);
     uint32_t* fix_count = reinterpret_cast<uint32_t*>(ws);
-    float* pnorm = reinterpret_cast<float*>(ws + 256);
     uint32_t* fix_list = reinterpret_cast<uint32_t*>(ws + TC_WS_HEADER);
     const uint32_t fix_cap = (uint32_t)((workspace_bytes - TC_WS_HEADER) / sizeof(uint32_t));
     CUtensorMap map_k, map_p;
@@ -533,19 +541,19 @@ int launch_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* pl
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "sk_hash_keys_tc: cudaMemsetAsync: %s", cudaGetErrorString(e));
     const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(keys);
     const __nv_bfloat16* pb = static_cast<const __nv_bfloat16*>(planes);
-    plane_norm_kernel<<<1, 1024, 0, st>>>(pb, pnorm);
     const size_t smem = TC_PIPE_SMEM + 1024;
     e = cudaFuncSetAttribute(hash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_tc_kernel smem attribute: %s", cudaGetErrorString(e));
     const int64_t tiles = (N + TC_ROWS - 1) / TC_ROWS;
     const unsigned n_cta = (unsigned)(tiles < 148 ? tiles : 148);     // one persistent CTA per SM
-    hash_tc_kernel<<<n_cta, TC_PIPE_THREADS, smem, st>>>(map_k, map_p, pnorm, N, codes, code_row_stride, dst_row,
+    hash_tc_kernel<<<n_cta, TC_PIPE_THREADS, smem, st>>>(map_k, map_p, pb, N, codes, code_row_stride, dst_row,
                                                         fix_count, fix_list, fix_cap, status);
     rc = check_launch("hash_tc_kernel");
     if (rc != SK_OK) return rc;
-    hash_fix_kernel<<<148, 256, 0, st>>>(kb, key_row_stride, pb, codes, code_row_stride, dst_row, fix_count,
-                                         fix_list, fix_cap);
-    dim3 grid(148 * 4, TC_N / 8 / HASH_WARPS);
+    // one listed projection per warp in the common case (about 1.4e-4 of the projections are listed)
+    hash_fix_kernel<<<148 * 8, 256, 0, st>>>(kb, key_row_stride, pb, codes, code_row_stride, dst_row, fix_count,
+                                             fix_list, fix_cap);
+    dim3 grid(148, TC_N / 8 / HASH_WARPS);
     hash_exact_if_overflow_kernel<<<grid, HASH_THREADS, 0, st>>>(kb, key_row_stride, pb, N, codes, code_row_stride,
                                                                  dst_row, fix_count, fix_cap);
     return check_launch("hash_tc fix-up kernels");
