@@ -28,7 +28,7 @@ constexpr int TC_KHALF = 64;          // bf16 elements per 128-byte swizzle row
 constexpr uint32_t TC_A_HALF_BYTES = TC_ROWS * 128;   // 16 KiB
 constexpr uint32_t TC_B_HALF_BYTES = TC_N * 128;      // 32 KiB
 constexpr uint32_t TC_PIPE_SMEM = 2 * TC_B_HALF_BYTES + 2 * 2 * TC_A_HALF_BYTES;   // planes + two K tiles: 128 KiB
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 17;   // polls; a poll that fails takes microseconds, so well under a second
 constexpr float TC_BAND = 1.52587890625e-05f;         // 2^-16
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -102,13 +102,13 @@ struct TcShared {
     uint64_t b_full;                   // planes have landed (once)
     uint64_t a_full[TC_STAGES];        // K tile of the stage has landed
     uint64_t a_empty[TC_STAGES];       // MMAs and the norm warps are done with the stage's K tile
-    uint64_t norm_full[TC_STAGES];     // row norms of the stage's K tile are in knorm[]
+    uint64_t norm_full[2 * TC_STAGES]; // row norms of tile i are in knorm[i % 4]
     uint64_t acc_full[TC_STAGES];      // accumulator is complete
     uint64_t acc_empty[TC_STAGES];     // accumulator has been read back
     uint32_t tmem_base;
     int failed;                        // some bounded wait ran out
     float plane_norm[TC_N + 1];        // [TC_N] = the largest norm
-    float knorm[TC_STAGES][TC_ROWS];   // |k| * 1.001 of the rows of the stage's tile (inf: decide every bit exactly)
+    float knorm[2 * TC_STAGES][TC_ROWS];   // |k| * 1.001 of the rows of tile i in slot i % 4 (inf: decide every bit exactly)
 };
 
 __device__ __forceinline__ void mbar_init_count(uint64_t* bar, uint32_t count) {
@@ -192,6 +192,7 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             mbar_init_count(&ts.a_full[s], 1);
             mbar_init_count(&ts.a_empty[s], 1 + TC_NORM_WARPS); // MMA commit + one arrival per norm warp
             mbar_init_count(&ts.norm_full[s], TC_NORM_WARPS);
+            mbar_init_count(&ts.norm_full[s + TC_STAGES], TC_NORM_WARPS);
             mbar_init_count(&ts.acc_full[s], 1);
             mbar_init_count(&ts.acc_empty[s], TC_EPI_WARPS);
         }
@@ -271,9 +272,12 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             if (__any_sync(FULL, *failed != 0)) break;                 // warp-uniform
             const int s = (int)(i & 1);
             const uint32_t par = (uint32_t)((i >> 1) & 1);
-            // the tile has landed, and the epilogue of the tile before last has read its norms
-            if (!__all_sync(FULL, mbar_wait_bounded(&ts.a_full[s], par)) ||
-                (i >= TC_STAGES && !__all_sync(FULL, mbar_wait_bounded(&ts.acc_empty[s], par ^ 1u)))) {
+            // The tile has landed.  Its norms go to slot i % 4, which has a barrier of its own (the norm
+            // warps may be two tiles ahead of the epilogue, and a barrier must not complete two phases
+            // ahead of a waiter): the tile can only have been loaded after the MMAs of tile i-2 were
+            // done, which started after the epilogue of tile i-4 - the last reader of that slot - had
+            // finished, so the norm warps never wait for the epilogue.
+            if (!__all_sync(FULL, mbar_wait_bounded(&ts.a_full[s], par))) {
                 *failed = 1;
                 break;
             }
@@ -296,10 +300,10 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             // a row whose products could overflow fp32 gets an infinite norm: every projection of it is
             // then listed for the exact kernel (a NaN norm stays NaN and is handled in the epilogue)
             if (kn * ts.plane_norm[TC_N] >= 1e38f) kn = INFINITY;
-            ts.knorm[s][r_in_tile] = kn;
+            ts.knorm[i & 3][r_in_tile] = kn;
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&ts.norm_full[s]);
+                mbar_arrive(&ts.norm_full[i & 3]);
                 mbar_arrive(&ts.a_empty[s]);
             }
         }
@@ -316,11 +320,11 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             const bool valid = row < N;
             int64_t dst = valid ? row : -1;
             if (valid && dst_row != nullptr) dst = dst_row[row];    // requested before the waits below
-            if (!__all_sync(FULL, mbar_wait_bounded(&ts.norm_full[s], par))) {  // warp-uniform decision
+            if (!__all_sync(FULL, mbar_wait_bounded(&ts.norm_full[i & 3], (uint32_t)((i >> 2) & 1)))) {  // warp-uniform decision
                 *failed = 1;
                 break;
             }
-            const float knorm = valid ? ts.knorm[s][r_in_tile] : 0.f;
+            const float knorm = valid ? ts.knorm[i & 3][r_in_tile] : 0.f;
             const float thr = TC_BAND * knorm;
             const float thr_max = valid ? thr * ts.plane_norm[TC_N] : -1.f;  // cheap first test, exact test inside
             if (!__all_sync(FULL, mbar_wait_bounded(&ts.acc_full[s], par))) {

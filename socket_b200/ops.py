@@ -57,9 +57,9 @@ def hash_keys(keys: torch.Tensor, planes: torch.Tensor, code_dtype=torch.uint8) 
     return codes
 
 
-def hash_keys_tc(keys: torch.Tensor, planes: torch.Tensor) -> torch.Tensor:
+def hash_keys_tc(keys: torch.Tensor, planes: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core bulk hashing: bf16 keys [..., 128], planes [32, 8, 128] -> uint8 codes [..., 32],
-    bit-identical to `hash_keys`."""
+    bit-identical to `hash_keys`.  `status` (int32 device word) collects device-side flags."""
     _require_cuda(keys, planes)
     L, P, D = planes.shape
     keys = keys.contiguous()
@@ -70,7 +70,7 @@ def hash_keys_tc(keys: torch.Tensor, planes: torch.Tensor) -> torch.Tensor:
     if dtype_code(keys) != _lib.SK_BF16 or dtype_code(planes) != _lib.SK_BF16:
         raise RuntimeError("hash_keys_tc needs bf16 keys and planes")
     check(lib().sk_hash_keys_tc(ptr(keys), D, ptr(planes), N, D, L, P, ptr(codes), L, None, ptr(ws), ws.numel(),
-                                None, stream_ptr(keys.device)), "sk_hash_keys_tc")
+                                ptr(status), stream_ptr(keys.device)), "sk_hash_keys_tc")
     return codes
 
 

@@ -652,6 +652,28 @@ def test_tensor_core_hashing_is_bit_exact():
     assert (got[5] == 255).all()
 
 
+def test_tensor_core_hashing_pipeline_over_many_tiles():
+    """Enough rows that every persistent CTA walks several tiles, so that the load / multiply /
+    epilogue pipeline and its barriers go round many times: no wait may run out (status stays 0, and
+    the call takes milliseconds, not the seconds a timed-out wait costs), and the codes equal the
+    exact kernel's."""
+    g = torch.Generator().manual_seed(35)
+    N = 148 * 128 * 9 + 77
+    planes = cu(torch.randn(32, 8, 128, generator=g).bfloat16())
+    keys = cu((torch.randn(N, 128, generator=g) * torch.exp(0.5 * torch.randn(128, generator=g))).bfloat16())
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.hash_keys_tc(keys, planes, status=status)                  # warm-up (tensor maps, attributes)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    got = ops.hash_keys_tc(keys, planes, status=status)
+    e1.record()
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    assert e0.elapsed_time(e1) < 50.0, e0.elapsed_time(e1)
+    assert torch.equal(got, ops.hash_keys(keys, planes))
+
+
 def test_tensor_core_hashing_overflow_path_is_exact():
     # every key exactly orthogonal to many planes: the near-zero list overflows and the exact
     # rehash takes over
