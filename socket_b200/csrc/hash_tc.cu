@@ -27,7 +27,7 @@ constexpr int TC_D = 128;             // head dim (MMA K total)
 constexpr int TC_KHALF = 64;          // bf16 elements per 128-byte swizzle row
 constexpr uint32_t TC_A_HALF_BYTES = TC_ROWS * 128;   // 16 KiB
 constexpr uint32_t TC_B_HALF_BYTES = TC_N * 128;      // 32 KiB
-constexpr uint32_t TC_PIPE_SMEM = 2 * TC_B_HALF_BYTES + 2 * 2 * TC_A_HALF_BYTES;   // planes + two K tiles: 128 KiB
+constexpr uint32_t TC_PIPE_SMEM = 2 * TC_B_HALF_BYTES + 4 * 2 * TC_A_HALF_BYTES;   // planes + four K tiles: 192 KiB
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 17;   // polls; a poll that fails takes microseconds, so well under a second
 constexpr float TC_BAND = 1.52587890625e-05f;         // 2^-16
 
@@ -93,22 +93,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-constexpr int TC_STAGES = 2;          // K tiles in flight and accumulators in tensor memory
+constexpr int TC_STAGES = 2;          // accumulators in tensor memory
+constexpr int TC_ARING = 4;           // K tiles in flight (the TMA round trip is longer than two tiles' work)
+constexpr int TC_NSLOTS = 8;          // norm slots
 constexpr int TC_NORM_WARPS = 4;      // one thread per row of the K tile
 constexpr int TC_EPI_WARPS = 16;      // four threads per accumulator row, 64 columns each
 constexpr int TC_PIPE_THREADS = 32 * (2 + TC_NORM_WARPS + TC_EPI_WARPS);   // TMA warp, MMA warp, norm warps, epilogue warps
 
 struct TcShared {
     uint64_t b_full;                   // planes have landed (once)
-    uint64_t a_full[TC_STAGES];        // K tile of the stage has landed
-    uint64_t a_empty[TC_STAGES];       // MMAs and the norm warps are done with the stage's K tile
-    uint64_t norm_full[2 * TC_STAGES]; // row norms of tile i are in knorm[i % 4]
+    uint64_t a_full[TC_ARING];         // K tile of the ring slot has landed
+    uint64_t a_empty[TC_ARING];        // MMAs and the norm warps are done with the slot's K tile
+    uint64_t norm_full[TC_NSLOTS];     // row norms of tile i are in knorm[i % 8]
     uint64_t acc_full[TC_STAGES];      // accumulator is complete
     uint64_t acc_empty[TC_STAGES];     // accumulator has been read back
     uint32_t tmem_base;
     int failed;                        // some bounded wait ran out
     float plane_norm[TC_N + 1];        // [TC_N] = the largest norm
-    float knorm[2 * TC_STAGES][TC_ROWS];   // |k| * 1.001 of the rows of tile i in slot i % 4 (inf: decide every bit exactly)
+    float knorm[TC_NSLOTS][TC_ROWS];   // |k| * 1.001 of the rows of tile i in slot i % 8 (inf: decide every bit exactly)
 };
 
 __device__ __forceinline__ void mbar_init_count(uint64_t* bar, uint32_t count) {
@@ -170,7 +172,7 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     __shared__ TcShared ts;
     char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
     char* b_half[2] = {tiles, tiles + TC_B_HALF_BYTES};
-    char* a_base = tiles + 2 * TC_B_HALF_BYTES;                 // [stage][half][16 KiB]
+    char* a_base = tiles + 2 * TC_B_HALF_BYTES;                 // [ring slot][half][16 KiB]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t n_tiles = (N + TC_ROWS - 1) / TC_ROWS;
     const int64_t my_tiles = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;     // >= 1: grid <= n_tiles
@@ -188,11 +190,12 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     }
     if (tid == 0) {
         mbar_init_count(&ts.b_full, 1);
-        for (int s = 0; s < TC_STAGES; ++s) {
+        for (int s = 0; s < TC_ARING; ++s) {
             mbar_init_count(&ts.a_full[s], 1);
             mbar_init_count(&ts.a_empty[s], 1 + TC_NORM_WARPS); // MMA commit + one arrival per norm warp
-            mbar_init_count(&ts.norm_full[s], TC_NORM_WARPS);
-            mbar_init_count(&ts.norm_full[s + TC_STAGES], TC_NORM_WARPS);
+        }
+        for (int s = 0; s < TC_NSLOTS; ++s) mbar_init_count(&ts.norm_full[s], TC_NORM_WARPS);
+        for (int s = 0; s < TC_STAGES; ++s) {
             mbar_init_count(&ts.acc_full[s], 1);
             mbar_init_count(&ts.acc_empty[s], TC_EPI_WARPS);
         }
@@ -227,16 +230,16 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             tma_load_2d(b_half[0], &map_p, 0, 0, &ts.b_full);
             tma_load_2d(b_half[1], &map_p, TC_KHALF, 0, &ts.b_full);
             for (int64_t i = 0; i < my_tiles && !*failed; ++i) {
-                const int s = (int)(i & 1);
-                if (i >= TC_STAGES && !mbar_wait_bounded(&ts.a_empty[s], (uint32_t)(((i >> 1) - 1) & 1))) {
+                const int ra = (int)(i % TC_ARING);
+                if (i >= TC_ARING && !mbar_wait_bounded(&ts.a_empty[ra], (uint32_t)((i / TC_ARING - 1) & 1))) {
                     *failed = 1;
                     break;
                 }
                 const int row0 = (int)((blockIdx.x + i * gridDim.x) * TC_ROWS);
-                char* a = a_base + (size_t)s * 2 * TC_A_HALF_BYTES;
-                mbar_expect(&ts.a_full[s], 2 * TC_A_HALF_BYTES);
-                tma_load_2d(a, &map_k, 0, row0, &ts.a_full[s]);
-                tma_load_2d(a + TC_A_HALF_BYTES, &map_k, TC_KHALF, row0, &ts.a_full[s]);
+                char* a = a_base + (size_t)ra * 2 * TC_A_HALF_BYTES;
+                mbar_expect(&ts.a_full[ra], 2 * TC_A_HALF_BYTES);
+                tma_load_2d(a, &map_k, 0, row0, &ts.a_full[ra]);
+                tma_load_2d(a + TC_A_HALF_BYTES, &map_k, TC_KHALF, row0, &ts.a_full[ra]);
             }
         }
     } else if (warp == 1) {
@@ -244,15 +247,15 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         if (lane == 0) {
             if (!mbar_wait_bounded(&ts.b_full, 0)) *failed = 1;
             for (int64_t i = 0; i < my_tiles && !*failed; ++i) {
-                const int s = (int)(i & 1);
+                const int s = (int)(i & 1), ra = (int)(i % TC_ARING);
                 const uint32_t par = (uint32_t)((i >> 1) & 1);
-                if (!mbar_wait_bounded(&ts.a_full[s], par) ||
+                if (!mbar_wait_bounded(&ts.a_full[ra], (uint32_t)((i / TC_ARING) & 1)) ||
                     (i >= TC_STAGES && !mbar_wait_bounded(&ts.acc_empty[s], par ^ 1u))) {
                     *failed = 1;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_addr(a_base + (size_t)s * 2 * TC_A_HALF_BYTES);
+                const uint32_t a_addr = smem_addr(a_base + (size_t)ra * 2 * TC_A_HALF_BYTES);
 #pragma unroll
                 for (int k = 0; k < TC_D / 16; ++k) {
                     const int half = k >> 2, kb = k & 3;           // 16 bf16 = 32 bytes along the swizzled row
@@ -261,7 +264,7 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                     umma_bf16(tmem + (uint32_t)s * TC_N, da, db, k > 0 ? 1u : 0u);
                 }
                 umma_commit(&ts.acc_full[s]);                       // accumulator complete ...
-                umma_commit(&ts.a_empty[s]);                        // ... and the K tile no longer read by the MMAs
+                umma_commit(&ts.a_empty[ra]);                       // ... and the K tile no longer read by the MMAs
             }
         }
     } else if (warp < 2 + TC_NORM_WARPS) {
@@ -270,19 +273,18 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         const int r_in_tile = (warp - 2) * 32 + lane;
         for (int64_t i = 0; i < my_tiles; ++i) {
             if (__any_sync(FULL, *failed != 0)) break;                 // warp-uniform
-            const int s = (int)(i & 1);
-            const uint32_t par = (uint32_t)((i >> 1) & 1);
-            // The tile has landed.  Its norms go to slot i % 4, which has a barrier of its own (the norm
-            // warps may be two tiles ahead of the epilogue, and a barrier must not complete two phases
-            // ahead of a waiter): the tile can only have been loaded after the MMAs of tile i-2 were
-            // done, which started after the epilogue of tile i-4 - the last reader of that slot - had
-            // finished, so the norm warps never wait for the epilogue.
-            if (!__all_sync(FULL, mbar_wait_bounded(&ts.a_full[s], par))) {
+            const int ra = (int)(i % TC_ARING);
+            // The tile has landed.  Its norms go to slot i % 8, which has a barrier of its own (the norm
+            // warps may be several tiles ahead of the epilogue, and a barrier must not complete two
+            // phases ahead of a waiter): tile i can only have been loaded after the MMAs of tile i-4
+            // were done, which started after the epilogue of tile i-6 had finished, so the last reader
+            // of the slot (tile i-8) is long gone and the norm warps never wait for the epilogue.
+            if (!__all_sync(FULL, mbar_wait_bounded(&ts.a_full[ra], (uint32_t)((i / TC_ARING) & 1)))) {
                 *failed = 1;
                 break;
             }
             float ss = 0.f;
-            const char* a = a_base + (size_t)s * 2 * TC_A_HALF_BYTES + (size_t)r_in_tile * 128;
+            const char* a = a_base + (size_t)ra * 2 * TC_A_HALF_BYTES + (size_t)r_in_tile * 128;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -300,11 +302,11 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             // a row whose products could overflow fp32 gets an infinite norm: every projection of it is
             // then listed for the exact kernel (a NaN norm stays NaN and is handled in the epilogue)
             if (kn * ts.plane_norm[TC_N] >= 1e38f) kn = INFINITY;
-            ts.knorm[i & 3][r_in_tile] = kn;
+            ts.knorm[i % TC_NSLOTS][r_in_tile] = kn;
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&ts.norm_full[i & 3]);
-                mbar_arrive(&ts.a_empty[s]);
+                mbar_arrive(&ts.norm_full[i % TC_NSLOTS]);
+                mbar_arrive(&ts.a_empty[ra]);
             }
         }
     } else {
@@ -320,11 +322,11 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
             const bool valid = row < N;
             int64_t dst = valid ? row : -1;
             if (valid && dst_row != nullptr) dst = dst_row[row];    // requested before the waits below
-            if (!__all_sync(FULL, mbar_wait_bounded(&ts.norm_full[i & 3], (uint32_t)((i >> 2) & 1)))) {  // warp-uniform decision
+            if (!__all_sync(FULL, mbar_wait_bounded(&ts.norm_full[i % TC_NSLOTS], (uint32_t)((i / TC_NSLOTS) & 1)))) {  // warp-uniform decision
                 *failed = 1;
                 break;
             }
-            const float knorm = valid ? ts.knorm[i & 3][r_in_tile] : 0.f;
+            const float knorm = valid ? ts.knorm[i % TC_NSLOTS][r_in_tile] : 0.f;
             const float thr = TC_BAND * knorm;
             const float thr_max = valid ? thr * ts.plane_norm[TC_N] : -1.f;  // cheap first test, exact test inside
             if (!__all_sync(FULL, mbar_wait_bounded(&ts.acc_full[s], par))) {
