@@ -468,6 +468,32 @@ def main():
             "frac_of_hbm_peak": round(bytes_pf / t_us / 1e3 / peak, 4),
             "note": "sk_kv_append_tc: copy + v_norm kernel, then tensor-core hashing; not in the step"}
         del k_pf, v_pf
+    # context figure, not on the path: dense attention of the same query over the whole cache
+    # (torch's fused SDPA, a library kernel), i.e. what the sparse path replaces per layer and token
+    try:
+        import torch.nn.functional as F
+        qd = q_s.view(B, Hkv, H // Hkv, D)                         # the rep query heads of a KV head as "rows"
+        kd, vd = cache.k_cache[:, :, :T_now], cache.v_cache[:, :, :T_now]
+        t_dense = time_kernel(lambda: F.scaled_dot_product_attention(qd, kd, vd))
+        dense_bytes = 2 * B * Hkv * T_now * D * cfg.kv_bytes()
+        stages["dense_attention_sdpa"] = {
+            "us": round(t_dense, 2), "algorithmic_bytes": dense_bytes,
+            "achieved_gbs": round(dense_bytes / (t_dense * 1e-6) / 1e9, 1),
+            "note": "torch SDPA over the full context, for comparison; not on the step's path"}
+    except Exception as e:  # a comparison figure must never cost the line
+        stages["dense_attention_sdpa"] = {"us": None, "note": f"unavailable: {e!r}"}
+    try:
+        from flash_attn import flash_attn_with_kvcache           # split-KV dense decode, a library kernel
+        qf = q_s.view(B, 1, H, D)
+        kf, vf = cache.k_cache.transpose(1, 2), cache.v_cache.transpose(1, 2)      # [B, Tcap, Hkv, D] views
+        lens = torch.full((B,), T_now, dtype=torch.int32, device=dev)
+        t_fa = time_kernel(lambda: flash_attn_with_kvcache(qf, kf, vf, cache_seqlens=lens))
+        stages["dense_attention_flash_decode"] = {
+            "us": round(t_fa, 2), "algorithmic_bytes": dense_bytes,
+            "achieved_gbs": round(dense_bytes / (t_fa * 1e-6) / 1e9, 1),
+            "note": "flash_attn_with_kvcache over the full context, for comparison; not on the step's path"}
+    except Exception as e:
+        stages["dense_attention_flash_decode"] = {"us": None, "note": f"unavailable: {e!r}"[:200]}
     A = a_codes + a_kv
     step_gbs = A / (ms_per_step * 1e-3) / 1e9
     stages["whole_step"] = {"us": round(ms_per_step * 1e3, 2), "algorithmic_bytes": A,
