@@ -535,7 +535,7 @@ def main():
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
-        hd.h_in.copy_(packed[i])
+        hd.stage(packed[i])
         hd.launch()
         e1.record()
         hd.wait()

@@ -3,6 +3,7 @@ codes and value norms, the hash methods of `Attention`, and the decode branch of
 `Attention.sparse_forward` between the QKV projection and the output projection."""
 from __future__ import annotations
 
+import ctypes
 import math
 from typing import Optional
 
@@ -154,11 +155,12 @@ class SocketAttention(nn.Module):
 class HostDecodeStep:
     """One decode step whose inputs live in host memory: a single pinned staging block
     `[input_pos | q | k_new | v_new]` goes to the device in one copy, the four kernels of
-    `sk_decode_step` run, and the output comes back into pinned memory — all of it one CUDA
-    graph, so a step costs one launch call.  Write the inputs through `h_q`, `h_k`, `h_v`,
-    `h_pos` (views of the staging block), call `launch()` and, once `wait()` returns, read
-    `h_out`.  `__call__` does the three for host tensors.  Build it after the cache is
-    allocated; the graph holds the cache's addresses."""
+    `sk_decode_step` run, and the last of them writes the output straight into pinned host
+    memory (it is mapped into the device's address space, so no copy node is needed) — all of it
+    one CUDA graph, so a step costs one launch call.  Write the inputs through `h_q`, `h_k`,
+    `h_v`, `h_pos` (views of the staging block) or hand a packed block to `stage()`, call
+    `launch()` and, once `wait()` returns, read `h_out`.  `__call__` does the three for host
+    tensors.  Build it after the cache is allocated; the graph holds the cache's addresses."""
 
     def __init__(self, attn: SocketAttention, batch: int):
         cache = attn.kv_cache
@@ -181,10 +183,9 @@ class HostDecodeStep:
 
         self.h_pos, self.h_q, self.h_k, self.h_v = views(self.h_in)
         d_pos, d_q, d_k, d_v = views(self.d_in)
-        self.d_out = torch.empty(B, H, D, dtype=dt, device=dev)
         self.h_out = torch.empty(B, H, D, dtype=dt).pin_memory()
         self.h2d_bytes, self.d2h_bytes = total, self.h_out.numel() * es
-        self.step = ops.DecodeStep(cache, d_q, d_k, d_v, d_pos, attn.planes, attn.protos_T, self.d_out,
+        self.step = ops.DecodeStep(cache, d_q, d_k, d_v, d_pos, attn.planes, attn.protos_T, self.h_out,
                                    topk=attn.heavy_const, sink=attn.sink_size, window=attn.window_size,
                                    T_max=cache.k_cache.shape[2], temperature=attn.temperature)
         self.done = torch.cuda.Event()
@@ -192,7 +193,12 @@ class HostDecodeStep:
         with torch.cuda.graph(self.graph):
             self.d_in.copy_(self.h_in, non_blocking=True)
             self.step.run()
-            self.h_out.copy_(self.d_out, non_blocking=True)
+
+    def stage(self, packed: Tensor) -> None:
+        """Copy one packed input block (same layout and size as `h_in`, host memory) into the
+        staging block."""
+        assert packed.numel() * packed.element_size() == self.h_in.numel() and packed.is_contiguous()
+        ctypes.memmove(self.h_in.data_ptr(), packed.data_ptr(), self.h_in.numel())
 
     def launch(self) -> None:
         self.graph.replay()
