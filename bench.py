@@ -41,9 +41,9 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None where no capture of that kernel/workload exists yet.
 NCU_TRAFFIC = {
-    ("score_filter", "c2"): 10008320, ("select_candidates", "c2"): 2437888, ("sparse_decode", "c2"): 13186560,
-    ("score_filter", "c3"): 157108480, ("select_candidates", "c3"): 9341440, ("sparse_decode", "c3"): 118190336,
-    ("score_select_cluster", "c2"): 10065664,
+    ("score_filter", "c2"): 10013440, ("select_candidates", "c2"): 2436864, ("sparse_decode", "c2"): 13187328,
+    ("score_filter", "c3"): 157842176, ("select_candidates", "c3"): 9340160, ("sparse_decode", "c3"): 117413376,
+    ("score_select_cluster", "c2"): 10066176,
 }
 
 
