@@ -81,6 +81,14 @@ inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block,
     cfg.numAttrs = chained ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
+// Always chained to the kernel before it on the stream (that kernel must be one of this library's,
+// executing pdl_launch_dependents).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                Args... args) {
+    PdlChain chain;
+    return launch_chained(kern, grid, block, smem, st, args...);
+}
 
 // ---------------------------------------------------------------- shared-memory histograms
 // Histogram increment by all 32 lanes of a warp.  The lanes that hit the same bin as the first

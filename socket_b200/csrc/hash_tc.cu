@@ -170,6 +170,7 @@ hash_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
                uint32_t* __restrict__ fix_list, uint32_t fix_cap, int32_t* status) {
     extern __shared__ char tc_raw[];
     __shared__ TcShared ts;
+    pdl_launch_dependents();                   // the fix-up kernels may start launching; they wait for this grid
     char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(tc_raw) + 1023) & ~(uintptr_t)1023);
     char* b_half[2] = {tiles, tiles + TC_B_HALF_BYTES};
     char* a_base = tiles + 2 * TC_B_HALF_BYTES;                 // [ring slot][half][16 KiB]
@@ -405,10 +406,12 @@ hash_fix_kernel(const __nv_bfloat16* __restrict__ keys, int64_t key_row_stride,
                 const uint32_t* __restrict__ fix_count, const uint32_t* __restrict__ fix_list,
                 uint32_t fix_cap) {
     const int lane = threadIdx.x & 31;
-    const uint32_t n = min(*fix_count, fix_cap);
+    pdl_launch_dependents();
+    pdl_wait();                                // the list, its length and the codes come from the kernel before
+    const uint32_t n = min(__ldcg(fix_count), fix_cap);
     const uint32_t warps = gridDim.x * (blockDim.x >> 5);
     for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < n; e += warps) {
-        const uint32_t ent = fix_list[e];
+        const uint32_t ent = __ldcg(fix_list + e);
         const int64_t row = ent >> 8;
         const int col = (int)(ent & 0xffu);               // l * 8 + p
         const __nv_bfloat16* k = keys + row * key_row_stride;
@@ -438,7 +441,8 @@ hash_exact_if_overflow_kernel(const __nv_bfloat16* __restrict__ keys, int64_t ke
                               const __nv_bfloat16* __restrict__ planes, int64_t N, uint8_t* codes,
                               int64_t code_row_stride, const int64_t* __restrict__ dst_row,
                               const uint32_t* __restrict__ fix_count, uint32_t fix_cap) {
-    if (*fix_count <= fix_cap) return;
+    pdl_wait();                                // after the fix-up kernel, which may still be patching codes
+    if (__ldcg(fix_count) <= fix_cap) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int l = blockIdx.y * HASH_WARPS + warp;
     for (int64_t n0 = (int64_t)blockIdx.x * HASH_ROWS; n0 < N; n0 += (int64_t)gridDim.x * HASH_ROWS) {
@@ -557,11 +561,13 @@ int launch_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* pl
     rc = check_launch("hash_tc_kernel");
     if (rc != SK_OK) return rc;
     // one listed projection per warp in the common case (about 1.4e-4 of the projections are listed)
-    hash_fix_kernel<<<148 * 8, 256, 0, st>>>(kb, key_row_stride, pb, codes, code_row_stride, dst_row, fix_count,
-                                             fix_list, fix_cap);
+    e = launch_after(hash_fix_kernel, dim3(148 * 8), dim3(256), 0, st, kb, key_row_stride, pb, codes, code_row_stride,
+                     dst_row, (const uint32_t*)fix_count, (const uint32_t*)fix_list, fix_cap);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_fix_kernel: %s", cudaGetErrorString(e));
     dim3 grid(148, TC_N / 8 / HASH_WARPS);
-    hash_exact_if_overflow_kernel<<<grid, HASH_THREADS, 0, st>>>(kb, key_row_stride, pb, N, codes, code_row_stride,
-                                                                 dst_row, fix_count, fix_cap);
+    e = launch_after(hash_exact_if_overflow_kernel, grid, dim3(HASH_THREADS), 0, st, kb, key_row_stride, pb, N, codes,
+                     code_row_stride, dst_row, (const uint32_t*)fix_count, fix_cap);
+    if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_exact_if_overflow_kernel: %s", cudaGetErrorString(e));
     return check_launch("hash_tc fix-up kernels");
 }
 
