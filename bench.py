@@ -442,7 +442,7 @@ def main():
             "us": round(t_us, 1), "rows": n_rows, "tflops": round(flops / t_us / 1e6, 1),
             "frac_of_bf16_peak": None if tf_peak is None else round(flops / t_us / 1e6 / tf_peak, 4),
             "gbs": round(n_rows * (D * 2 + cfg.L) / t_us / 1e3, 1),
-            "note": "sk_hash_keys_tc incl. its plane-norm, fix-up and gate launches; not in the step"}
+            "note": "sk_hash_keys_tc incl. its fix-up and gate launches; not in the step"}
         # the whole prefill cache write (copy K/V + v_norm + codes) of S tokens; the tokens are the
         # cache's own first S rows, so the cache is left unchanged
         S_pf = min(T0, 8192)

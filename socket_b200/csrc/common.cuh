@@ -40,6 +40,10 @@ __device__ __forceinline__ uint32_t order_key(float f) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+__device__ __forceinline__ float order_key_inverse(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
 __device__ __forceinline__ int effective_len(int64_t T, const int32_t* T_dev) {
     int64_t t = T;
     if (T_dev != nullptr) {

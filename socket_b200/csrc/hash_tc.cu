@@ -94,7 +94,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 constexpr int TC_STAGES = 2;          // accumulators in tensor memory
-constexpr int TC_ARING = 4;           // K tiles in flight (the TMA round trip is longer than two tiles' work)
+constexpr int TC_ARING = 4;           // K tiles in flight
 constexpr int TC_NSLOTS = 8;          // norm slots
 constexpr int TC_NORM_WARPS = 4;      // one thread per row of the K tile
 constexpr int TC_EPI_WARPS = 16;      // four threads per accumulator row, 64 columns each

@@ -23,9 +23,7 @@ namespace {
 // Shared memory after the table: mbarrier | per-head sample statistics for the filter mode.
 struct FilterShared {
     uint64_t bar;
-    float red_min[4][SC_WARPS], red_max[4][SC_WARPS];
-    float fmin[4], scale[4], cut[4];
-    uint32_t hist[4][256];
+    float warp_stat[4][SC_WARPS];          // per head: every warp's order statistic of its sample
 };
 
 struct FilterArgs {
@@ -36,92 +34,71 @@ struct FilterArgs {
     float frac;
 };
 
-// Per-head cut from one sample score per thread (sv[j], `valid`): block-wide min / max, a
-// 256-bin value histogram, and the bin boundary that about frac of the sample exceeds.  The cuts
-// end up in fs.cut[] (all threads read them after the trailing barrier) and, for the select
-// kernel's check, in cut_out[j * cut_stride].  Must be called by the whole CTA.
+// Per-head cut from one sample score per thread (sv[j], `valid`), chosen so that about `frac` of
+// the keys exceed it.  Every warp finds an order statistic of its own 32 samples - the t-th largest,
+// t = frac * 33 + 0.5, interpolated between two neighbouring ranks - with a few rounds of
+// redux-max, and the cut is the mean of the warps' values: one barrier, no histogram.  Any value
+// would be correct (the select kernel proves or repairs the result); this one only has to be close.
+// The cuts are returned in cut[] and, for the select kernel's check, written to cut_out[j * cut_stride].
+// Must be called by the whole CTA.
 template <int HT>
 __device__ __forceinline__ void filter_cuts(FilterShared& fs, const float (&sv)[HT], bool valid, float frac,
-                                            float* __restrict__ cut_out, size_t cut_stride) {
+                                            float* __restrict__ cut_out, size_t cut_stride, float (&cut)[HT]) {
+    static_assert(SC_WARPS == 32, "one lane per warp in the final mean");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float t = frac * 33.0f + 0.5f;                  // wanted rank among 32 samples (1 = the largest)
+    const int r_lo = max(1, min(31, (int)t));
+    const float w = fminf(fmaxf(t - (float)r_lo, 0.f), 1.f);
+    uint32_t key[HT], s_lo[HT], s_hi[HT];
 #pragma unroll
     for (int j = 0; j < HT; ++j) {
         const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
-        float lo = fin ? sv[j] : INFINITY, hi = fin ? sv[j] : -INFINITY;
+        key[j] = fin ? order_key(sv[j]) : 0u;             // 0 = no sample (below every finite score's key)
+        s_lo[j] = s_hi[j] = 0u;
+    }
+    for (int r = 1; r <= r_lo + 1; ++r) {                 // uniform trip count
 #pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) {
-            lo = fminf(lo, __shfl_xor_sync(FULL, lo, o));
-            hi = fmaxf(hi, __shfl_xor_sync(FULL, hi, o));
-        }
-        if (lane == 0) {
-            fs.red_min[j][warp] = lo;
-            fs.red_max[j][warp] = hi;
+        for (int j = 0; j < HT; ++j) {
+            const uint32_t mx = __reduce_max_sync(FULL, key[j]);
+            if (r == r_lo) s_lo[j] = mx;
+            if (r == r_lo + 1) s_hi[j] = mx;
+            const unsigned who = __ballot_sync(FULL, key[j] == mx);
+            if (lane == __ffs(who) - 1) key[j] = 0u;      // take one instance out
         }
     }
-    __syncthreads();
-    if (warp < HT) {
-        float lo = fs.red_min[warp][lane], hi = fs.red_max[warp][lane];
+    if (lane == 0) {
 #pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) {
-            lo = fminf(lo, __shfl_xor_sync(FULL, lo, o));
-            hi = fmaxf(hi, __shfl_xor_sync(FULL, hi, o));
-        }
-        if (lane == 0) {
-            fs.fmin[warp] = lo;
-            fs.scale[warp] = hi > lo ? 254.0f / (hi - lo) : 0.f;
+        for (int j = 0; j < HT; ++j) {
+            // a warp with fewer than r_lo + 1 samples contributes nothing
+            fs.warp_stat[j][warp] = (s_hi[j] != 0u)
+                                        ? (1.f - w) * order_key_inverse(s_lo[j]) + w * order_key_inverse(s_hi[j])
+                                        : NAN;
         }
     }
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < HT; ++j) {
-        const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
-        const uint32_t bin = min(__float2uint_rz((sv[j] - fs.fmin[j]) * fs.scale[j]), 255u);
-        warp_hist_add(fs.hist[j], fin ? bin : 0u, fin);
+        const float v = fs.warp_stat[j][lane];
+        const bool have = v == v;
+        const int n = __popc(__ballot_sync(FULL, have));
+        float sum = have ? v : 0.f;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(FULL, sum, o);
+        cut[j] = n > 0 ? sum / (float)n : -INFINITY;      // no usable sample: keep everything
     }
-    __syncthreads();
-    if (warp < HT) {
-        // bins in descending order, 8 per lane
-        uint32_t c[8], local = 0;
+    if (threadIdx.x < HT) {
+        float mine = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            c[i] = fs.hist[warp][255 - (8 * lane + i)];
-            local += c[i];
-        }
-        uint32_t inc = local;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t n = __shfl_up_sync(FULL, inc, o);
-            if (lane >= o) inc += n;
-        }
-        const uint32_t n_samp = __shfl_sync(FULL, inc, 31);
-        uint32_t target = (uint32_t)ceilf(frac * (float)n_samp) + 4u;
-        if (target > n_samp) target = n_samp;
-        uint32_t before = inc - local;
-        int found = -1;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (target > 0 && before < target && before + c[i] >= target) found = 255 - (8 * lane + i);
-            before += c[i];
-        }
-        // exactly one lane finds the bin (none if the sample is empty)
-        const unsigned who = __ballot_sync(FULL, found >= 0);
-        float cut = -INFINITY;       // empty or degenerate sample: keep everything
-        if (who) {
-            const int bin = __shfl_sync(FULL, found, __ffs(who) - 1);
-            if (fs.scale[warp] > 0.f && bin >= 1) cut = fs.fmin[warp] + (float)bin / fs.scale[warp];
-        }
-        if (lane == 0) {
-            fs.cut[warp] = cut;
-            cut_out[(size_t)warp * cut_stride] = cut;
-        }
+        for (int j = 0; j < HT; ++j)
+            if (j == (int)threadIdx.x) mine = cut[j];
+        cut_out[(size_t)threadIdx.x * cut_stride] = mine;
     }
-    __syncthreads();
 }
 
 // L: tables per key (bytes per key), HT: query heads per table word.
 // FILTER = false: every score is written to `scores`.
 // FILTER = true:  nothing is written for most keys.  Each CTA estimates, per head, a cut from
-//   the first 32 keys of each of its warps (a value histogram of up to 1024 scores) that about
+//   the first 32 keys of each of its warps (the mean of the warps' order statistics) that about
 //   `frac` of the keys exceed, and every warp appends the (score, index) pairs >= cut to its own
 //   run of the row's candidate buffer — runs are ordered (chunk, warp, index), so the candidates
 //   of a row are in ascending index order without atomics.  The select kernel checks that the
@@ -215,9 +192,6 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             if (threadIdx.x == 0) request_table(g);
         }
         in_flight = false;
-        if (FILTER) {
-            for (int i = threadIdx.x; i < 4 * 256; i += SC_THREADS) (&fs.hist[0][0])[i] = 0;
-        }
 
         // each warp owns a contiguous run of keys (a multiple of 32 long)
         const int per_warp = (int)(((t1_raw - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32);
@@ -234,14 +208,17 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         const __half* vg = v_norm + (size_t)bk * Tcap;
 
         uint4 cur[NV], nxt[NV];
+        __half vcur = __float2half(0.f), vnxt = __float2half(0.f);   // ||v|| travels with the codes
         int t = ws + lane;
         if (t < we) {
 #pragma unroll
             for (int i = 0; i < NV; ++i) cur[i] = __ldcg(cg + (size_t)t * NV + i);
+            vcur = __ldcg(vg + t);
         }
         if (t + 32 < we) {
 #pragma unroll
             for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cg + (size_t)(t + 32) * NV + i);
+            vnxt = __ldcg(vg + t + 32);
         }
 
         const bool ok = mbar_wait(bar, phase);
@@ -262,22 +239,20 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         const int run_index0 = FILTER ? (((int)row0 * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w : 0;
 
         if (FILTER) {
-            // ---- sample = first key of every lane: scores, min / max, histogram, cut
+            // ---- sample = first key of every lane: scores, cut
             float sv[HT];
             const bool valid = t < we;
             if (valid) {
                 float acc[HT];
                 score_key<L, HT>(cur, lut_s, sel_lo, sel_hi, mL, acc);
-                const float vn = __half2float(__ldcg(vg + t));
+                const float vn = __half2float(vcur);
 #pragma unroll
                 for (int j = 0; j < HT; ++j) sv[j] = acc[j] * vn;
             } else {
 #pragma unroll
                 for (int j = 0; j < HT; ++j) sv[j] = 0.f;
             }
-            filter_cuts<HT>(fs, sv, valid, fa.frac, fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max);
-#pragma unroll
-            for (int j = 0; j < HT; ++j) cutv[j] = fs.cut[j];
+            filter_cuts<HT>(fs, sv, valid, fa.frac, fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
             // the sample keys themselves
 #pragma unroll
             for (int j = 0; j < HT; ++j) {
@@ -300,9 +275,11 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             t += 32;
 #pragma unroll
             for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
+            vcur = vnxt;
             if (t + 32 < we) {
 #pragma unroll
                 for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cg + (size_t)(t + 32) * NV + i);
+                vnxt = __ldcg(vg + t + 32);
             }
         }
         for (; t - lane < we; t += 32) {
@@ -311,7 +288,7 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             if (valid) {
                 float acc[HT];
                 score_key<L, HT>(cur, lut_s, sel_lo, sel_hi, mL, acc);
-                const float vn = __half2float(__ldcg(vg + t));
+                const float vn = __half2float(vcur);
 #pragma unroll
                 for (int j = 0; j < HT; ++j) sv[j] = acc[j] * vn;
             }
@@ -339,9 +316,11 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             }
 #pragma unroll
             for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
+            vcur = vnxt;
             if (t + 64 < we) {
 #pragma unroll
                 for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cg + (size_t)(t + 64) * NV + i);
+                vnxt = __ldcg(vg + t + 64);
             }
         }
         if (FILTER && lane == 0) {
