@@ -24,6 +24,7 @@ namespace {
 struct FilterShared {
     uint64_t bar;
     float warp_stat[4][SC_WARPS];          // per head: every warp's order statistic of its sample
+    float margin;                          // extra rank for short segments, see filter_cuts
 };
 
 struct FilterArgs {
@@ -39,6 +40,9 @@ struct FilterArgs {
 // t = frac * 33 + 0.5, interpolated between two neighbouring ranks - with a few rounds of
 // redux-max, and the cut is the mean of the warps' values: one barrier, no histogram.  Any value
 // would be correct (the select kernel proves or repairs the result); this one only has to be close.
+// With few sampling warps (a short segment) the mean is noisy and a cut above the row's k-th
+// score sends the row to the rescoring path, so the rank is moved down by `margin` =
+// 4 / (warps holding keys) - 4 / 32: as if 4 more samples of the chunk were kept.
 // The cuts are returned in cut[] and, for the select kernel's check, written to cut_out[j * cut_stride].
 // Must be called by the whole CTA.
 template <int HT>
@@ -46,7 +50,8 @@ __device__ __forceinline__ void filter_cuts(FilterShared& fs, const float (&sv)[
                                             float* __restrict__ cut_out, size_t cut_stride, float (&cut)[HT]) {
     static_assert(SC_WARPS == 32, "one lane per warp in the final mean");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float t = frac * 33.0f + 0.5f;                  // wanted rank among 32 samples (1 = the largest)
+    // wanted rank among 32 samples (1 = the largest)
+    const float t = frac * 33.0f + 0.5f + fs.margin;      // (written before the CTA's last barrier)
     const int r_lo = max(1, min(31, (int)t));
     const float w = fminf(fmaxf(t - (float)r_lo, 0.f), 1.f);
     uint32_t key[HT], s_lo[HT], s_hi[HT];
@@ -221,6 +226,9 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             vnxt = __ldcg(vg + t + 32);
         }
 
+        // 4 / (warps that hold keys of this segment) - 4 / 32, without the rounding up
+        if (FILTER && threadIdx.x == 0)
+            fs.margin = fmaxf(fminf(4.0f * (float)per_warp / (float)(int)(t1 - t0), 4.0f) - 0.125f, 0.f);
         const bool ok = mbar_wait(bar, phase);
         phase ^= 1u;
         if (!__syncthreads_and(ok)) {

@@ -535,6 +535,33 @@ def test_fused_score_select_falls_back_exactly_on_hostile_rows():
     assert codes_equal >= 0
 
 
+@pytest.mark.parametrize("T", [131072 + 55, 131072 + 105, 131072 - 1, 130000])
+def test_fused_score_select_short_segments_stay_on_the_candidate_path(T):
+    # context lengths at which scorer CTAs straddle a KV-head boundary with a few hundred keys on
+    # one side: the cut of such a short segment comes from one or two warps' samples and must still
+    # stay below the row's k-th score
+    assert _fused_vs_two_step(4, 32, 8, T, 2048, 64, 256, seed=T) == 0
+
+
+def test_fused_score_select_long_runs():
+    # >= 128 keys per scorer warp, benign and hostile score layouts
+    T = 140000
+    n0 = _fused_vs_two_step(1, 8, 2, T, 1024, 8, 24, seed=11)
+    assert n0 == 0
+    ramp = (1.0 + 6.0 * torch.arange(T) / T).to(torch.float16)
+    n1 = _fused_vs_two_step(1, 8, 2, T, 512, 4, 4, v_norm=ramp.expand(1, 2, T), seed=12)
+    block = torch.ones(T)
+    block[60000:66000] = 50.0
+    n2 = _fused_vs_two_step(1, 8, 2, T, 1024, 4, 4, v_norm=block.to(torch.float16).expand(1, 2, T), seed=13)
+    assert n1 + n2 > 0
+    # tiny and huge weights side by side: bounds in the half-precision subnormal range and near its top
+    g = torch.Generator().manual_seed(14)
+    mixed = torch.where(torch.rand(1, 2, T, generator=g) < 0.5, torch.full((1, 2, T), 3e-5),
+                        torch.full((1, 2, T), 900.0)).to(torch.float16)
+    _fused_vs_two_step(1, 8, 2, T, 700, 2, 2, v_norm=mixed, seed=15)
+    _fused_vs_two_step(2, 32, 8, 300000, 2048, 64, 256, seed=16)
+
+
 def test_fused_score_select_device_length_and_capacity():
     T_live, Tcap = 30000, 33000
     g = torch.Generator().manual_seed(9)
