@@ -133,18 +133,23 @@ struct ScorePlan {
 constexpr int SC_THREADS = 1024;
 constexpr int SC_WARPS = SC_THREADS / 32;
 constexpr int SEL_CAP = 16384;   // candidates the select kernel can hold on chip
+constexpr int64_t SC_SWITCH_PAD = 3584;   // empty slots after each group in the flat split, see make_score_plan
 
 inline ScorePlan make_score_plan(int n_groups, int64_t T, int64_t M) {
     ScorePlan p;
     const int n_sm = 148;
     const int64_t total = (int64_t)n_groups * T;
     if (total / n_sm >= 16384) {
-        // large: split the flat (group, key) space evenly; a CTA may cross one group boundary
-        p.Tslots = T;
-        p.per_cta = (total + n_sm - 1) / n_sm;
+        // large: split the flat (group, key) space evenly; a CTA may cross one group boundary.
+        // Crossing costs a second table load, sample and cut - about what 3.5 K keys cost (measured:
+        // 128K context, 91.5 us without padding, 87.2 us with 3-4 K, 89.9 us with 8 K) - so every
+        // group ends with that many empty slots: the CTA that crosses gets fewer keys
+        p.Tslots = T + SC_SWITCH_PAD;
+        const int64_t slots = (int64_t)n_groups * p.Tslots;
+        p.per_cta = (slots + n_sm - 1) / n_sm;
         p.per_cta = (p.per_cta + 31) / 32 * 32;
-        p.grid = (total + p.per_cta - 1) / p.per_cta;
-        p.chunks_max = (int)((T + p.per_cta - 1) / p.per_cta) + 1;
+        p.grid = (slots + p.per_cta - 1) / p.per_cta;
+        p.chunks_max = (int)((p.Tslots + p.per_cta - 1) / p.per_cta) + 1;
     } else {
         // small: whole CTAs per group, no CTA loads two tables
         int64_t chunks = n_groups >= n_sm ? 1 : n_sm / n_groups;
