@@ -91,13 +91,16 @@ __device__ __forceinline__ void soft_hash_body(
         for (int i = threadIdx.x; i < P * R; i += SH_THREADS) pr_s[i] = protos_T[i];
     }
     const float inv_sqrt_d = 1.0f / fmaxf(sqrtf((float)D), 1e-6f);
+    // lane p keeps the p-th dot product, so the P tanh evaluations run side by side
+    float mine = 0.f;
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
         if (p < P) {
             const float s = warp_sum_f(part[p]);
-            if (lane == 0) t_s[warp * 16 + p] = tanhf(s) * inv_sqrt_d;
+            if (lane == p) mine = s;
         }
     }
+    if (lane < P) t_s[warp * 16 + lane] = tanhf(mine) * inv_sqrt_d;
     __syncthreads();
 
     if (active) {
