@@ -579,6 +579,9 @@ def finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, roofline,
             "config": workload_config(args, cfg_full, world), "roofline": roofline, "stages": stages,
             "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": clocks,
             "gpu_launches": K * step.n_launches,
+            # (batch, head) rows that took the select kernel's exact-but-slow rescoring path, over
+            # every step this process ran on the timed workspace (warm-up, timed loop, whole-step stage)
+            "rescored_rows": step.rescored_rows(),
         }
         print(json.dumps(line))
     if world > 1:

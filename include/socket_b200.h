@@ -324,6 +324,13 @@ typedef struct sk_decode_params {
 SK_API size_t sk_decode_step_workspace_bytes(int B, int H, int Hkv, int D, int L, int R, int64_t T_max,
                                       int64_t M, int sink, int window);
 SK_API int sk_decode_step(const sk_decode_params* p, void* stream);
+/* Byte offset, inside a workspace of sk_decode_step_workspace_bytes() of the same shape, of an int32
+ * counter: the (batch, head) rows whose candidate set could not be proven complete and that were
+ * rescored in full (an exact but slow path) by the steps run on that workspace so far.  -1 if the
+ * shape's select path keeps no such counter.  The counter starts from whatever the caller put
+ * there (zero the workspace once). */
+SK_API int64_t sk_decode_step_rescored_rows_offset(int B, int H, int Hkv, int D, int L, int R, int64_t T_max,
+                                            int64_t M, int sink, int window);
 
 #ifdef __cplusplus
 }

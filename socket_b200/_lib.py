@@ -80,6 +80,7 @@ SIGNATURES = {
     "sk_sparse_decode_static": (_i, [_p, _i, _p, _p, _i, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _i, _i,
                                      _i, _i, _i64, _p, _p, _p]),
     "sk_decode_step_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i64, _i64, _i, _i]),
+    "sk_decode_step_rescored_rows_offset": (_i64, [_i, _i, _i, _i, _i, _i, _i64, _i64, _i, _i]),
     "sk_decode_step": (_i, [C.POINTER(DecodeParams), _p]),
 }
 

@@ -400,6 +400,16 @@ size_t sk_decode_step_workspace_bytes(int B, int H, int Hkv, int D, int L, int R
     return step_layout(B, H, Hkv, D, L, R, T_max, M, sink, window).total;
 }
 
+int64_t sk_decode_step_rescored_rows_offset(int B, int H, int Hkv, int D, int L, int R, int64_t T_max,
+                                            int64_t M, int sink, int window) {
+    if (B <= 0 || H <= 0 || Hkv <= 0 || T_max <= 0) return -1;
+    const StepLayout lay = step_layout(B, H, Hkv, D, L, R, T_max, M, sink, window);
+    if (!lay.fused) return -1;
+    const int ht = lut_head_tile(H / Hkv);
+    const ScorePlan plan = make_score_plan(B * Hkv * ((H / Hkv) / ht), T_max, M);
+    return (int64_t)(lay.scores + make_fused_layout((int64_t)B * H, plan, T_max).stats);
+}
+
 int sk_decode_step(const sk_decode_params* p, void* stream) {
     SK_REQUIRE(p != nullptr, "sk_decode_step: null params");
     SK_REQUIRE(p->B > 0 && p->H > 0 && p->Hkv > 0 && p->D > 0 && p->L > 0 && p->P > 0 && p->R > 0,

@@ -168,6 +168,8 @@ inline ScorePlan make_score_plan(int n_groups, int64_t T, int64_t M) {
     if (f > 1.0) f = 1.0;
     p.frac = (float)f;
     p.cap_w = (int)((int64_t)(4.0 * f * (double)per_warp + 7) / 8 * 8) + 16;
+    // room for whole runs of short segments (up to 64 keys per warp), which are kept unfiltered
+    if (p.cap_w < 64) p.cap_w = (int)(per_warp < 64 ? per_warp : 64);
     return p;
 }
 // The filtering scorer pays off (and its buffers stay small) only for small k / T.

@@ -24,7 +24,7 @@ namespace {
 struct FilterShared {
     uint64_t bar;
     float warp_stat[4][SC_WARPS];          // per head: every warp's order statistic of its sample
-    float margin;                          // extra rank for short segments, see filter_cuts
+    int warp_full[SC_WARPS];               // the warp's sample has all 32 keys
 };
 
 struct FilterArgs {
@@ -40,9 +40,9 @@ struct FilterArgs {
 // t = frac * 33 + 0.5, interpolated between two neighbouring ranks - with a few rounds of
 // redux-max, and the cut is the mean of the warps' values: one barrier, no histogram.  Any value
 // would be correct (the select kernel proves or repairs the result); this one only has to be close.
-// With few sampling warps (a short segment) the mean is noisy and a cut above the row's k-th
-// score sends the row to the rescoring path, so the rank is moved down by `margin` =
-// 4 / (warps holding keys) - 4 / 32: as if 4 more samples of the chunk were kept.
+// (Short segments - at most 1024 keys and half a CTA's share - never get here: with so few sampling
+// warps the mean is noisy, and a cut above the row's k-th score sends the row to the rescoring path,
+// so they keep every key.)
 // The cuts are returned in cut[] and, for the select kernel's check, written to cut_out[j * cut_stride].
 // Must be called by the whole CTA.
 template <int HT>
@@ -51,7 +51,7 @@ __device__ __forceinline__ void filter_cuts(FilterShared& fs, const float (&sv)[
     static_assert(SC_WARPS == 32, "one lane per warp in the final mean");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // wanted rank among 32 samples (1 = the largest)
-    const float t = frac * 33.0f + 0.5f + fs.margin;      // (written before the CTA's last barrier)
+    const float t = frac * 33.0f + 0.5f;
     const int r_lo = max(1, min(31, (int)t));
     const float w = fminf(fmaxf(t - (float)r_lo, 0.f), 1.f);
     uint32_t key[HT], s_lo[HT], s_hi[HT];
@@ -71,7 +71,9 @@ __device__ __forceinline__ void filter_cuts(FilterShared& fs, const float (&sv)[
             if (lane == __ffs(who) - 1) key[j] = 0u;      // take one instance out
         }
     }
+    const bool full = __all_sync(FULL, valid);
     if (lane == 0) {
+        fs.warp_full[warp] = full ? 1 : 0;
 #pragma unroll
         for (int j = 0; j < HT; ++j) {
             // a warp with fewer than r_lo + 1 samples contributes nothing
@@ -81,10 +83,14 @@ __device__ __forceinline__ void filter_cuts(FilterShared& fs, const float (&sv)[
         }
     }
     __syncthreads();
+    // a warp with a partial sample (the last one of a short segment) reports a lower quantile - with
+    // barely r_lo + 1 keys, about its minimum - and would drag the mean down until the runs
+    // overflow: it only counts when no warp has a full sample
+    const bool any_full = __any_sync(FULL, fs.warp_full[lane] != 0);
 #pragma unroll
     for (int j = 0; j < HT; ++j) {
         const float v = fs.warp_stat[j][lane];
-        const bool have = v == v;
+        const bool have = v == v && (!any_full || fs.warp_full[lane] != 0);
         const int n = __popc(__ballot_sync(FULL, have));
         float sum = have ? v : 0.f;
 #pragma unroll
@@ -226,9 +232,6 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             vnxt = __ldcg(vg + t + 32);
         }
 
-        // 4 / (warps that hold keys of this segment) - 4 / 32, without the rounding up
-        if (FILTER && threadIdx.x == 0)
-            fs.margin = fmaxf(fminf(4.0f * (float)per_warp / (float)(int)(t1 - t0), 4.0f) - 0.125f, 0.f);
         const bool ok = mbar_wait(bar, phase);
         phase ^= 1u;
         if (!__syncthreads_and(ok)) {
@@ -260,7 +263,15 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
 #pragma unroll
                 for (int j = 0; j < HT; ++j) sv[j] = 0.f;
             }
-            filter_cuts<HT>(fs, sv, valid, fa.frac, fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
+            // a short segment (the newest keys of a partly filled chunk, or the few keys a CTA has on
+            // one side of a KV-head boundary) keeps everything when its runs have the room
+            // (at most half a CTA's share: a whole chunk of a small problem goes the normal way, where
+            // every one of its keys is a sample)
+            if (t1 - t0 <= 1024 && 2 * (t1 - t0) <= slots_per_cta && per_warp <= fa.cap_w) {   // uniform across the CTA
+                if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
+            } else {
+                filter_cuts<HT>(fs, sv, valid, fa.frac, fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
+            }
             // the sample keys themselves
 #pragma unroll
             for (int j = 0; j < HT; ++j) {

@@ -360,5 +360,15 @@ class DecodeStep:
         if select_path == "cluster" or (select_path == "auto" and cluster and not fused):
             self.n_launches -= 1          # scorer and select are one launch
 
+        self._rescored_off = int(lib().sk_decode_step_rescored_rows_offset(B, H, Hkv, D, L, R, T_max, topk,
+                                                                           sink, window))
+
     def run(self) -> None:
         check(lib().sk_decode_step(C.byref(self.params), stream_ptr(self.device)), "sk_decode_step")
+
+    def rescored_rows(self) -> Optional[int]:
+        """Rows that went through the select kernel's full rescoring path in the steps run so far
+        (None if this shape's path keeps no count).  Synchronises."""
+        if self._rescored_off < 0:
+            return None
+        return int(self.workspace[self._rescored_off:self._rescored_off + 4].view(torch.int32).item())
