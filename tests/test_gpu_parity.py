@@ -351,6 +351,43 @@ def test_model_flow_decode_step_matches_reference():
     assert int(step.status) == 0
 
 
+def test_steps_across_a_partly_filled_chunk_never_rescore():
+    """While the context grows through a scorer chunk, that chunk holds a handful of keys, then a few
+    hundred: at every fill level its cut must stay below each row's k-th score and its runs must not
+    overflow, or the row drops to the select kernel's rescoring path (exact, but many times slower)."""
+    B, H, Hkv, M, sink, window = 1, 32, 8, 1024, 64, 128
+    Tcap = 34872                                   # 18 chunks of 1952 slots per KV head; one starts at 33184
+    T0, steps = 33150, 1150
+    inp = make_decode_inputs(B, H, Hkv, T0, seed=1234, dtype=torch.bfloat16)
+    attn = SocketAttention(H, Hkv, 128, heavy_const=M, sink_size=sink, window_size=window,
+                           planes=inp.planes, protos_T=inp.protos_T, dtype=torch.bfloat16, device=DEV)
+    cache = attn.setup_cache(B, Tcap, dtype=torch.bfloat16)
+    k_bshd, v_bshd = inp.k.permute(0, 2, 1, 3), inp.v.permute(0, 2, 1, 3)
+    for s0 in range(0, T0, 8192):
+        s1 = min(T0, s0 + 8192)
+        cache.append(torch.arange(s0, s1, device=DEV), cu(k_bshd[:, s0:s1].contiguous()),
+                     cu(v_bshd[:, s0:s1].contiguous()), attn.planes)
+    g = torch.Generator().manual_seed(77)
+    q_all = cu(torch.randn(steps, B, H, 128, generator=g).to(torch.bfloat16))
+    k_all = cu(torch.randn(steps, B, 1, Hkv, 128, generator=g).to(torch.bfloat16))
+    v_all = cu(torch.randn(steps, B, 1, Hkv, 128, generator=g).to(torch.bfloat16))
+    q = torch.empty(B, H, 128, dtype=torch.bfloat16, device=DEV)
+    kn = torch.empty(B, 1, Hkv, 128, dtype=torch.bfloat16, device=DEV)
+    vn = torch.empty_like(kn)
+    pos = torch.zeros(1, dtype=torch.int64, device=DEV)
+    out = torch.empty_like(q)
+    step = ops.DecodeStep(cache, q, kn, vn, pos, attn.planes, attn.protos_T, out, topk=M, sink=sink,
+                          window=window, T_max=Tcap)
+    assert step.rescored_rows() == 0
+    for i in range(steps):
+        q.copy_(q_all[i]); kn.copy_(k_all[i]); vn.copy_(v_all[i]); pos.fill_(T0 + i)
+        step.run()
+    torch.cuda.synchronize()
+    assert int(step.status) == 0 and int(cache.prefill_len) == T0 + steps
+    assert step.rescored_rows() == 0
+    assert torch.isfinite(out.float()).all()
+
+
 def test_graph_replayed_steps_see_the_newest_token():
     """The step's kernels are chained so that each may start while its predecessor drains.  Replayed
     from a CUDA graph they do overlap, and every replay must still score and attend over the token
