@@ -205,7 +205,9 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         in_flight = false;
 
         // each warp owns a contiguous run of keys (a multiple of 32 long)
-        const int per_warp = (int)(((t1_raw - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32);
+        // (of the LIVE keys of the segment: a partly filled segment still spreads over all warps, so
+        // that its sample comes from 32 warps as soon as it has 1024 keys)
+        const int per_warp = (int)(((t1 - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32);
         const int ws = (int)t0 + warp * per_warp;
         const int we = min((int)t1, ws + per_warp);
         // table order of a key depends on its index only: table = j ^ (t & 7) inside each group of

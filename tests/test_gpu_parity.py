@@ -580,6 +580,30 @@ def test_fused_score_select_short_segments_stay_on_the_candidate_path(T):
     assert _fused_vs_two_step(4, 32, 8, T, 2048, 64, 256, seed=T) == 0
 
 
+@pytest.mark.parametrize("extra", [40, 300, 700, 1500, 5000])
+def test_fused_score_select_live_length_just_past_a_cta_boundary(extra):
+    # 128K-sized problem, flat split: the live length (device value) ends `extra` keys after the start
+    # of some CTA's segment, so that CTA has a short live segment inside a long slot range
+    B, H, Hkv, M, Tcap = 4, 32, 8, 2048, 131072 + 600
+    per_cta = ((32 * (Tcap + 3584) + 147) // 148 + 31) // 32 * 32
+    T_live = 4 * per_cta + extra
+    g = torch.Generator().manual_seed(extra)
+    q = torch.randn(B, H, 128, generator=g)
+    planes = torch.randn(32, 8, 128, generator=g)
+    codes = cu(torch.randint(0, 256, (B, Hkv, Tcap, 32), generator=g, dtype=torch.uint8))
+    vn = cu((torch.rand(B, Hkv, Tcap, generator=g) + 10.5).to(torch.float16))
+    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv, want_probs=False,
+                           want_lut=True)
+    T_dev = torch.tensor(T_live, dtype=torch.int32, device=DEV)
+    got, got_len, ws = ops.score_select_list(lut, codes, vn, H, Tcap, M, 64, 256, T_dev=T_dev)
+    assert int(ws[:4].view(torch.int32).item()) == 0          # no row went through the rescoring path
+    scores = ops.score(lut, codes, vn, H, T_live)
+    want, want_len = ops.select_list(scores, T_live, M, 64, 256)
+    k = want.shape[-1]
+    assert (got_len == k).all()
+    assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values)
+
+
 def test_fused_score_select_long_runs():
     # >= 128 keys per scorer warp, benign and hostile score layouts
     T = 140000
