@@ -187,6 +187,11 @@ def run_reference(args, cfg):
     n = max(1, min(args.steps, 50))
     state = host_state(cfg, args.seed, n + args.warmup)
     from oracle import c_oracle
+    # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1 to its ranks)
+    try:
+        c_oracle.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        c_oracle.set_num_threads(os.cpu_count() or 1)
     per_step, cores, done = cpu_reference_steps(cfg, state, n_steps_cap=n + min(args.warmup, 3))
     val = cfg.batch / per_step
     sample = (f"{done} decode steps of workload {args.workload} (full context, all heads) with the C "
