@@ -165,8 +165,7 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         const int g = (int)(slot / Tslots);
         const int64_t t0 = slot - (int64_t)g * Tslots;
         const int64_t seg_end = min((int64_t)(g + 1) * Tslots, slot_end);
-        const int64_t t1_raw = seg_end - (int64_t)g * Tslots;
-        int64_t t1 = t1_raw;
+        int64_t t1 = seg_end - (int64_t)g * Tslots;
         slot = seg_end;
         if (t1 > Teff) t1 = Teff;
 
