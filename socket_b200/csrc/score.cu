@@ -32,7 +32,7 @@ struct FilterArgs {
     float* cut;          // [rows][chunks_max]
     uint2* cand;         // [rows][chunks_max][32][cap_w]  (score bits, key index)
     int chunks_max, cap_w;
-    float frac;
+    float keep;          // keys the filter aims to keep per row: 3 * M (the fraction follows the LIVE length)
 };
 
 // Per-head cut from one sample score per thread (sv[j], `valid`), chosen so that about `frac` of
@@ -271,7 +271,9 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
             if (t1 - t0 <= 1024 && 2 * (t1 - t0) <= slots_per_cta && per_warp <= fa.cap_w) {   // uniform across the CTA
                 if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
             } else {
-                filter_cuts<HT>(fs, sv, valid, fa.frac, fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
+                // the kept fraction is taken of the live length: the capacity the plan was made for may
+                // be several times larger, and a cut for 3M / capacity would drop needed keys
+                filter_cuts<HT>(fs, sv, valid, fminf(__fdividef(fa.keep, (float)Teff), 1.0f), fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
             }
             // the sample keys themselves
 #pragma unroll
@@ -447,7 +449,7 @@ int launch_score_filter(const float* lut, const uint8_t* codes, const uint16_t* 
     fa.cand = reinterpret_cast<uint2*>(ws + lay.cand);
     fa.chunks_max = plan.chunks_max;
     fa.cap_w = plan.cap_w;
-    fa.frac = plan.frac;
+    fa.keep = plan.frac * (float)T;
 #define SK_SCORE_CASE(LL, HT)                                                                      \
     if (L == LL && ht == HT)                                                                       \
         return score_launch<LL, HT, true>(lut, codes, v_norm, nullptr, B, H, Hkv, R, T, T_dev, Tcap, \

@@ -604,6 +604,28 @@ def test_fused_score_select_live_length_just_past_a_cta_boundary(extra):
     assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values)
 
 
+@pytest.mark.parametrize("B,H,Hkv,Tcap,T_live,M", [(1, 32, 8, 65536, 32768, 1024), (1, 2, 1, 50001, 25592, 512),
+                                                   (2, 8, 2, 40000, 14000, 256)])
+def test_fused_score_select_capacity_well_above_the_live_length(B, H, Hkv, Tcap, T_live, M):
+    # the plan (chunks, run capacity) is made for the capacity; the kept fraction must follow the live
+    # length, or the cut lands above the k-th score and every row is rescored
+    g = torch.Generator().manual_seed(Tcap + M)
+    q = torch.randn(B, H, 128, generator=g)
+    planes = torch.randn(32, 8, 128, generator=g)
+    codes = cu(torch.randint(0, 256, (B, Hkv, Tcap, 32), generator=g, dtype=torch.uint8))
+    vn = cu((torch.rand(B, Hkv, Tcap, generator=g) + 10.5).to(torch.float16))
+    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv, want_probs=False,
+                           want_lut=True)
+    T_dev = torch.tensor(T_live, dtype=torch.int32, device=DEV)
+    got, got_len, ws = ops.score_select_list(lut, codes, vn, H, Tcap, M, 8, 24, T_dev=T_dev)
+    assert int(ws[:4].view(torch.int32).item()) == 0
+    scores = ops.score(lut, codes, vn, H, T_live)
+    want, want_len = ops.select_list(scores, T_live, M, 8, 24)
+    k = want.shape[-1]
+    assert (got_len == k).all()
+    assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values)
+
+
 def test_fused_score_select_long_runs():
     # >= 128 keys per scorer warp, benign and hostile score layouts
     T = 140000
