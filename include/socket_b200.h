@@ -313,7 +313,11 @@ typedef struct sk_decode_params {
     int q_dtype, kv_dtype, plane_dtype;
     int B, H, Hkv, D, L, P, R;
     int64_t Tcap;
-    int64_t T_max;         /* upper bound of the live length during this call */
+    int64_t T_max;         /* upper bound of the live length during this call.  Grids, chunks and
+                            * candidate capacities are sized from it: keep it within about 4x of
+                            * the live length (the result is exact either way, but far below that
+                            * rows start to take the slow rescoring path, see
+                            * sk_decode_step_rescored_rows_offset) */
     int64_t M;
     int sink, window;
     /* how the list is built: SK_SELECT_AUTO picks the fastest path the shape allows; the others pin
