@@ -41,8 +41,8 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None where no capture of that kernel/workload exists yet.
 NCU_TRAFFIC = {
-    ("score_filter", "c2"): 10011648, ("select_candidates", "c2"): 2238720, ("sparse_decode", "c2"): 13187584,
-    ("score_filter", "c3"): 154151424, ("select_candidates", "c3"): 8300288, ("sparse_decode", "c3"): 117576448,
+    ("score_filter", "c2"): 10011648, ("select_candidates", "c2"): 2239232, ("sparse_decode", "c2"): 13187072,
+    ("score_filter", "c3"): 158364928, ("select_candidates", "c3"): 8302592, ("sparse_decode", "c3"): 118857984,
     ("score_select_cluster", "c2"): 10066176,
 }
 
