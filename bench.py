@@ -1,6 +1,13 @@
 """Benchmark of the sparse-attention decode path (one layer, one decode step per "step").
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c2] [--impl reference]
+
+Default workload: the 128K long-context configuration (`c3`: batch 4, 32 query / 8 KV heads,
+context 131072, top-k 2048 + 64 + 256).  With N > 1 GPUs its 8 KV heads are split over the ranks
+(8/N KV heads and 32/N query heads per GPU, the split GPT-FAST/tp.py:124-137,143-148 makes), so
+the run is strong scaling: every rank works on the same decode step and the slowest rank sets the
+step time.  The 32K configuration (`c2`) is measured in the same process and reported inside the
+same JSON line under "c2".
 
 A step = append+hash one new token, soft-hash the query, score every cached key, select the
 top-k plus sink/window, sparse attention over the selected rows — the body of the reference's
@@ -38,13 +45,17 @@ METRIC = "sparse_attn_decode_tokens_per_s"
 UNIT = "tokens/s/layer"
 FALLBACK_HBM_GBS = 6650.0
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/; None where no capture of that kernel/workload exists yet.
-NCU_TRAFFIC = {
-    ("score_filter", "c2"): 10011648, ("select_candidates", "c2"): 2239232, ("sparse_decode", "c2"): 13187072,
-    ("score_filter", "c3"): 158364928, ("select_candidates", "c3"): 8302592, ("sparse_decode", "c3"): 118857984,
-    ("score_select_cluster", "c2"): 10066176,
-}
+
+
+def ncu_traffic(kernel: str, workload: str):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of `kernel` at `workload`
+    from the ncu captures summarised under profiles/ (profiles/ncu_traffic.json, written next to the
+    summaries); None where no capture of that kernel/workload exists."""
+    try:
+        table = json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json")))
+        return table.get(workload, {}).get(kernel)
+    except Exception:
+        return None
 
 
 def parse_args():
@@ -52,11 +63,13 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default="c2", choices=sorted(PRESETS))
+    ap.add_argument("--workload", default="c3", choices=sorted(PRESETS))
+    ap.add_argument("--secondary", default="c2", choices=sorted(PRESETS) + ["none"],
+                    help="second workload measured in the same process and reported under its own key")
     ap.add_argument("--impl", default="socket_b200", choices=["socket_b200", "reference"])
-    ap.add_argument("--shard", default="weak", choices=["weak", "strong"],
-                    help="N>1: weak = every GPU owns a full set of KV-head groups of the workload; "
-                         "strong = the workload's KV heads are split over the GPUs")
+    ap.add_argument("--shard", default="strong", choices=["weak", "strong"],
+                    help="N>1: strong = the workload's KV heads are split over the GPUs (the reference's "
+                         "tensor-parallel split); weak = every GPU owns a full copy of the workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--skip-stages", action="store_true", help="skip the per-kernel timing loops")
@@ -179,6 +192,7 @@ def host_state(cfg, seed, steps):
     return (k, v, codes, vnorm, planes, inp.protos_T.cpu(), q_all, k_all, v_all)
 
 
+
 def run_reference(args, cfg):
     """`--impl reference`: the reference path's CPU implementation on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -199,8 +213,8 @@ def run_reference(args, cfg):
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": done, "warmup": 1, "ms_per_step": per_step * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": cfg.kv_dtype, "data": "synthetic",
-        "config": workload_config(args, cfg, 1),
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": cfg.kv_dtype,
+        "data": "synthetic", "config": workload_config(args, args.workload, cfg, 1),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -208,49 +222,44 @@ def run_reference(args, cfg):
     print(json.dumps(line))
 
 
-def workload_config(args, cfg, world):
+def workload_config(args, wl, cfg, world):
+    if world == 1:
+        par = "single GPU"
+    elif args.shard == "strong":
+        par = (f"{world} GPUs, the {cfg.n_local_heads} KV heads split {cfg.n_local_heads // world} per GPU "
+               f"({cfg.n_head // world} query heads per GPU); no collective on the attention path")
+    else:
+        par = (f"{world} GPUs, each owning a full copy of the workload's {cfg.n_local_heads} KV-head groups "
+               f"(no collective on the path)")
     return {
-        "workload": f"{args.workload}: one layer, batch {cfg.batch}, {cfg.n_head} query / "
+        "workload": f"{wl}: one layer, batch {cfg.batch}, {cfg.n_head} query / "
                     f"{cfg.n_local_heads} KV heads, head_dim {cfg.head_dim}, context {cfg.context}, "
                     f"{cfg.kv_dtype} KV, L={cfg.L} P={cfg.P}, top-k {cfg.topk} + sink {cfg.sink} + "
                     f"window {cfg.window}",
-        "parallelism": ("single GPU" if world == 1 else
-                        (f"{world} GPUs, each owning the workload's {cfg.n_local_heads} KV-head groups "
-                         f"(no collective on the path)" if args.shard == "weak" else
-                         f"{world} GPUs, the {cfg.n_local_heads} KV heads split {cfg.n_local_heads // world} per GPU")),
+        "parallelism": par,
         "l2": "flushed between timed steps (256 MiB write)" if not args.no_flush else "not flushed",
         "timing": "per-step CUDA events around one CUDA-graph launch, summed over the steps",
     }
 
 
 # ------------------------------------------------------------------------------------------
-def main():
-    args = parse_args()
-    cfg_full = PRESETS[args.workload]
-    if args.impl == "reference":
-        run_reference(args, cfg_full)
-        return
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
-
+def measure(args, wl, K, W, world, rank, local_rank, full):
+    """One workload on this rank's GPU: the timed decode loop, the per-kernel stages, the
+    end-to-end loop through the host-memory entry.  `full` adds the bulk-hashing and dense
+    comparison stages.  Returns the fields of the JSON line that belong to the workload."""
     from socket_b200 import ops
     from socket_b200.attention import SocketAttention
     from socket_b200.synth import make_decode_inputs, make_step_inputs
-    from socket_b200 import tp
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
+    cfg_full = PRESETS[wl]
+    split = world > 1 and args.shard == "strong"
+    if split and cfg_full.n_local_heads % world != 0:
+        raise SystemExit(f"{cfg_full.n_local_heads} KV heads do not split over {world} GPUs")
+    cfg = cfg_full.shard_kv_heads(world) if split else cfg_full
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        tp.maybe_init_dist("nccl")
-    cfg = cfg_full.shard_kv_heads(world) if (world > 1 and args.shard == "strong") else cfg_full
 
     dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[cfg.kv_dtype]
     B, H, Hkv, T0, D = cfg.batch, cfg.n_head, cfg.n_local_heads, cfg.context, cfg.head_dim
-    K, W = args.steps, args.warmup
     total_steps = K + W
     Tcap = T0 + 2 * total_steps + 64
     inp = make_decode_inputs(B, H, Hkv, T0, D=D, L=cfg.L, P=cfg.P, seed=args.seed + rank, dtype=dt, device=dev)
@@ -322,17 +331,21 @@ def main():
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     total_ms = float(t.item())
+    clocks = sampler.stop() if sampler is not None else None
     assert int(step.status) == 0, f"device status {int(step.status)}"
-    tokens = B * K * (world if args.shard == "weak" else 1)
+    # split: all ranks work on the same B tokens; replicas: every rank has its own B tokens
+    tokens = B * K * (1 if (split or world == 1) else world)
     value = tokens / (total_ms * 1e-3)
     ms_per_step = total_ms / K
+    res = {"value": value, "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3,
+           "dtype": cfg.kv_dtype, "config": workload_config(args, wl, cfg_full, world), "clocks": clocks,
+           "gpu_launches": K * step.n_launches, "roofline": None, "stages": {}, "e2e": None}
 
     # ---- per-kernel timing (same stream, same flush discipline) --------------------------
     T_now = T0 + total_steps
     peak, peak_src = peak_hbm()
     stages = {}
-    lutbuf = torch.empty(B * H * cfg.L * cfg.R, dtype=torch.float32, device=dev)
-    a_codes = B * Hkv * T_now * cfg.L
+    a_codes = B * Hkv * T_now * cfg.L          # this GPU's share
     a_kv = B * H * cfg.ktot * 2 * D * cfg.kv_bytes()
 
     REP = 8
@@ -371,8 +384,8 @@ def main():
 
     us = {}
     if args.skip_stages:
-        return finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, None, {}, None,
-                      sampler, step, peak, peak_src)
+        res["rescored_rows"] = step.rescored_rows()
+        return res
     from socket_b200._lib import lib, ptr, stream_ptr
     probs, lut = ops.soft_hash(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv, want_probs=False,
                                want_lut=True)
@@ -383,7 +396,7 @@ def main():
     cluster = ops.score_select_cluster_size(B, H, Hkv, cfg.L, cfg.R, Tcap, cfg.topk)
     use_cluster = step.n_launches == 3
     extra = {}
-    if cluster and not use_cluster:
+    if cluster and not use_cluster and full:
         # not the step's path for this shape, timed for comparison only
         lst_c, ln_c = ops.score_select_cluster(lut, cache.k_hard, cache.v_norm, H, T_now, cfg.topk, cfg.sink,
                                                cfg.window)
@@ -422,9 +435,10 @@ def main():
     for name, t_us in us.items():
         gbs = alg[name] / (t_us * 1e-6) / 1e9 if alg[name] else None
         stages[name] = {"us": round(t_us, 2), "algorithmic_bytes": alg[name],
-                        "achieved_gbs": None if gbs is None else round(gbs, 1)}
+                        "achieved_gbs": None if gbs is None else round(gbs, 1),
+                        "frac_of_hbm_peak": None if gbs is None else round(gbs / peak, 4)}
     # prefill hashing of the whole context on the tensor cores (not part of the decode step)
-    if dt == torch.bfloat16 and D == 128 and cfg.L == 32 and cfg.P == 8:
+    if full and dt == torch.bfloat16 and D == 128 and cfg.L == 32 and cfg.P == 8:
         n_rows = B * Hkv * T0
         keys2d = cache.k_cache[:, :, :T0].reshape(-1, D)
         for _ in range(2):
@@ -438,16 +452,19 @@ def main():
         torch.cuda.synchronize()
         t_us = e0.elapsed_time(e1) / 5 * 1e3
         flops = 2.0 * n_rows * D * cfg.L * cfg.P
-        tf_peak = None
+        tf_peak = tf_sus = None
         try:
-            tf_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            tf_peak, tf_sus = float(peaks["bf16_tflops"]), float(peaks.get("bf16_tflops_sustained", 0)) or None
         except Exception:
             pass
         stages["prefill_hash_tc"] = {
             "us": round(t_us, 1), "rows": n_rows, "tflops": round(flops / t_us / 1e6, 1),
             "frac_of_bf16_peak": None if tf_peak is None else round(flops / t_us / 1e6 / tf_peak, 4),
+            "frac_of_bf16_sustained": None if tf_sus is None else round(flops / t_us / 1e6 / tf_sus, 4),
             "gbs": round(n_rows * (D * 2 + cfg.L) / t_us / 1e3, 1),
-            "note": "sk_hash_keys_tc incl. its fix-up and gate launches; not in the step"}
+            "note": "sk_hash_keys_tc incl. its fix-up launch; not in the step"}
+        del keys2d
         # the whole prefill cache write (copy K/V + v_norm + codes) of S tokens; the tokens are the
         # cache's own first S rows, so the cache is left unchanged
         S_pf = min(T0, 8192)
@@ -474,19 +491,20 @@ def main():
             "note": "sk_kv_append_tc: copy + v_norm kernel, then tensor-core hashing; not in the step"}
         del k_pf, v_pf
     # context figure, not on the path: dense attention of the same query over the whole cache
-    # (torch's fused SDPA, a library kernel), i.e. what the sparse path replaces per layer and token
-    try:
-        import torch.nn.functional as F
-        qd = q_s.view(B, Hkv, H // Hkv, D)                         # the rep query heads of a KV head as "rows"
-        kd, vd = cache.k_cache[:, :, :T_now], cache.v_cache[:, :, :T_now]
-        t_dense = time_kernel(lambda: F.scaled_dot_product_attention(qd, kd, vd))
-        dense_bytes = 2 * B * Hkv * T_now * D * cfg.kv_bytes()
-        stages["dense_attention_sdpa"] = {
-            "us": round(t_dense, 2), "algorithmic_bytes": dense_bytes,
-            "achieved_gbs": round(dense_bytes / (t_dense * 1e-6) / 1e9, 1),
-            "note": "torch SDPA over the full context, for comparison; not on the step's path"}
-    except Exception as e:  # a comparison figure must never cost the line
-        stages["dense_attention_sdpa"] = {"us": None, "note": f"unavailable: {e!r}"}
+    # (library kernels), i.e. what the sparse path replaces per layer and token
+    dense_bytes = 2 * B * Hkv * T_now * D * cfg.kv_bytes()
+    if full:
+        try:
+            import torch.nn.functional as F
+            qd = q_s.view(B, Hkv, H // Hkv, D)                         # the rep query heads of a KV head as "rows"
+            kd, vd = cache.k_cache[:, :, :T_now], cache.v_cache[:, :, :T_now]
+            t_dense = time_kernel(lambda: F.scaled_dot_product_attention(qd, kd, vd))
+            stages["dense_attention_sdpa"] = {
+                "us": round(t_dense, 2), "algorithmic_bytes": dense_bytes,
+                "achieved_gbs": round(dense_bytes / (t_dense * 1e-6) / 1e9, 1),
+                "note": "torch SDPA over the full context, for comparison; not on the step's path"}
+        except Exception as e:  # a comparison figure must never cost the line
+            stages["dense_attention_sdpa"] = {"us": None, "note": f"unavailable: {e!r}"[:200]}
     try:
         from flash_attn import flash_attn_with_kvcache           # split-KV dense decode, a library kernel
         qf = q_s.view(B, 1, H, D)
@@ -503,23 +521,50 @@ def main():
     step_gbs = A / (ms_per_step * 1e-3) / 1e9
     stages["whole_step"] = {"us": round(ms_per_step * 1e3, 2), "algorithmic_bytes": A,
                             "achieved_gbs": round(step_gbs, 1), "frac_of_hbm_peak": round(step_gbs / peak, 4),
-                            "frac_of_8tbs": round(step_gbs / 8000.0, 4)}
+                            "frac_of_8tbs": round(step_gbs / 8000.0, 4),
+                            "note": "this GPU's share of the layer-step (its KV heads' codes + gathered rows)"}
+    fa_us = stages.get("dense_attention_flash_decode", {}).get("us")
+    if fa_us:
+        stages["whole_step"]["speedup_vs_dense_flash_decode"] = round(fa_us / (ms_per_step * 1e3), 3)
     for name, t_us in extra.items():
         stages[name] = {"us": round(t_us, 2), "algorithmic_bytes": a_codes,
                         "achieved_gbs": round(a_codes / (t_us * 1e-6) / 1e9, 1), "note": "not on the step's path"}
-    if cluster:
+    if cluster and "score_select_cluster" in stages:
         stages["score_select_cluster"]["cluster_size"] = cluster
     dominant = max((score_name, "sparse_decode", select_name), key=lambda n: us[n])
     dom_alg = alg[dominant] if alg[dominant] else A
     dom_gbs = dom_alg / (us[dominant] * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "kernel": dominant, "achieved": round(dom_gbs, 1), "peak": peak,
-                "unit": "GB/s", "frac": round(dom_gbs / peak, 4), "peak_source": peak_src,
-                "traffic": NCU_TRAFFIC.get((dominant, args.workload))}
+    res["roofline"] = {"bound": "hbm", "kernel": dominant, "achieved": round(dom_gbs, 1), "peak": peak,
+                       "unit": "GB/s", "frac": round(dom_gbs / peak, 4), "peak_source": peak_src,
+                       "traffic": ncu_traffic(dominant, wl) if world == 1 else None,
+                       "per": "GPU" if world > 1 else "launch",
+                       "whole_step_frac": round(step_gbs / peak, 4)}
+    if world > 1:
+        # the one collective that follows the path under tensor parallelism: the sum of the
+        # row-sharded output projection, [B, 1, d_model] bf16 (d_model = all query heads x head_dim)
+        from socket_b200 import tp
+        y = torch.zeros(B, 1, cfg_full.n_head * D, dtype=torch.bfloat16, device=dev)
+        for _ in range(5):
+            tp.all_reduce_sum(y)
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(50):
+            tp.all_reduce_sum(y)
+        e1.record()
+        torch.cuda.synchronize()
+        ar = torch.tensor([e0.elapsed_time(e1) / 50 * 1e3], dtype=torch.float64, device=dev)
+        torch.distributed.all_reduce(ar, op=torch.distributed.ReduceOp.MAX)
+        stages["tp_all_reduce"] = {"us": round(float(ar.item()), 2), "bytes": y.numel() * 2,
+                                   "note": "NCCL all-reduce of the output projection's partial sums; follows "
+                                           "the path under tensor parallelism, not inside the timed step"}
+    res["stages"] = stages
 
     # ---- end to end through the public API with host buffers -----------------------------
     if args.skip_e2e:
-        return finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, roofline, stages, None,
-                      sampler, step, peak, peak_src)
+        res["rescored_rows"] = step.rescored_rows()
+        return res
     n_e2e = min(K, 200)
     # the public host-memory entry: one pinned staging block -> device, the step, the output back
     # to pinned memory, replayed as one graph.  Each step's inputs wait in pinned host memory in the
@@ -551,18 +596,42 @@ def main():
     if world > 1:
         torch.distributed.all_reduce(e2e_t, op=torch.distributed.ReduceOp.MAX)
     e2e_ms_step = float(e2e_t.item())
-    h2d, d2h = hd.h2d_bytes, hd.d2h_bytes
-    e2e = {"value": B * (world if args.shard == "weak" else 1) / (e2e_ms_step * 1e-3), "unit": UNIT,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms_step,
-           "steps": len(e2e_ms)}
-    finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, roofline, stages, e2e, sampler,
-           step, peak, peak_src)
+    res["e2e"] = {"value": B * (1 if (split or world == 1) else world) / (e2e_ms_step * 1e-3), "unit": UNIT,
+                  "h2d_bytes_per_step": hd.h2d_bytes, "d2h_bytes_per_step": hd.d2h_bytes,
+                  "ms_per_step": e2e_ms_step, "steps": len(e2e_ms)}
+    res["rescored_rows"] = step.rescored_rows()
+    return res
 
 
-def finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, roofline, stages, e2e, sampler,
-           step, peak, peak_src):
-    clocks = sampler.stop() if sampler is not None else None
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args, PRESETS[args.workload])
+        return
 
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+
+    from socket_b200 import tp
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        tp.maybe_init_dist("nccl")
+    K, W = args.steps, args.warmup
+
+    res = measure(args, args.workload, K, W, world, rank, local_rank, full=True)
+    torch.cuda.empty_cache()
+    second = None
+    if args.secondary not in ("none", args.workload):
+        wl2 = PRESETS[args.secondary]
+        if not (world > 1 and args.shard == "strong" and wl2.n_local_heads % world):
+            second = measure(args, args.secondary, K, W, world, rank, local_rank, full=False)
+            torch.cuda.empty_cache()
+
+    cfg_full = PRESETS[args.workload]
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
@@ -578,16 +647,21 @@ def finish(args, cfg, cfg_full, world, rank, value, ms_per_step, K, W, roofline,
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3, "higher_is_better": True,
-            "scaling": args.shard, "vs_baseline": None, "dtype": cfg.kv_dtype, "data": "synthetic",
-            "config": workload_config(args, cfg_full, world), "roofline": roofline, "stages": stages,
-            "e2e": e2e, "cpu_baseline": cpu_baseline, "clocks": clocks,
-            "gpu_launches": K * step.n_launches,
+            "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": res["ms_per_step"], "us_per_layer": res["us_per_layer"], "higher_is_better": True,
+            "scaling": "weak" if world == 1 else args.shard, "vs_baseline": None, "dtype": res["dtype"],
+            "data": "synthetic", "config": res["config"], "roofline": res["roofline"], "stages": res["stages"],
+            "e2e": res["e2e"], "cpu_baseline": cpu_baseline, "clocks": res["clocks"],
+            "gpu_launches": res["gpu_launches"],
             # (batch, head) rows that took the select kernel's exact-but-slow rescoring path, over
             # every step this process ran on the timed workspace (warm-up, timed loop, whole-step stage)
-            "rescored_rows": step.rescored_rows(),
+            "rescored_rows": res.get("rescored_rows"),
         }
+        if second is not None:
+            line[args.secondary] = {k: second[k] for k in ("value", "ms_per_step", "us_per_layer", "config",
+                                                            "roofline", "stages", "e2e", "clocks", "gpu_launches",
+                                                            "rescored_rows") if k in second}
+            line[args.secondary]["unit"] = UNIT
         print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()

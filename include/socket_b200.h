@@ -257,7 +257,9 @@ SK_API int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, con
  *     buffer are rejected with SK_ERR_WORKSPACE and a message naming both sizes; nothing is
  *     enqueued.  The buffer covers e.g. B*H = 128 rows with lists of a few thousand entries.
  *   - the first call on each device looks up the buffer's device address (with that device
- *     current); make that first call outside any stream capture.
+ *     current); make that first call outside any stream capture.  The address is kept for
+ *     the life of the process: after a cudaDeviceReset of that device it is stale, so a
+ *     process that resets a device must not call this entry point on it again.
  *   - all calls on a device share the one buffer: calls that can overlap on the GPU (two
  *     streams, two threads) race on it.  Serialise them, or use sk_sparse_decode with
  *     separate workspaces.  Each call clears the ticket counters it uses before its kernel.

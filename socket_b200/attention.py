@@ -98,6 +98,7 @@ class SocketAttention(nn.Module):
         self.register_buffer("protos_T", protos_T.to(device=device, dtype=torch.float32))
         self.kv_cache: Optional[KVCache] = None
         self._step = None
+        self._stage = None
 
     def setup_cache(self, max_batch_size: int, max_seq_length: int, dtype=torch.bfloat16) -> KVCache:
         self.kv_cache = KVCache(max_batch_size, max_seq_length, self.n_local_heads, self.head_dim,
@@ -135,15 +136,34 @@ class SocketAttention(nn.Module):
         if input_pos.dtype != torch.long:
             input_pos = input_pos.long()
         if out is None:
-            out = torch.empty_like(q_bhd)
+            out = torch.empty(q_bhd.shape, dtype=q_bhd.dtype, device=q_bhd.device)
         Tcap = cache.k_cache.shape[2]
-        key = (q_bhd.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), input_pos.data_ptr(), out.data_ptr())
-        if self._step is None or self._step[0] != key:
-            step = ops.DecodeStep(cache, q_bhd.contiguous(), k_new.contiguous(), v_new.contiguous(),
-                                  input_pos, self.planes, self.protos_T, out, topk=self.heavy_const,
-                                  sink=self.sink_size, window=self.window_size, T_max=Tcap,
-                                  temperature=self.temperature)
+        # The step holds raw addresses.  Contiguous inputs are read in place; a non-contiguous one
+        # (the reference flow hands over `v` as a view of the fused QKV projection) is copied, on
+        # every call, into a staging tensor that lives as long as the step does - never into a
+        # temporary behind the address cache.
+        ins = [q_bhd, k_new, v_new]
+        if self._stage is None or any(s.shape != t.shape or s.dtype != t.dtype or s.device != t.device
+                                      for s, t in zip(self._stage, ins)):
+            self._stage = [torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in ins]
+            self._step = None
+        src = []
+        for t, s in zip(ins, self._stage):
+            if t.is_contiguous():
+                src.append(t)
+            else:
+                s.copy_(t)
+                src.append(s)
+        key = tuple(t.data_ptr() for t in src) + (input_pos.data_ptr(), out.data_ptr())
+        if self._step is None:
+            step = ops.DecodeStep(cache, src[0], src[1], src[2], input_pos, self.planes, self.protos_T, out,
+                                  topk=self.heavy_const, sink=self.sink_size, window=self.window_size,
+                                  T_max=Tcap, temperature=self.temperature)
             self._step = (key, step)
+        elif self._step[0] != key:
+            # other tensors of the same shapes: new addresses, same scratch memory
+            self._step[1].rebind(src[0], src[1], src[2], input_pos, out)
+            self._step = (key, self._step[1])
         self._step[1].run()
         return out
 

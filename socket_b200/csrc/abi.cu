@@ -1,4 +1,5 @@
 // extern "C" entry points: argument validation, workspace carving, kernel launches.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -24,6 +25,24 @@ int fail(int status, const char* fmt, ...) {
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
     return status;
+}
+
+int sm_count() {
+    constexpr int MAX_DEV = 64;
+    static std::atomic<int> cached[MAX_DEV];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) {
+        cudaGetLastError();   // a size query without a device is not an error of the next launch
+        return 148;
+    }
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        return 148;
+    }
+    cached[dev].store(n, std::memory_order_relaxed);
+    return n;
 }
 
 int check_launch(const char* what) {
@@ -425,6 +444,37 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
     SK_REQUIRE(p->k_new == nullptr || p->input_pos != nullptr, "sk_decode_step: input_pos missing");
     SK_REQUIRE((p->list == nullptr) == (p->list_len == nullptr), "sk_decode_step: list and list_len go together");
     SK_ALIGNED(p->workspace, 256, "sk_decode_step: workspace");
+    // Everything the chain can refuse is refused here, before the first launch: a step either runs
+    // whole or leaves the cache untouched.  The kernels use 16-byte loads and asynchronous copies
+    // on q, the new rows, the caches, the codes and the output.
+    SK_REQUIRE(valid_dtype(p->q_dtype) && valid_dtype(p->kv_dtype) && valid_dtype(p->plane_dtype),
+               "sk_decode_step: bad dtype");
+    SK_ALIGNED(p->q, 16, "sk_decode_step: q");
+    SK_ALIGNED(p->k_cache, 16, "sk_decode_step: k_cache");
+    SK_ALIGNED(p->v_cache, 16, "sk_decode_step: v_cache");
+    SK_ALIGNED(p->codes, 16, "sk_decode_step: codes");
+    SK_ALIGNED(p->out, 16, "sk_decode_step: out");
+    SK_ALIGNED(p->v_norm, 2, "sk_decode_step: v_norm");
+    SK_ALIGNED(p->prefill_len, 4, "sk_decode_step: prefill_len");
+    SK_ALIGNED(p->protos_T, 4, "sk_decode_step: protos_T");
+    SK_ALIGNED(p->planes, 16, "sk_decode_step: planes");
+    if (p->k_new != nullptr) {
+        SK_ALIGNED(p->k_new, 16, "sk_decode_step: k_new");
+        SK_ALIGNED(p->v_new, 16, "sk_decode_step: v_new");
+        SK_ALIGNED(p->input_pos, 8, "sk_decode_step: input_pos");
+    }
+    if (p->list != nullptr) {
+        SK_ALIGNED(p->list, 4, "sk_decode_step: list");
+        SK_ALIGNED(p->list_len, 4, "sk_decode_step: list_len");
+    }
+    if (p->D != 128)
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: head_dim %d not supported (128)", p->D);
+    if (!((p->q_dtype == p->kv_dtype) || (p->q_dtype == SK_F32 && p->kv_dtype == SK_BF16)))
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: unsupported q/kv dtype pair (%d,%d)", p->q_dtype, p->kv_dtype);
+    if (!score_shape_supported(p->L, lut_head_tile(p->H / p->Hkv), p->R))
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: L=%d with %d query heads per KV head (R=%d) not supported "
+                                        "by the scorer", p->L, p->H / p->Hkv, p->R);
+    SK_REQUIRE((int64_t)p->B * p->H < 65535, "sk_decode_step: B*H must stay below 65535");
     const StepLayout lay = step_layout(p->B, p->H, p->Hkv, p->D, p->L, p->R, p->T_max, p->M, p->sink, p->window);
     if (p->workspace_bytes < lay.total)
         return fail(SK_ERR_WORKSPACE, "sk_decode_step: workspace %zu < %zu bytes", p->workspace_bytes, lay.total);

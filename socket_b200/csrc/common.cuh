@@ -15,6 +15,9 @@ constexpr unsigned FULL = 0xffffffffu;
 // ---------------------------------------------------------------- host error plumbing
 int fail(int status, const char* fmt, ...);       // records a thread-local message
 int check_launch(const char* what);               // cudaGetLastError -> SK_ERR_CUDA
+// Streaming multiprocessors of the current device (queried once per device; 148, the B200 count,
+// when no device can be asked, e.g. a size query on a machine without a GPU).
+int sm_count();
 
 // ---------------------------------------------------------------- element access
 template <int DT> struct Elem;
@@ -137,7 +140,7 @@ constexpr int64_t SC_SWITCH_PAD = 3584;   // empty slots after each group in the
 
 inline ScorePlan make_score_plan(int n_groups, int64_t T, int64_t M) {
     ScorePlan p;
-    const int n_sm = 148;
+    const int n_sm = sm_count();
     const int64_t total = (int64_t)n_groups * T;
     if (total / n_sm >= 16384) {
         // large: split the flat (group, key) space evenly; a CTA may cross one group boundary.
@@ -214,6 +217,8 @@ int launch_score(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
                  const uint8_t* allowed, int B, int H, int Hkv, int L, int R, int64_t T,
                  const int32_t* T_dev, int64_t Tcap, float* scores, int64_t score_row_stride,
                  int32_t* status, cudaStream_t st);
+// (L, heads per table word, R) combinations the native scorer has a kernel for
+bool score_shape_supported(int L, int ht, int R);
 int launch_score_compat(const float* q_probs, const int16_t* key_buckets, const uint8_t* allowed,
                         const float* v_hist, float* out, int B, int H, int L, int R, int64_t T,
                         cudaStream_t st);

@@ -43,9 +43,10 @@ constexpr size_t DEC_TICKET_BYTES = DEC_MAX_ROWS * sizeof(int32_t);
 inline int decode_splits(int64_t rows, int64_t max_len) {
     // Few fat CTAs rather than many thin ones: the block scheduler starts roughly 150 CTAs per
     // microsecond, so a grid of 900 small CTAs spends more time ramping up than gathering.
-    int64_t s = (148 * 2) / rows;                       // all CTAs resident: 2 per SM
+    const int n_sm = sm_count();
+    int64_t s = (n_sm * 2) / rows;                      // all CTAs resident: 2 per SM
     // long lists are bandwidth work: a third CTA per SM keeps more rows in flight
-    if (s >= 1 && max_len / s > 64 * DEC_WARPS) s = (148 * 3) / rows;
+    if (s >= 1 && max_len / s > 64 * DEC_WARPS) s = (n_sm * 3) / rows;
     const int64_t cap = (max_len + DEC_G * DEC_WARPS - 1) / (DEC_G * DEC_WARPS);   // at least one stage per warp
     if (s > cap) s = cap;
     if (s < 1) s = 1;

@@ -99,7 +99,7 @@ template <typename KT, typename PT>
 int hash_keys_dispatch(const void* keys, int64_t krs, const void* planes, int64_t N, int D, int L,
                        int P, void* codes, int cb, int64_t crs, cudaStream_t st) {
     int64_t groups = (N + HASH_ROWS - 1) / HASH_ROWS;
-    dim3 grid((unsigned)(groups < 148 * 8 ? groups : 148 * 8), (unsigned)((L + HASH_WARPS - 1) / HASH_WARPS));
+    dim3 grid((unsigned)(groups < sm_count() * 8 ? groups : sm_count() * 8), (unsigned)((L + HASH_WARPS - 1) / HASH_WARPS));
     if (D == 128)
         hash_keys_kernel<KT, PT, 4><<<grid, HASH_THREADS, 0, st>>>(
             (const KT*)keys, krs, (const PT*)planes, N, L, P, codes, cb, crs);
@@ -172,7 +172,7 @@ int launch_kv_copy(const void* k_new, const void* v_new, int kv_dtype, const int
     if ((((uintptr_t)k_new | (uintptr_t)v_new | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) != 0)
         return fail(SK_ERR_MISALIGNED, "kv copy: K/V pointers must be 16-byte aligned");
     int64_t gx = (N + 7) / 8;
-    if (gx > 148 * 16) gx = 148 * 16;
+    if (gx > sm_count() * 16) gx = sm_count() * 16;
     kv_copy_kernel<<<(unsigned)gx, 256, 0, st>>>((const uint4*)k_new, (const uint4*)v_new, input_pos, (uint4*)k_cache,
                                                  (uint4*)v_cache, (__half*)v_norm, prefill_len, status, N, S, Hkv,
                                                  Tcap);

@@ -521,7 +521,7 @@ int launch_cache_rows(const int64_t* input_pos, int B, int S, int Hkv, int64_t T
                       int32_t* status, cudaStream_t st) {
     const int64_t N = (int64_t)B * S * Hkv;
     int64_t g = (N + 255) / 256;
-    if (g > 148 * 8) g = 148 * 8;
+    if (g > sm_count() * 8) g = sm_count() * 8;
     cache_rows_kernel<<<(unsigned)g, 256, 0, st>>>(input_pos, B, S, Hkv, Tcap, dst_row, status);
     return check_launch("cache_rows_kernel");
 }
@@ -555,16 +555,16 @@ int launch_hash_keys_tc(const void* keys, int64_t key_row_stride, const void* pl
     e = cudaFuncSetAttribute(hash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_tc_kernel smem attribute: %s", cudaGetErrorString(e));
     const int64_t tiles = (N + TC_ROWS - 1) / TC_ROWS;
-    const unsigned n_cta = (unsigned)(tiles < 148 ? tiles : 148);     // one persistent CTA per SM
+    const unsigned n_cta = (unsigned)(tiles < sm_count() ? tiles : sm_count());     // one persistent CTA per SM
     hash_tc_kernel<<<n_cta, TC_PIPE_THREADS, smem, st>>>(map_k, map_p, pb, N, codes, code_row_stride, dst_row,
                                                         fix_count, fix_list, fix_cap, status);
     rc = check_launch("hash_tc_kernel");
     if (rc != SK_OK) return rc;
     // one listed projection per warp in the common case (about 1.4e-4 of the projections are listed)
-    e = launch_after(hash_fix_kernel, dim3(148 * 8), dim3(256), 0, st, kb, key_row_stride, pb, codes, code_row_stride,
+    e = launch_after(hash_fix_kernel, dim3(sm_count() * 8), dim3(256), 0, st, kb, key_row_stride, pb, codes, code_row_stride,
                      dst_row, (const uint32_t*)fix_count, (const uint32_t*)fix_list, fix_cap);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_fix_kernel: %s", cudaGetErrorString(e));
-    dim3 grid(148, TC_N / 8 / HASH_WARPS);
+    dim3 grid(sm_count(), TC_N / 8 / HASH_WARPS);
     e = launch_after(hash_exact_if_overflow_kernel, grid, dim3(HASH_THREADS), 0, st, kb, key_row_stride, pb, N, codes,
                      code_row_stride, dst_row, (const uint32_t*)fix_count, fix_cap);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "hash_exact_if_overflow_kernel: %s", cudaGetErrorString(e));

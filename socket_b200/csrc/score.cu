@@ -402,6 +402,13 @@ int score_launch(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
 
 }  // namespace
 
+bool score_shape_supported(int L, int ht, int R) {
+    if (R > 256 || (size_t)256 * L * ht * 4 + sizeof(FilterShared) > 227 * 1024) return false;
+    if (L == 32 || L == 16) return ht == 4 || ht == 2 || ht == 1;
+    if (L == 64) return ht == 2 || ht == 1;
+    return false;
+}
+
 int launch_score(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
                  const uint8_t* allowed, int B, int H, int Hkv, int L, int R, int64_t T,
                  const int32_t* T_dev, int64_t Tcap, float* scores, int64_t score_row_stride,

@@ -363,6 +363,22 @@ class DecodeStep:
         self._rescored_off = int(lib().sk_decode_step_rescored_rows_offset(B, H, Hkv, D, L, R, T_max, topk,
                                                                            sink, window))
 
+    def rebind(self, q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Optional[torch.Tensor],
+               input_pos: Optional[torch.Tensor], out: torch.Tensor) -> None:
+        """Point the step at other input/output tensors of the same shapes and dtypes; the
+        scratch memory is kept.  (A CUDA graph captured before this call still holds the old
+        addresses.)"""
+        old_q, old_out = self._keep[1], self._keep[7]
+        assert q.shape == old_q.shape and q.dtype == old_q.dtype and out.shape == old_out.shape
+        assert q.is_contiguous() and out.is_contiguous()
+        assert (k_new is None) == (self._keep[2] is None)
+        if k_new is not None:
+            assert k_new.is_contiguous() and v_new.is_contiguous()
+            assert k_new.shape == self._keep[2].shape and k_new.dtype == self._keep[2].dtype
+        self._keep = (self._keep[0], q, k_new, v_new, input_pos) + self._keep[5:7] + (out,)
+        p = self.params
+        p.q, p.k_new, p.v_new, p.input_pos, p.out = ptr(q), ptr(k_new), ptr(v_new), ptr(input_pos), ptr(out)
+
     def run(self) -> None:
         check(lib().sk_decode_step(C.byref(self.params), stream_ptr(self.device)), "sk_decode_step")
 

@@ -103,3 +103,51 @@ def test_operators_refuse_cpu_tensors():
     with pytest.raises(RuntimeError, match="must be CUDA"):
         ops.soft_hash_collision(torch.zeros(1, 1, 1, 2, 4), torch.zeros(1, 1, 2, 3, dtype=torch.int16),
                                 torch.ones(1, 1, 1, 3, dtype=torch.bool), torch.zeros(1, 1, 1, 3))
+
+
+def _step_params(**over):
+    """A parameter block that passes every host check up to the launch (fake, aligned addresses;
+    nothing is ever dereferenced on the host)."""
+    p = _lib.DecodeParams()
+    a = 1 << 20
+    for name in ("q", "k_new", "v_new", "input_pos", "planes", "protos_T", "k_cache", "v_cache", "codes",
+                 "v_norm", "prefill_len", "out", "workspace", "status"):
+        setattr(p, name, a)
+        a += 1 << 20
+    p.temperature = 1.0
+    p.q_dtype = p.kv_dtype = p.plane_dtype = _lib.SK_BF16
+    p.B, p.H, p.Hkv, p.D, p.L, p.P, p.R = 1, 32, 8, 128, 32, 8, 256
+    p.Tcap = p.T_max = 8192
+    p.M, p.sink, p.window, p.select_path = 256, 16, 64, 0
+    p.workspace_bytes = 1 << 40
+    for k, v in over.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("field", ["q", "k_new", "v_new", "k_cache", "v_cache", "codes", "out", "planes"])
+def test_decode_step_rejects_misaligned_pointers_on_the_host(field):
+    lib = _lib.lib()
+    p = _step_params()
+    setattr(p, field, getattr(p, field) + 2)          # element-aligned only, like an odd storage offset
+    rc = lib.sk_decode_step(C.byref(p), None)
+    assert rc == -3, lib.sk_last_error()
+    assert field.encode() in lib.sk_last_error() and b"aligned" in lib.sk_last_error()
+    p = _step_params()
+    p.v_norm += 1
+    assert lib.sk_decode_step(C.byref(p), None) == -3 and b"v_norm" in lib.sk_last_error()
+
+
+def test_decode_step_refuses_unsupported_shapes_before_touching_the_cache():
+    lib = _lib.lib()
+    # refused on the host before the first launch, so the append of the new token is never enqueued
+    rc = lib.sk_decode_step(C.byref(_step_params(D=64)), None)
+    assert rc == -2 and b"head_dim" in lib.sk_last_error()
+    rc = lib.sk_decode_step(C.byref(_step_params(q_dtype=_lib.SK_BF16, kv_dtype=_lib.SK_F32)), None)
+    assert rc == -2 and b"dtype pair" in lib.sk_last_error()
+    rc = lib.sk_decode_step(C.byref(_step_params(L=24)), None)
+    assert rc == -2 and b"scorer" in lib.sk_last_error()
+    rc = lib.sk_decode_step(C.byref(_step_params(L=64)), None)      # 64 tables x 4 heads: table too large
+    assert rc == -2 and b"scorer" in lib.sk_last_error()
+    rc = lib.sk_decode_step(C.byref(_step_params(P=9, R=512)), None)
+    assert rc == -1 and b"uint8" in lib.sk_last_error()
