@@ -3,7 +3,7 @@
 * ``oracle/c/libsocket_oracle.so`` — the plain-C restatement (`oracle/c/socket_oracle.c`).
 * ``oracle/_ref/libref_scorer.so`` — the reference's own scorer kernel source compiled as
   C++ through `oracle/ref_shim.cpp`.  Built only where the reference tree is present
-  (``SOCKET_REFERENCE_ROOT`` or the default location); the sources are compiled where they
+  (``SOCKET_REFERENCE_ROOT``, else a ``reference`` directory beside the repository); the sources are compiled where they
   lie and never copied.  The output directory is git-ignored.
 
 Run ``python oracle/build_oracle.py``.
@@ -15,7 +15,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("SOCKET_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: named by SOCKET_REFERENCE_ROOT, else a `reference` directory beside this repository
+REF_ROOT = os.environ.get("SOCKET_REFERENCE_ROOT") or os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 REF_KERNEL = os.path.join(REF_ROOT, "GPT-FAST", "kernels", "soft_hash_collision.cu")
 C_SRC = os.path.join(HERE, "c", "socket_oracle.c")
 C_LIB = os.path.join(HERE, "c", "libsocket_oracle.so")

@@ -9,8 +9,7 @@ import os
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-# SOCKET_B200_LIB names another build of the library (for comparing two builds on one machine)
-LIB_PATH = os.environ.get("SOCKET_B200_LIB") or os.path.join(_PKG, "libsocket_b200.so")
+LIB_PATH = os.path.join(_PKG, "libsocket_b200.so")
 
 SK_F32, SK_BF16, SK_F16 = 0, 1, 2
 DTYPE_CODE = {torch.float32: SK_F32, torch.bfloat16: SK_BF16, torch.float16: SK_F16}

@@ -1,6 +1,6 @@
 """Generate the golden fixtures by running the REFERENCE's own code on CPU.
 
-Run once, in a container that has the reference tree (default /root/reference, override
+Run once, in a container that has the reference tree (a `reference` directory beside this repository, override
 with SOCKET_REFERENCE_ROOT):
 
     python tests/golden/make_golden.py
@@ -32,7 +32,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("SOCKET_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("SOCKET_REFERENCE_ROOT") or os.path.normpath(os.path.join(ROOT, "..", "reference"))
 sys.path.insert(0, os.path.join(REF, "GPT-FAST"))
 sys.path.insert(0, ROOT)
 

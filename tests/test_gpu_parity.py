@@ -512,6 +512,50 @@ def test_fused_decode_step_against_chained_oracle(dtype):
     assert torch.equal(out, out1)
 
 
+def test_sparse_decode_rereads_non_contiguous_inputs_on_every_call():
+    """The reference flow hands `v` over as a view of the fused QKV projection (not contiguous for
+    B > 1).  Two calls with the same buffers and different contents must each use the contents of
+    their own call; the result must equal the one obtained with contiguous copies."""
+    B, H, Hkv, T, M, sink, window = 2, 8, 2, 2500, 64, 4, 16
+    inp = make_decode_inputs(B, H, Hkv, T + 2, seed=31, dtype=torch.bfloat16)
+    k_bshd = cu(inp.k.permute(0, 2, 1, 3).contiguous())
+    v_bshd = cu(inp.v.permute(0, 2, 1, 3).contiguous())
+    g = torch.Generator().manual_seed(8)
+    qs = [cu(torch.randn(B, H, 128, generator=g).bfloat16()) for _ in range(2)]
+
+    def run(contiguous):
+        attn = SocketAttention(H, Hkv, 128, heavy_const=M, sink_size=sink, window_size=window,
+                               planes=inp.planes, protos_T=inp.protos_T, dtype=torch.bfloat16, device=DEV)
+        cache = attn.setup_cache(B, T + 64)
+        cache.append(torch.arange(T, device=DEV), k_bshd[:, :T], v_bshd[:, :T], attn.planes)
+        # one projection buffer [B, 1, (H + 2 Hkv) * D]; q, k, v are views of it, as in the reference
+        qkv = torch.zeros(B, 1, (H + 2 * Hkv) * 128, dtype=torch.bfloat16, device=DEV)
+        qv, kv, vv = qkv.split([H * 128, Hkv * 128, Hkv * 128], dim=-1)
+        qv, kv, vv = qv.view(B, H, 128), kv.view(B, 1, Hkv, 128), vv.view(B, 1, Hkv, 128)
+        assert not vv.is_contiguous() and not kv.is_contiguous()
+        pos = torch.zeros(1, dtype=torch.long, device=DEV)
+        outs = []
+        for i in range(2):
+            qv.copy_(qs[i]); kv.copy_(k_bshd[:, T + i:T + i + 1]); vv.copy_(v_bshd[:, T + i:T + i + 1])
+            pos.fill_(T + i)
+            if contiguous:
+                o = attn.sparse_decode(qv.contiguous(), kv.contiguous(), vv.contiguous(), pos)
+            else:
+                o = attn.sparse_decode(qv, kv, vv, pos)
+            outs.append(o.clone())
+        torch.cuda.synchronize()
+        assert int(cache.prefill_len) == T + 2 and int(cache.status) == 0
+        return outs, cache.k_cache[:, :, T:T + 2].clone(), cache.v_cache[:, :, T:T + 2].clone()
+
+    want, wk, wv = run(True)
+    got, gk, gv = run(False)
+    assert torch.equal(gk, wk) and torch.equal(gv, wv)
+    assert torch.equal(gv, v_bshd[:, T:T + 2].permute(0, 2, 1, 3))
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    assert not torch.equal(got[0], got[1])
+
+
 def test_run_to_run_determinism():
     inp = make_decode_inputs(1, 32, 8, 8192, seed=5, dtype=torch.bfloat16)
     qp = orc.soft_hash(inp.q.float(), inp.planes.float(), inp.protos_T)
