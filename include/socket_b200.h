@@ -240,6 +240,34 @@ SK_API int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, con
                      size_t workspace_bytes, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Packed form of the fused scorer + select (L = 32, R <= 256, query heads per KV head a multiple
+ * of 4): the scan reads a 12-bit fixed-point copy of the scorer table (8 bytes per bucket and table
+ * for the four heads, summed as exact integers), which halves the shared-memory traffic of the scan;
+ * the select brackets the k-th score with rigorous bounds and scores the few keys inside the
+ * bracket with the fp32 table.  The list is the one sk_score + sk_select_list return, element for
+ * element.  Replaces the same reference span as sk_score_select_list
+ * (GPT-FAST/kernels/sparse.py:39-95 with soft_hash_collision.cu:25-54); the fixed-point table has no
+ * counterpart in the reference.
+ *
+ *   sk_packed_table_bytes      size of the packed-table buffer [B*Hkv*(H/Hkv/4) x 64 KiB | constants]
+ *   sk_soft_hash_packed        sk_soft_hash that writes the fp32 table AND its packed copy; the
+ *                              quantisation range follows from protos_T and the temperature alone
+ *                              (|tanh| <= 1), so it needs the soft hash, not just q_probs
+ *   sk_score_select_packed     stages & 1: the scan, stages & 2: the select (3 = both, the normal
+ *                              call); workspace as for sk_score_select_list; codes 32-byte aligned
+ * ---------------------------------------------------------------------------------- */
+SK_API size_t sk_packed_table_bytes(int B, int H, int Hkv);
+SK_API int sk_packed_applicable(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M);
+SK_API int sk_soft_hash_packed(const void* q, int q_dtype, const void* planes, int plane_dtype,
+                        const float* protos_T, float temperature, int B, int H, int Hkv, int D, int L,
+                        int P, int R, float* lut, void* packed, void* stream);
+SK_API int sk_score_select_packed(const float* lut, const void* packed, const uint8_t* codes,
+                           const uint16_t* v_norm, int B, int H, int Hkv, int L, int R, int64_t T,
+                           const int32_t* T_dev, int64_t Tcap, int64_t M, int sink, int window,
+                           int32_t* list, int64_t list_row_stride, int32_t* list_len, void* workspace,
+                           size_t workspace_bytes, int32_t* status, int stages, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * sk_sparse_decode without any caller-provided or allocated scratch.  No counterpart in the
  * reference (its sparse_attention_fwd allocates its partial-result tensors on every call,
  * GPT-FAST/kernels/sparse.py:323-325).
@@ -282,8 +310,9 @@ SK_API int sk_sparse_decode_static(const void* q, int q_dtype, const void* k_cac
 enum sk_select_path {
     SK_SELECT_AUTO = 0,
     SK_SELECT_TWO_LAUNCH = 1,   /* sk_score + sk_select_list (score matrix in the workspace) */
-    SK_SELECT_FILTER = 2,       /* sk_score_filter + sk_select_candidates                   */
-    SK_SELECT_CLUSTER = 3       /* sk_score_select_cluster                                   */
+    SK_SELECT_FILTER = 2,       /* filtering scorer + candidate select, packed table where it applies */
+    SK_SELECT_CLUSTER = 3,      /* sk_score_select_cluster                                   */
+    SK_SELECT_FILTER_F32 = 4    /* sk_score_filter + sk_select_candidates on the fp32 table  */
 };
 
 typedef struct sk_decode_params {

@@ -358,6 +358,78 @@ int sk_select_candidates(const float* lut, const uint8_t* codes, const uint16_t*
                                     list, list_row_stride, list_len, workspace, status, (cudaStream_t)stream);
 }
 
+static inline int packed_groups(int B, int H, int Hkv) { return B * Hkv * ((H / Hkv) / 4); }
+static inline size_t packed_param_offset(int B, int H, int Hkv) { return (size_t)packed_groups(B, H, Hkv) * 65536; }
+
+size_t sk_packed_table_bytes(int B, int H, int Hkv) {
+    if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || (H / Hkv) % 4) return 0;
+    return packed_param_offset(B, H, Hkv) + up256((size_t)packed_groups(B, H, Hkv) * sizeof(float));
+}
+
+int sk_packed_applicable(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M) {
+    return sk_score_select_applicable(B, H, Hkv, L, R, T, M) && packed_filter_applicable(H, Hkv, L, R) ? 1 : 0;
+}
+
+int sk_soft_hash_packed(const void* q, int q_dtype, const void* planes, int plane_dtype,
+                        const float* protos_T, float temperature, int B, int H, int Hkv, int D, int L,
+                        int P, int R, float* lut, void* packed, void* stream) {
+    SK_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && D > 0 && L > 0 && P > 0 && R > 0,
+               "sk_soft_hash_packed: sizes must be positive");
+    if (B == 0) return SK_OK;
+    SK_REQUIRE(H % Hkv == 0, "sk_soft_hash_packed: H=%d not a multiple of Hkv=%d", H, Hkv);
+    SK_REQUIRE(q && planes && protos_T && lut && packed, "sk_soft_hash_packed: null pointer");
+    SK_REQUIRE(valid_dtype(q_dtype) && valid_dtype(plane_dtype), "sk_soft_hash_packed: bad dtype");
+    SK_REQUIRE(temperature > 0.f, "sk_soft_hash_packed: temperature must be positive");
+    if (!packed_filter_applicable(H, Hkv, L, R))
+        return fail(SK_ERR_UNSUPPORTED, "sk_soft_hash_packed: needs L=32, R<=256 and a multiple of 4 query heads per KV head");
+    SK_ALIGNED(lut, 16, "sk_soft_hash_packed: lut");
+    SK_ALIGNED(packed, 256, "sk_soft_hash_packed: packed");
+    char* pk = static_cast<char*>(packed);
+    return launch_soft_hash(q, q_dtype, planes, plane_dtype, protos_T, temperature, B, H, Hkv, D, L, P, R,
+                            nullptr, lut, (cudaStream_t)stream, pk,
+                            reinterpret_cast<float*>(pk + packed_param_offset(B, H, Hkv)));
+}
+
+int sk_score_select_packed(const float* lut, const void* packed, const uint8_t* codes,
+                           const uint16_t* v_norm, int B, int H, int Hkv, int L, int R, int64_t T,
+                           const int32_t* T_dev, int64_t Tcap, int64_t M, int sink, int window,
+                           int32_t* list, int64_t list_row_stride, int32_t* list_len, void* workspace,
+                           size_t workspace_bytes, int32_t* status, int stages, void* stream) {
+    SK_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && L > 0 && R > 0 && T > 0 && M >= 0,
+               "sk_score_select_packed: sizes must be positive");
+    if (B == 0) return SK_OK;
+    SK_REQUIRE(H % Hkv == 0, "sk_score_select_packed: H=%d not a multiple of Hkv=%d", H, Hkv);
+    SK_REQUIRE(lut && packed && codes && v_norm && workspace, "sk_score_select_packed: null pointer");
+    SK_REQUIRE((stages & 3) != 0 && (stages & ~3) == 0, "sk_score_select_packed: stages must be 1, 2 or 3");
+    SK_REQUIRE(!(stages & 2) || (list && list_len), "sk_score_select_packed: null list");
+    SK_REQUIRE(T <= Tcap, "sk_score_select_packed: T exceeds the cache capacity");
+    SK_REQUIRE(!(stages & 2) || list_row_stride >= list_len_host(T, sink, window, M),
+               "sk_score_select_packed: list_row_stride smaller than the list length");
+    SK_ALIGNED(lut, 16, "sk_score_select_packed: lut");
+    SK_ALIGNED(packed, 256, "sk_score_select_packed: packed");
+    SK_ALIGNED(codes, 32, "sk_score_select_packed: codes");
+    SK_ALIGNED(workspace, 256, "sk_score_select_packed: workspace");
+    if (!sk_packed_applicable(B, H, Hkv, L, R, T, M))
+        return fail(SK_ERR_UNSUPPORTED,
+                    "sk_score_select_packed: shape outside the packed path (needs L=32, R<=256, 4 | H/Hkv, T>=4096, "
+                    "12*M<=T, M<=4096); use sk_score_select_list or sk_score + sk_select_list");
+    if (workspace_bytes < score_select_workspace_bytes(B, H, Hkv, L, T, M))
+        return fail(SK_ERR_WORKSPACE, "sk_score_select_packed: workspace %zu < %zu bytes", workspace_bytes,
+                    score_select_workspace_bytes(B, H, Hkv, L, T, M));
+    cudaStream_t st = (cudaStream_t)stream;
+    const char* pk = static_cast<const char*>(packed);
+    const float* qpar = reinterpret_cast<const float*>(pk + packed_param_offset(B, H, Hkv));
+    if (stages & 1) {
+        int rc = launch_score_filter(lut, codes, v_norm, B, H, Hkv, L, R, T, T_dev, Tcap, M, workspace, status, st,
+                                     pk, qpar);
+        if (rc != SK_OK) return rc;
+    }
+    if (stages & 2)
+        return launch_select_candidates(lut, codes, v_norm, B, H, Hkv, L, R, T, T_dev, Tcap, M, sink, window, 0,
+                                        list, list_row_stride, list_len, workspace, status, st, qpar);
+    return SK_OK;
+}
+
 size_t sk_sparse_decode_workspace_bytes(int B, int H, int D, int64_t max_list_len) {
     return sparse_decode_workspace_bytes(B, H, D, max_list_len);
 }
@@ -389,9 +461,10 @@ int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, const void
 
 /* Workspace of one fused step: [decode scratch | table | scores | list | list_len] */
 struct StepLayout {
-    size_t dec, lut, scores, list, len, total;
+    size_t dec, lut, scores, list, len, packed, total;
     int64_t score_stride, list_stride;
     bool fused;      // scores region holds the fused scorer+select workspace instead
+    bool has_packed; // a packed-table region exists (the packed scan applies to the shape)
 };
 
 static StepLayout step_layout(int B, int H, int Hkv, int D, int L, int R, int64_t T_max, int64_t M,
@@ -409,6 +482,9 @@ static StepLayout step_layout(int B, int H, int Hkv, int D, int L, int R, int64_
                    : up256((size_t)B * H * s.score_stride * sizeof(float));
     s.list = off;   off += up256((size_t)B * H * s.list_stride * sizeof(int32_t));
     s.len = off;    off += up256((size_t)B * H * sizeof(int32_t));
+    s.has_packed = s.fused && packed_filter_applicable(H, Hkv, L, R);
+    s.packed = off;
+    if (s.has_packed) off += up256(sk_packed_table_bytes(B, H, Hkv));
     s.total = off;
     return s;
 }
@@ -480,14 +556,14 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
         return fail(SK_ERR_WORKSPACE, "sk_decode_step: workspace %zu < %zu bytes", p->workspace_bytes, lay.total);
     SK_REQUIRE(p->list == nullptr || p->list_row_stride >= lay.list_stride,
                "sk_decode_step: list_row_stride smaller than the list length %lld", (long long)lay.list_stride);
-    SK_REQUIRE(p->select_path >= SK_SELECT_AUTO && p->select_path <= SK_SELECT_CLUSTER,
+    SK_REQUIRE(p->select_path >= SK_SELECT_AUTO && p->select_path <= SK_SELECT_FILTER_F32,
                "sk_decode_step: select_path %d is not an sk_select_path", p->select_path);
     const bool can_cluster = score_select_cluster_size(p->B, p->H, p->Hkv, p->L, p->R, p->T_max, p->M) != 0;
     int path = p->select_path;
     if (path == SK_SELECT_AUTO) path = lay.fused ? SK_SELECT_FILTER : (can_cluster ? SK_SELECT_CLUSTER : SK_SELECT_TWO_LAUNCH);
     if (path == SK_SELECT_CLUSTER && !can_cluster)
         return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the one-launch scorer + select");
-    if (path == SK_SELECT_FILTER && !lay.fused)
+    if ((path == SK_SELECT_FILTER || path == SK_SELECT_FILTER_F32) && !lay.fused)
         return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the filtering scorer + candidate select");
     if (path == SK_SELECT_TWO_LAUNCH && lay.fused)
         return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: the workspace of this shape holds no score matrix; "
@@ -499,6 +575,10 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
     int32_t* list = p->list ? p->list : reinterpret_cast<int32_t*>(ws + lay.list);
     int32_t* list_len = p->list ? p->list_len : reinterpret_cast<int32_t*>(ws + lay.len);
     const int64_t list_stride = p->list ? p->list_row_stride : lay.list_stride;
+    // the packed scan needs 32-byte aligned code rows (one 256-bit load per key)
+    const bool use_packed = path == SK_SELECT_FILTER && lay.has_packed && aligned(p->codes, 32);
+    char* pk = use_packed ? ws + lay.packed : nullptr;
+    float* qpar = use_packed ? reinterpret_cast<float*>(pk + packed_param_offset(p->B, p->H, p->Hkv)) : nullptr;
     int rc;
     bool fused = false;
     if (p->k_new != nullptr && p->q_dtype == p->kv_dtype) {
@@ -506,7 +586,7 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
         rc = launch_decode_prologue(p->q, p->k_new, p->v_new, p->kv_dtype, p->input_pos, p->planes,
                                     p->plane_dtype, p->protos_T, p->temperature, p->k_cache, p->v_cache,
                                     p->codes, p->v_norm, p->prefill_len, p->status, lut, p->B, p->H, p->Hkv,
-                                    p->D, p->Tcap, p->L, p->P, p->R, st, &fused);
+                                    p->D, p->Tcap, p->L, p->P, p->R, st, &fused, pk, qpar);
         if (rc != SK_OK) return rc;
     }
     if (!fused) {
@@ -516,8 +596,8 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
                               1, p->Hkv, p->D, p->Tcap, p->L, p->P, stream);
             if (rc != SK_OK) return rc;
         }
-        rc = sk_soft_hash(p->q, p->q_dtype, p->planes, p->plane_dtype, p->protos_T, p->temperature, p->B,
-                          p->H, p->Hkv, p->D, p->L, p->P, p->R, nullptr, lut, stream);
+        rc = launch_soft_hash(p->q, p->q_dtype, p->planes, p->plane_dtype, p->protos_T, p->temperature, p->B,
+                              p->H, p->Hkv, p->D, p->L, p->P, p->R, nullptr, lut, st, pk, qpar);
         if (rc != SK_OK) return rc;
     }
     // from here on every launch may start while its predecessor drains (see pdl_wait in the kernels)
@@ -528,14 +608,14 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
                                          p->prefill_len, p->Tcap, p->M, p->sink, p->window, list, list_stride,
                                          list_len, p->status, st);
         if (rc != SK_OK) return rc;
-    } else if (path == SK_SELECT_FILTER) {
+    } else if (path == SK_SELECT_FILTER || path == SK_SELECT_FILTER_F32) {
         // filtering scorer + candidate select: no score array is written or re-read
         rc = launch_score_filter(lut, p->codes, p->v_norm, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
-                                 p->prefill_len, p->Tcap, p->M, ws + lay.scores, p->status, st);
+                                 p->prefill_len, p->Tcap, p->M, ws + lay.scores, p->status, st, pk, qpar);
         if (rc != SK_OK) return rc;
         rc = launch_select_candidates(lut, p->codes, p->v_norm, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
                                       p->prefill_len, p->Tcap, p->M, p->sink, p->window, 0, list, list_stride,
-                                      list_len, ws + lay.scores, p->status, st);
+                                      list_len, ws + lay.scores, p->status, st, qpar);
         if (rc != SK_OK) return rc;
     } else {
         rc = sk_score(lut, p->codes, p->v_norm, nullptr, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,

@@ -210,7 +210,8 @@ int launch_kv_append(const void* k_new, const void* v_new, int kv_dtype, const i
                      int B, int S, int Hkv, int D, int64_t Tcap, int L, int P, cudaStream_t st);
 int launch_soft_hash(const void* q, int q_dtype, const void* planes, int plane_dtype,
                      const float* protos_T, float temperature, int B, int H, int Hkv, int D, int L,
-                     int P, int R, float* q_probs, float* lut, cudaStream_t st);
+                     int P, int R, float* q_probs, float* lut, cudaStream_t st, void* lutq = nullptr,
+                     float* qpar = nullptr);
 int launch_lut_from_probs(const void* q_probs, int dtype, int B, int H, int Hkv, int L, int R,
                           float* lut, cudaStream_t st);
 int launch_score(const float* lut, const uint8_t* codes, const uint16_t* v_norm,
@@ -238,11 +239,15 @@ int launch_sparse_decode(const void* q, int q_dtype, const void* k_cache, const 
 size_t score_select_workspace_bytes(int B, int H, int Hkv, int L, int64_t T, int64_t M);
 int launch_score_filter(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
                         int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
-                        void* workspace, int32_t* status, cudaStream_t st);
+                        void* workspace, int32_t* status, cudaStream_t st, const void* lutq = nullptr,
+                        const float* qpar = nullptr);
+// The packed (12-bit table) form of the filtering scorer exists for this shape
+bool packed_filter_applicable(int H, int Hkv, int L, int R);
 int launch_select_candidates(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
                              int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
                              int sink, int window, int sorted, int32_t* list, int64_t list_row_stride,
-                             int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st);
+                             int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st,
+                             const float* qpar = nullptr);
 
 // One-launch scorer + exact select on thread-block clusters (score_cluster.cu)
 int score_select_cluster_size(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M);
@@ -268,6 +273,6 @@ int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, 
                            const float* protos_T, float temperature, void* k_cache, void* v_cache,
                            uint8_t* codes, uint16_t* v_norm, int32_t* prefill_len, int32_t* status,
                            float* lut, int B, int H, int Hkv, int D, int64_t Tcap, int L, int P, int R,
-                           cudaStream_t st, bool* launched);
+                           cudaStream_t st, bool* launched, void* lutq = nullptr, float* qpar = nullptr);
 
 }  // namespace sk

@@ -353,6 +353,297 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Packed mode of the filtering scorer (L = 32 tables, 4 query heads per KV-head group).
+//
+// The fp32 walk above is bound by shared-memory bandwidth (16 bytes per key and table) with the
+// integer pipe close behind.  Here the table is the 12-bit fixed-point copy written by the soft
+// hash (soft_hash_body.cuh): 8 bytes per (bucket, table) = four 16-bit fields, one per head.  A
+// key's sum over 16 tables fits a 16-bit field (16 * 4095 < 65536), so the four heads are summed
+// as two packed 32-bit integers per half of the tables - two adds per lookup instead of four, half
+// the shared-memory bytes, and no rounding at all: the sums S are exact integers.
+//
+// What is written per kept key is (S, ||v||) packed into 32 bits, from which scorer and select
+// kernel compute the same upper bound  U = (S + K0 + 33) * ||v||  of C * (exact fp32 score); keys
+// with U >= the chunk's cut are kept.  The select kernel brackets the k-th exact score with these
+// bounds, rescans only the few keys inside the bracket with the fp32 table, and so returns exactly
+// the list the fp32 path returns.
+//
+// Lookups: one LDS.64 per (key, table).  The table lies at a 64 KiB-aligned shared address, one
+// 256-byte line per bucket (32 tables x 8 bytes), so a lookup address is
+// [8 * table | code | address bits 16..23 | 0] byte by byte and ONE byte permute builds it from
+// the register holding the code byte and a per-lane constant.  The 16 lanes of a half warp (one
+// shared-memory wavefront of 8-byte accesses) visit, at step p, the tables (p ^ lane) of the
+// current half of the tables: 16 distinct bank pairs whatever the codes are.
+constexpr int PK_SMEM = 129 * 1024;
+
+__device__ __forceinline__ uint32_t prmt_r(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+template <uint32_t SEL>
+__device__ __forceinline__ uint32_t prmt_i(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "n"(SEL));
+    return d;
+}
+// volatile: ordered with the mbarrier wait that guards the table
+template <int IMM>
+__device__ __forceinline__ void lds64(uint32_t addr, uint32_t& x, uint32_t& y) {
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(x), "=r"(y) : "r"(addr), "n"(IMM));
+}
+__device__ __forceinline__ void ldg256(const uint8_t* p, uint32_t (&c)[8]) {
+    asm volatile("ld.global.cg.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]), "=r"(c[4]), "=r"(c[5]), "=r"(c[6]), "=r"(c[7])
+                 : "l"(p));
+}
+
+// One half of the tables (16 code bytes in w[0..3]): 16 lookups, packed adds into (a, b).
+template <int IMM>
+__device__ __forceinline__ void packed_half(const uint32_t* w, bool swap, uint32_t sel_lo, uint32_t sel_hi,
+                                            const uint32_t (&X)[6], uint32_t& a, uint32_t& b) {
+    // position p of the permuted vector holds the code of table (p ^ m): bit 3 of m swaps the
+    // 8-byte halves, bits 0..2 permute inside a half
+    const uint32_t h0a = swap ? w[2] : w[0], h0b = swap ? w[3] : w[1];
+    const uint32_t h1a = swap ? w[0] : w[2], h1b = swap ? w[1] : w[3];
+    uint32_t pv[4];
+    pv[0] = prmt_r(h0a, h0b, sel_lo);
+    pv[1] = prmt_r(h0a, h0b, sel_hi);
+    pv[2] = prmt_r(h1a, h1b, sel_lo);
+    pv[3] = prmt_r(h1a, h1b, sel_hi);
+    uint32_t x[16], y[16];
+#define SK_PK_LOOKUP(P)                                                                             \
+    lds64<IMM>(prmt_i<0xF700u | (((P) & 3) << 4) | (4 + (P) % 3)>(pv[(P) >> 2], X[(P) / 3]), x[P], y[P])
+    SK_PK_LOOKUP(0); SK_PK_LOOKUP(1); SK_PK_LOOKUP(2); SK_PK_LOOKUP(3);
+    SK_PK_LOOKUP(4); SK_PK_LOOKUP(5); SK_PK_LOOKUP(6); SK_PK_LOOKUP(7);
+    SK_PK_LOOKUP(8); SK_PK_LOOKUP(9); SK_PK_LOOKUP(10); SK_PK_LOOKUP(11);
+    SK_PK_LOOKUP(12); SK_PK_LOOKUP(13); SK_PK_LOOKUP(14); SK_PK_LOOKUP(15);
+#undef SK_PK_LOOKUP
+    a = 0; b = 0;
+#pragma unroll
+    for (int p = 0; p < 16; p += 2) {
+        a += x[p] + x[p + 1];
+        b += y[p] + y[p + 1];
+    }
+}
+
+// Upper bound, in table units times ||v||, of a key's exact score; computed with exactly these
+// operations by the scorer and by the select kernel.
+__device__ __forceinline__ float packed_upper(uint32_t S, float K0p, float vn) {
+    return __fmul_rn(__fadd_rn(__uint2float_rn(S), K0p), vn);
+}
+
+__global__ void __launch_bounds__(SC_THREADS, 1)
+score_packed_kernel(const uint8_t* __restrict__ lutq, const float* __restrict__ qpar,
+                    const uint8_t* __restrict__ codes, const __half* __restrict__ v_norm, int H, int Hkv, int R,
+                    int64_t T, const int32_t* __restrict__ T_dev, int64_t Tcap, int64_t Tslots,
+                    int64_t slots_per_cta, int n_groups, int32_t* status, FilterArgs fa) {
+    constexpr int L = 32, HT = 4;
+    extern __shared__ __align__(1024) char smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t tab = (base + 0xffffu) & ~0xffffu;          // shared address of the table, 64 KiB aligned
+    char* lut_s = smem_raw + (tab - base);
+    // the statistics block sits in front of the table when the alignment gap has room, else behind it
+    FilterShared& fs = *reinterpret_cast<FilterShared*>((tab - base) >= 1024 ? smem_raw : lut_s + 65536);
+    uint64_t* bar = &fs.bar;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rep = H / Hkv;
+    const int tiles = rep / HT;
+    const uint32_t lut_bytes = (uint32_t)R * 256u;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) mbar_init(bar, 1);
+    __syncthreads();
+    pdl_wait();                                // the table, the live length and the newest codes come from the predecessor
+
+    const int64_t total = (int64_t)n_groups * Tslots;
+    int64_t slot = (int64_t)blockIdx.x * slots_per_cta;
+    const int64_t slot_end = min(slot + slots_per_cta, total);
+    uint32_t phase = 0;
+    auto request_table = [&](int g) {          // one thread: bulk copies of group g's table, completing on `bar`
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(bar, lut_bytes);
+        const char* src = reinterpret_cast<const char*>(lutq) + (size_t)g * 65536;
+        for (uint32_t off = 0; off < lut_bytes; off += SC_COPY_CHUNK) {
+            const uint32_t n = min((uint32_t)SC_COPY_CHUNK, lut_bytes - off);
+            bulk_g2s(lut_s + off, src + off, n, bar);
+        }
+    };
+    bool in_flight = slot < slot_end;
+    if (in_flight && threadIdx.x == 0) request_table((int)(slot / Tslots));
+    const int Teff = effective_len(T, T_dev);
+
+    while (slot < slot_end) {
+        const int g = (int)(slot / Tslots);
+        const int64_t t0 = slot - (int64_t)g * Tslots;
+        const int64_t seg_end = min((int64_t)(g + 1) * Tslots, slot_end);
+        int64_t t1 = seg_end - (int64_t)g * Tslots;
+        slot = seg_end;
+        if (t1 > Teff) t1 = Teff;
+
+        const int tile = g % tiles;
+        const int bk = g / tiles;               // b*Hkv + kvh
+        const int b = bk / Hkv, kvh = bk - b * Hkv;
+        const int h0 = kvh * rep + tile * HT;
+        const size_t row0 = (size_t)b * H + h0;
+        const int chunk = (int)((int64_t)blockIdx.x - ((int64_t)g * Tslots) / slots_per_cta);
+
+        if (t0 >= t1) {   // uniform across the CTA: nothing live in this segment
+            if (threadIdx.x < SC_WARPS * HT) {
+                const int j = threadIdx.x / SC_WARPS, w = threadIdx.x % SC_WARPS;
+                fa.cnt[((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + w] = 0;
+            }
+            if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
+            if (in_flight) {   // its table was requested all the same: let the copy land before the barrier is reused
+                const bool landed = mbar_wait(bar, phase);
+                phase ^= 1u;
+                in_flight = false;
+                if (!__syncthreads_and(landed)) {
+                    if (threadIdx.x == 0 && status != nullptr) atomicOr(status, SK_DEV_WAIT_TIMEOUT);
+                    return;
+                }
+            }
+            continue;
+        }
+
+        if (!in_flight) {
+            __syncthreads();                    // previous segment's lookups are done before the table is overwritten
+            if (threadIdx.x == 0) request_table(g);
+        }
+        in_flight = false;
+        const float K0p = __ldcg(qpar + g) + 33.0f;
+
+        // each warp owns a contiguous run of the segment's live keys (a multiple of 32 long)
+        const int per_warp = (int)(((t1 - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32);
+        const int ws = (int)t0 + warp * per_warp;
+        const int we = min((int)t1, ws + per_warp);
+        // the lane's keys are 32 apart, so its visiting order (key index & 15) is fixed per segment
+        const uint32_t m = (uint32_t)(ws + lane) & 15u;
+        const uint32_t sel_lo = 0x3210u ^ (0x1111u * (m & 7u));
+        const uint32_t sel_hi = 0x7654u ^ (0x1111u * (m & 7u));
+        const bool swap = (m & 8u) != 0u;
+        uint32_t X[6];
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+            uint32_t v = (tab >> 16) << 24;
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                const uint32_t p = (uint32_t)(3 * i + c);
+                if (p < 16u) v |= (8u * (p ^ m)) << (8 * c);
+            }
+            X[i] = v;
+        }
+        const uint8_t* cg = codes + (size_t)bk * Tcap * L;
+        const __half* vg = v_norm + (size_t)bk * Tcap;
+
+        uint32_t cur[8], nxt[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cur[i] = nxt[i] = 0u;
+        uint16_t vcur = 0, vnxt = 0;                                 // ||v|| (fp16 bits) travels with the codes
+        int t = ws + lane;
+        if (t < we) {
+            ldg256(cg + (size_t)t * L, cur);
+            vcur = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t);
+        }
+        if (t + 32 < we) {
+            ldg256(cg + (size_t)(t + 32) * L, nxt);
+            vnxt = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t + 32);
+        }
+
+        const bool ok = mbar_wait(bar, phase);
+        phase ^= 1u;
+        if (!__syncthreads_and(ok)) {
+            if (threadIdx.x == 0 && status != nullptr) atomicOr(status, SK_DEV_WAIT_TIMEOUT);
+            return;
+        }
+
+        uint32_t cnt4 = 0;            // four 8-bit run lengths, saturating at 255 (cap_w <= 250)
+        float cutv[HT];
+#pragma unroll
+        for (int j = 0; j < HT; ++j) cutv[j] = -INFINITY;
+        const int run_stride = fa.chunks_max * SC_WARPS * fa.cap_w;
+        const int run_index0 = (((int)row0 * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w;
+
+        // scores of the key held in cur/vcur: the packed entries and the upper bounds
+        auto score_cur = [&](uint32_t (&pk)[HT], float (&sv)[HT]) {
+            uint32_t a0, b0, a1, b1;
+            packed_half<0>(cur, swap, sel_lo, sel_hi, X, a0, b0);
+            packed_half<128>(cur + 4, swap, sel_lo, sel_hi, X, a1, b1);
+            const uint32_t S[HT] = {(a0 & 0xffffu) + (a1 & 0xffffu), (a0 >> 16) + (a1 >> 16),
+                                    (b0 & 0xffffu) + (b1 & 0xffffu), (b0 >> 16) + (b1 >> 16)};
+            const uint32_t vb = (uint32_t)vcur & 0x7fffu;
+            const float vn = __half2float(__ushort_as_half((unsigned short)vb));
+#pragma unroll
+            for (int j = 0; j < HT; ++j) {
+                sv[j] = packed_upper(S[j], K0p, vn);
+                pk[j] = (S[j] << 15) | vb;
+            }
+        };
+        auto keep = [&](const uint32_t (&pk)[HT], const float (&sv)[HT], bool valid, int tk) {
+#pragma unroll
+            for (int j = 0; j < HT; ++j) {
+                const bool hit = valid && sv[j] >= cutv[j];
+                const unsigned bal = __ballot_sync(FULL, hit);
+                if (bal != 0u) {                              // warp-uniform
+                    const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
+                    const int pos = have + __popc(bal & ((1u << lane) - 1u));
+                    if (hit && pos < fa.cap_w)
+                        fa.cand[(size_t)(run_index0 + j * run_stride + pos)] = make_uint2(pk[j], (uint32_t)tk);
+                    cnt4 += (uint32_t)min(__popc(bal), 255 - have) << (8 * j);
+                }
+            }
+        };
+
+        {
+            // ---- sample = first key of every lane: scores, cut
+            float sv[HT];
+            uint32_t pk[HT];
+            const bool valid = t < we;
+            score_cur(pk, sv);
+            if (!valid) {
+#pragma unroll
+                for (int j = 0; j < HT; ++j) sv[j] = 0.f;
+            }
+            if (t1 - t0 <= 1024 && 2 * (t1 - t0) <= slots_per_cta && per_warp <= fa.cap_w) {   // uniform across the CTA
+                if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
+            } else {
+                filter_cuts<HT>(fs, sv, valid, fminf(__fdividef(fa.keep, (float)Teff), 1.0f),
+                                fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
+            }
+            keep(pk, sv, valid, t);
+        }
+        t += 32;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+        vcur = vnxt;
+        if (t + 32 < we) {
+            ldg256(cg + (size_t)(t + 32) * L, nxt);
+            vnxt = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t + 32);
+        }
+        for (; t - lane < we; t += 32) {
+            const bool valid = t < we;
+            float sv[HT];
+            uint32_t pk[HT];
+            score_cur(pk, sv);
+            keep(pk, sv, valid, t);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+            vcur = vnxt;
+            if (t + 64 < we) {
+                ldg256(cg + (size_t)(t + 64) * L, nxt);
+                vnxt = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t + 64);
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < HT; ++j)
+                fa.cnt[((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp] = (int32_t)((cnt4 >> (8 * j)) & 0xffu);
+        }
+    }
+}
+
 // Reference-surface scorer: [B,H,L,T] int16 codes, ascending-table summation.
 __global__ void __launch_bounds__(256)
 score_compat_kernel(const float* __restrict__ q_probs, const int16_t* __restrict__ key_buckets,
@@ -443,9 +734,13 @@ size_t score_select_workspace_bytes(int B, int H, int Hkv, int L, int64_t T, int
     return make_fused_layout((int64_t)B * H, plan, T).total;
 }
 
+bool packed_filter_applicable(int H, int Hkv, int L, int R) {
+    return Hkv > 0 && H % Hkv == 0 && L == 32 && R >= 1 && R <= 256 && lut_head_tile(H / Hkv) == 4;
+}
+
 int launch_score_filter(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
                         int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
-                        void* workspace, int32_t* status, cudaStream_t st) {
+                        void* workspace, int32_t* status, cudaStream_t st, const void* lutq, const float* qpar) {
     const int ht = lut_head_tile(H / Hkv);
     const ScorePlan plan = make_score_plan(B * Hkv * ((H / Hkv) / ht), T, M);
     const FusedLayout lay = make_fused_layout((int64_t)B * H, plan, T);
@@ -457,6 +752,20 @@ int launch_score_filter(const float* lut, const uint8_t* codes, const uint16_t* 
     fa.chunks_max = plan.chunks_max;
     fa.cap_w = plan.cap_w;
     fa.keep = plan.frac * (float)T;
+    if (lutq != nullptr) {
+        if (!packed_filter_applicable(H, Hkv, L, R) || qpar == nullptr)
+            return fail(SK_ERR_UNSUPPORTED, "packed scorer: needs L=32, R<=256 and a multiple of 4 query heads per KV head");
+        if (reinterpret_cast<uintptr_t>(codes) % 32 != 0 || reinterpret_cast<uintptr_t>(lutq) % 16 != 0)
+            return fail(SK_ERR_MISALIGNED, "packed scorer: codes must be 32-byte aligned, the table 16-byte aligned");
+        cudaError_t e = cudaFuncSetAttribute(score_packed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PK_SMEM);
+        if (e != cudaSuccess) return fail(SK_ERR_CUDA, "score_packed_kernel smem attribute: %s", cudaGetErrorString(e));
+        const int n_groups = B * Hkv * ((H / Hkv) / 4);
+        e = launch_chained(score_packed_kernel, dim3((unsigned)plan.grid), dim3(SC_THREADS), (size_t)PK_SMEM, st,
+                           (const uint8_t*)lutq, qpar, codes, (const __half*)v_norm, H, Hkv, R, T, T_dev, Tcap,
+                           plan.Tslots, plan.per_cta, n_groups, status, fa);
+        if (e != cudaSuccess) return fail(SK_ERR_CUDA, "score_packed_kernel: %s", cudaGetErrorString(e));
+        return check_launch("score_packed_kernel");
+    }
 #define SK_SCORE_CASE(LL, HT)                                                                      \
     if (L == LL && ht == HT)                                                                       \
         return score_launch<LL, HT, true>(lut, codes, v_norm, nullptr, B, H, Hkv, R, T, T_dev, Tcap, \

@@ -37,6 +37,7 @@ struct SelShared {
     uint32_t hist[SEL_BINS];
     uint32_t cand_key[SEL_CAP];
     int32_t cand_idx[SEL_CAP];
+    uint32_t cand_aux[SEL_CAP];                   // packed candidates: the (S, ||v||) word of every candidate
     int scan_buf[2][40];
     uint32_t red_lo[SEL_WARPS], red_hi[SEL_WARPS];
     int thr_bin, thr_above, thr_inbin;
@@ -669,7 +670,185 @@ struct CandArgs {
     const __half* v_norm;
     int H, Hkv, L, R, ht;
     int64_t Tcap;
+    const float* qpar;      // packed candidates: K0 of every KV-head group
 };
+
+// ------------------------------------------------------------------------------------------
+// Packed candidates (written by score_packed_kernel): every entry carries the exact integer sum S
+// of the key's 12-bit table entries and ||v||.  With K0 = L * lo * C of the group's table,
+//     X = C * sum_l p_l(code_l) - ... lies in [S - 0.1, S + 32.1)            (table construction)
+// and the fp32 score the exact scorer computes, e = fl(sum_l p_l) * ||v||, satisfies
+//     (S + K0 - 1) * ||v|| * (1 - 2^-21)  <=  C * e  <=  (S + K0 + 33) * ||v|| * (1 + 2^-21)
+// (fp32 summation and the two roundings of the bound itself are far inside the slack of 0.9).
+// Call the two sides lo_i and up_i.  The candidates are all keys with up_i >= their chunk's cut.
+// ------------------------------------------------------------------------------------------
+constexpr int BAND_MAX = 2048;                    // keys between the brackets that can be rescored on chip
+constexpr int BAND_DIRECT = 256;                  // up to here the band is ranked pair by pair
+
+__device__ __forceinline__ float packed_upper_sel(uint32_t S, float K0p, float vn) {
+    return __fmul_rn(__fadd_rn(__uint2float_rn(S), K0p), vn);     // same operations as the scorer
+}
+__device__ __forceinline__ float packed_lower_sel(uint32_t S, float K0m, float vn) {
+    const float v = __fmul_rn(__fadd_rn(__uint2float_rn(S), K0m), vn) * (1.0f - 4.8e-7f);
+    return fmaxf(v, 0.f);
+}
+
+// Exact fp32 score of key t for head column j of the group's table, the tables added in the very
+// order score_kernel adds them for this key (groups of 8 tables ascending, inside a group table
+// u ^ (t & 7) at step u), so that the value equals sk_score's bit for bit.
+__device__ __forceinline__ float exact_score_like_scorer(const float* __restrict__ lut_g, int ht, int j,
+                                                         const uint8_t* __restrict__ cg, const __half* __restrict__ vg,
+                                                         int t, int L, int R_unused) {
+    (void)R_unused;
+    const uint4* cp = reinterpret_cast<const uint4*>(cg + (size_t)t * L);
+    const int m = t & 7;
+    float sum = 0.f;
+    for (int v = 0; v < L / 16; ++v) {
+        const uint4 w4 = __ldcg(cp + v);
+        const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+        float term[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+            const int tb = (q & 8) | ((q & 7) ^ m);                       // table inside this group of 16
+            const uint32_t code = (w[tb >> 2] >> (8 * (tb & 3))) & 0xffu;
+            term[q] = __ldcg(lut_g + ((size_t)code * L + v * 16 + tb) * ht + j);
+        }
+#pragma unroll
+        for (int q = 0; q < 16; ++q) sum += term[q];
+    }
+    return sum * __half2float(__ldcg(vg + t));
+}
+
+
+// Exact top-Me of a row from its packed candidates (keys = order keys of up_i in cand_key, the
+// packed words in cand_aux, both in index order; hist zero on entry).  Returns false, with nothing
+// usable written, when the result cannot be proved or held on chip; the caller then rescans the row.
+//
+// One histogram of the up_i finds the bin that holds the Me-th largest; its upper edge UB bounds
+// C * (k-th exact score) from above, and LB = min lo_i over the candidates in that bin or higher
+// (at least Me keys) bounds it from below.  A key outside the candidate set has
+// up < its chunk's cut <= chi, so with chi <= LB it lies strictly below the k-th exact score.
+// Candidates with lo_i > UB are in the top Me, those with up_i < LB are not, and the few in
+// between are scored exactly (fp32 table, sk_score's summation order) and ranked by (score
+// descending, index ascending).  Output in ascending index order.
+__device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan, int n, int Me, uint32_t kmin,
+                                                       uint32_t kmax, uint32_t chi_key, float K0m,
+                                                       const float* __restrict__ lut_g, int ht, int hj,
+                                                       const uint8_t* __restrict__ cg,
+                                                       const __half* __restrict__ vg, int L,
+                                                       int32_t* __restrict__ heavy) {
+    const int tid = threadIdx.x;
+    const uint32_t range = kmax - kmin;
+    const int bits = range == 0 ? 0 : 32 - __clz(range);
+    const int shift = max(0, bits - 12);
+    for (int base = 0; base < n; base += SEL_THREADS) {
+        const int i = base + tid;
+        const uint32_t k = i < n ? s.cand_key[i] : kmin;
+        warp_hist_add(s.hist, (k - kmin) >> shift, i < n);
+    }
+    __syncthreads();
+    find_bin_desc(s, scan, Me);
+    const uint32_t thr = (uint32_t)s.thr_bin;
+    uint64_t ub64 = (uint64_t)kmin + (((uint64_t)thr + 1u) << shift) - 1u;
+    if (ub64 > (uint64_t)kmax) ub64 = kmax;
+    const float UB = order_key_inverse((uint32_t)ub64);
+
+    const int ept = (n + SEL_THREADS - 1) / SEL_THREADS;
+    const int i0 = tid * ept, i1 = min(n, i0 + ept);
+    auto lower_of = [&](uint32_t x) {
+        return packed_lower_sel(x >> 15, K0m, __half2float(__ushort_as_half((unsigned short)(x & 0x7fffu))));
+    };
+    uint32_t lbk = 0x7f800000u, dummy = 0u;          // +inf; non-negative floats order like their bit patterns
+    for (int i = i0; i < i1; ++i) {
+        if (((s.cand_key[i] - kmin) >> shift) >= thr) lbk = min(lbk, __float_as_uint(lower_of(s.cand_aux[i])));
+    }
+    block_minmax(s, lbk, dummy);
+    const float LB = __uint_as_float(lbk);
+    if (order_key(LB) < chi_key) return false;        // some chunk may have dropped a key of the top Me
+
+    // ---- classes: 1 = in, 2 = between the brackets, 0 = out
+    int n_sure = 0, n_band = 0;
+    for (int i = i0; i < i1; ++i) {
+        const float up = order_key_inverse(s.cand_key[i]);
+        const float lo = lower_of(s.cand_aux[i]);
+        const uint32_t cls = lo > UB ? 1u : (up >= LB ? 2u : 0u);
+        s.cand_key[i] = cls;
+        n_sure += cls == 1u;
+        n_band += cls == 2u;
+    }
+    int total;
+    const int off = scan.excl(n_sure | (n_band << 16), total, s);
+    const int tot_sure = total & 0xffff, tot_band = total >> 16;
+    const int want = Me - tot_sure;
+    if (tot_band > BAND_MAX || want < 1 || want > tot_band) return false;
+    // every read of cand_aux happened before the scan's barriers: its space now holds the band
+    uint32_t* band_e = s.cand_aux;                                     // [BAND_MAX] exact order keys
+    int32_t* band_t = reinterpret_cast<int32_t*>(s.cand_aux + BAND_MAX);   // [BAND_MAX] key index, then "taken" flag
+    {
+        int bpos = off >> 16;
+        for (int i = i0; i < i1; ++i) {
+            if (s.cand_key[i] == 2u) {
+                band_t[bpos] = s.cand_idx[i];
+                s.cand_key[i] = 2u + (uint32_t)bpos;
+                ++bpos;
+            }
+        }
+    }
+    __syncthreads();
+    for (int jb = tid; jb < tot_band; jb += SEL_THREADS)
+        band_e[jb] = order_key(exact_score_like_scorer(lut_g, ht, hj, cg, vg, band_t[jb], L, 0));
+    __syncthreads();
+
+    if (tot_band <= BAND_DIRECT) {
+        // four threads per key count the keys that precede it
+        const int kb = tid >> 2, part = tid & 3;
+        int cnt = 0;
+        if (kb < tot_band) {
+            const uint32_t mine = band_e[kb];
+            for (int jj = part; jj < tot_band; jj += 4) {
+                const uint32_t kj = band_e[jj];
+                cnt += (kj > mine) || (kj == mine && jj < kb);
+            }
+        }
+        cnt += __shfl_xor_sync(FULL, cnt, 1);
+        cnt += __shfl_xor_sync(FULL, cnt, 2);
+        if (kb < tot_band && part == 0) band_t[kb] = cnt < want;
+        __syncthreads();
+    } else {
+        uint32_t quota;
+        const uint32_t kth = smem_kth(s, scan, band_e, tot_band, (uint32_t)want, quota);
+        const int ept2 = (tot_band + SEL_THREADS - 1) / SEL_THREADS;
+        const int j0 = tid * ept2, j1 = min(tot_band, j0 + ept2);
+        int n_eq = 0;
+        for (int jb = j0; jb < j1; ++jb) n_eq += band_e[jb] == kth;
+        int tot2;
+        int eq_before = scan.excl(n_eq, tot2, s);
+        for (int jb = j0; jb < j1; ++jb) {
+            const uint32_t e = band_e[jb];
+            int take = e > kth;
+            if (e == kth) take = eq_before++ < (int)quota;
+            band_t[jb] = take;
+        }
+        __syncthreads();
+    }
+
+    // ---- ordered emission
+    int n_sel = 0;
+    for (int i = i0; i < i1; ++i) {
+        const uint32_t cls = s.cand_key[i];
+        n_sel += cls == 1u || (cls >= 2u && band_t[cls - 2u] != 0);
+    }
+    int tot_sel;
+    int pos = scan.excl(n_sel, tot_sel, s);
+    for (int i = i0; i < i1; ++i) {
+        const uint32_t cls = s.cand_key[i];
+        if (cls == 1u || (cls >= 2u && band_t[cls - 2u] != 0)) {
+            if (pos < Me) heavy[pos] = s.cand_idx[i];
+            ++pos;
+        }
+    }
+    return tot_sel == Me;
+}
 
 __global__ void __launch_bounds__(SEL_THREADS, 1)
 select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev, int64_t M,
@@ -690,8 +869,25 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
     const int64_t last_cta = ((int64_t)(g + 1) * a.Tslots - 1) / a.per_cta;
     const int n_runs = (int)(last_cta - first_cta + 1) * SC_WARPS;      // <= 1024
     const int32_t* cnt = a.cnt + row * a.chunks_max * SC_WARPS;
+    const bool packed = a.qpar != nullptr;
     pdl_launch_dependents();
     pdl_wait();                               // the runs, their lengths and the cuts come from the scorer
+    const float K0 = packed ? __ldcg(a.qpar + g) : 0.f;
+    // one candidate into shared memory: its order key (of the score, or of the packed entry's upper bound)
+    auto put = [&](int i, uint2 e, uint32_t& kmin, uint32_t& kmax) {
+        uint32_t k;
+        if (packed) {
+            const float vn = __half2float(__ushort_as_half((unsigned short)(e.x & 0x7fffu)));
+            k = order_key(packed_upper_sel(e.x >> 15, K0 + 33.0f, vn));
+            s.cand_aux[i] = e.x;
+        } else {
+            k = order_key(__uint_as_float(e.x));
+        }
+        s.cand_key[i] = k;
+        s.cand_idx[i] = (int32_t)e.y;
+        kmin = min(kmin, k);
+        kmax = max(kmax, k);
+    };
     // run length and chunk cut of this thread: issued before anything waits on the live length
     const int c_run = tid < n_runs ? __ldcg(cnt + tid) : 0;
     const float cut_chunk = tid < n_runs / SC_WARPS ? __ldcg(a.cut + row * a.chunks_max + tid) : -INFINITY;
@@ -752,13 +948,7 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const int i = base + u * SEL_THREADS + tid;
-                        if (i < total) {
-                            const uint32_t k = order_key(__uint_as_float(e[u].x));
-                            s.cand_key[i] = k;
-                            s.cand_idx[i] = (int32_t)e[u].y;
-                            kmin = min(kmin, k);
-                            kmax = max(kmax, k);
-                        }
+                        if (i < total) put(i, e[u], kmin, kmax);
                     }
                 }
             } else {
@@ -773,27 +963,30 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                     const int o = (int)s.hist[2 * r], n = (int)s.hist[2 * r + 1];
                     const uint2* src = cand + (size_t)r * a.cap_w;
                     for (int i = lane; i < n; i += 32) {
-                        const uint2 e = __ldcg(src + i);
-                        const uint32_t k = order_key(__uint_as_float(e.x));
-                        s.cand_key[o + i] = k;
-                        s.cand_idx[o + i] = (int32_t)e.y;
-                        kmin = min(kmin, k);
-                        kmax = max(kmax, k);
+                        put(o + i, __ldcg(src + i), kmin, kmax);
                     }
                 }
                 __syncthreads();
                 for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
             }
             block_minmax(s, kmin, kmax);               // also the barrier after the gather
-            uint32_t kth = 0;
-            if (!emit_candidates_binned(s, scan, total, Me, Me, kmin, kmax, heavy, kth)) {
-                __syncthreads();
-                kth = emit_from_candidates(s, scan, total, Me, 0, Me, heavy);
+            if (packed) {
+                const int j = hj % a.ht;
+                exact = emit_packed_candidates(s, scan, total, Me, kmin, kmax, chi, K0 - 1.0f,
+                                               a.lut + (size_t)g * a.R * a.L * a.ht, a.ht, j,
+                                               a.codes + (size_t)(b * a.Hkv + kvh) * a.Tcap * a.L,
+                                               a.v_norm + (size_t)(b * a.Hkv + kvh) * a.Tcap, a.L, heavy);
+            } else {
+                uint32_t kth = 0;
+                if (!emit_candidates_binned(s, scan, total, Me, Me, kmin, kmax, heavy, kth)) {
+                    __syncthreads();
+                    kth = emit_from_candidates(s, scan, total, Me, 0, Me, heavy);
+                }
+                exact = kth >= chi;                    // uniform: kth and chi are block-wide values
             }
-            exact = kth >= chi;                        // uniform: kth and chi are block-wide values
         }
         if (!exact) {
-            // ---- rescore this row (tables added in ascending order), then the full-row select
+            // ---- rescore this row (tables added in the scorer's order), then the full-row select
             if (tid == 0) atomicAdd(a.n_fallback, 1);
             __syncthreads();
             float* tab = reinterpret_cast<float*>(s.cand_key);           // [L][R] of this head
@@ -808,13 +1001,16 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
             const __half* vg = a.v_norm + (size_t)(b * a.Hkv + kvh) * a.Tcap;
             for (int t = tid; t < T; t += SEL_THREADS) {
                 const uint4* cp = reinterpret_cast<const uint4*>(cg + (size_t)t * a.L);
+                const int m = t & 7;                   // the scorer's table order for this key
                 float sum = 0.f;
                 for (int v = 0; v < a.L / 16; ++v) {
                     const uint4 w4 = __ldcg(cp + v);
                     const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-                    for (int q = 0; q < 16; ++q)
-                        sum += tab[(v * 16 + q) * a.R + ((w[q >> 2] >> (8 * (q & 3))) & 0xffu)];
+                    for (int q = 0; q < 16; ++q) {
+                        const int tb = (q & 8) | ((q & 7) ^ m);
+                        sum += tab[(v * 16 + tb) * a.R + ((w[tb >> 2] >> (8 * (tb & 3))) & 0xffu)];
+                    }
                 }
                 sc[t] = sum * __half2float(__ldcg(vg + t));
             }
@@ -853,7 +1049,8 @@ int launch_select_list(const float* scores, int64_t score_row_stride, const uint
 int launch_select_candidates(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
                              int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
                              int sink, int window, int sorted, int32_t* list, int64_t list_row_stride,
-                             int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st) {
+                             int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st,
+                             const float* qpar) {
     (void)status;
     if (sorted) return fail(SK_ERR_UNSUPPORTED, "fused score+select: sorted output not supported");
     const int ht = lut_head_tile(H / Hkv);
@@ -877,6 +1074,7 @@ int launch_select_candidates(const float* lut, const uint8_t* codes, const uint1
     a.v_norm = reinterpret_cast<const __half*>(v_norm);
     a.H = H; a.Hkv = Hkv; a.L = L; a.R = R; a.ht = ht;
     a.Tcap = Tcap;
+    a.qpar = qpar;
     if ((size_t)L * R * 4 > sizeof(uint32_t) * SEL_CAP)
         return fail(SK_ERR_UNSUPPORTED, "fused score+select: L*R too large for the rescoring table");
     const size_t smem = sizeof(SelShared);

@@ -22,10 +22,11 @@ template <typename QT, typename PT>
 __global__ void __launch_bounds__(SH_THREADS)
 soft_hash_kernel(const QT* __restrict__ q, const PT* __restrict__ planes,
                  const float* __restrict__ protos_T, float inv_temperature, int H, int Hkv, int D,
-                 int L, int P, int R, int ht, float* __restrict__ q_probs, float* __restrict__ lut) {
+                 int L, int P, int R, int ht, float* __restrict__ q_probs, float* __restrict__ lut,
+                 uint2* __restrict__ lutq, float* __restrict__ qpar) {
     extern __shared__ __align__(16) float sh_smem[];
     soft_hash_body<QT, PT>(q, planes, protos_T, inv_temperature, H, Hkv, D, L, P, R, ht, blockIdx.y,
-                           blockIdx.x * (SH_WARPS / ht), q_probs, lut, sh_smem);
+                           blockIdx.x * (SH_WARPS / ht), q_probs, lut, sh_smem, lutq, qpar);
 }
 
 template <typename T>
@@ -63,7 +64,7 @@ lut_from_probs_kernel(const T* __restrict__ q_probs, int H, int Hkv, int L, int 
 
 int launch_soft_hash(const void* q, int q_dtype, const void* planes, int plane_dtype,
                      const float* protos_T, float temperature, int B, int H, int Hkv, int D, int L,
-                     int P, int R, float* q_probs, float* lut, cudaStream_t st) {
+                     int P, int R, float* q_probs, float* lut, cudaStream_t st, void* lutq, float* qpar) {
     const int rep = H / Hkv;
     const int ht = lut_head_tile(rep);
     const int tiles = rep / ht;
@@ -79,7 +80,8 @@ int launch_soft_hash(const void* q, int q_dtype, const void* planes, int plane_d
         if (smem > 48 * 1024)                                                                     \
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         kern<<<grid, SH_THREADS, smem, st>>>((const QT*)q, (const PT*)planes, protos_T, inv_t, H, \
-                                             Hkv, D, L, P, R, ht, q_probs, lut);                  \
+                                             Hkv, D, L, P, R, ht, q_probs, lut,                   \
+                                             (uint2*)lutq, qpar);                                 \
     } while (0)
     if (q_dtype == SK_F32 && plane_dtype == SK_F32) SK_SH_LAUNCH(float, float);
     else if (q_dtype == SK_BF16 && plane_dtype == SK_BF16) SK_SH_LAUNCH(__nv_bfloat16, __nv_bfloat16);

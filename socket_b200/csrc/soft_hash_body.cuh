@@ -19,9 +19,41 @@ __device__ __forceinline__ float warp_max_f(float x) {
     return x;
 }
 
-// shared memory (floats): protos [P*R] | t [SH_WARPS*16] | stage [tables_per_cta * R * ht]
+// shared memory (floats): protos [P*R] | t [SH_WARPS*16] | red [SH_WARPS] | stage [tables_per_cta * R * ht]
 inline size_t soft_hash_smem_bytes(int P, int R, int ht) {
-    return sizeof(float) * ((size_t)P * R + SH_WARPS * 16 + (size_t)(SH_WARPS / ht) * R * ht);
+    return sizeof(float) * ((size_t)P * R + SH_WARPS * 16 + SH_WARPS + (size_t)(SH_WARPS / ht) * R * ht);
+}
+
+// ---- 12-bit fixed-point copy of the scorer table (the filtering scorer's packed mode) ----------
+// entry = floor((p - lo) * C), 0 <= entry <= PK_QMAX, with lo and C the same for every table and
+// head of a call: they follow from a bound that needs no data, |tanh| <= 1, so every CTA computes
+// the same constants on its own.  With lam = max_r sum_p |protos_T[p][r]| / (sqrt(D) * temperature)
+// every logit lies in [-lam, lam], hence every probability in
+//   [1 / (1 + (R-1) e^{2 lam}),  1 / (1 + (R-1) e^{-2 lam})].
+// The sum of a key's L entries then satisfies   sum_l (p_l - lo) * C  in  [S - 0.1, S + L + 0.1),
+// which is what the candidate select relies on (see select.cu).  K0 = L * lo * C is handed on.
+constexpr int PK_QMAX = 4095;
+struct PackedQuant {
+    float lo, C, K0;
+};
+__device__ __forceinline__ PackedQuant packed_quant(float lam, int R, int L) {
+    PackedQuant q;
+    const float e2 = __expf(fminf(2.f * lam, 80.f));
+    const float lo = 1.f / (1.f + (float)(R - 1) * e2);
+    const float hi = 1.f / (1.f + (float)(R - 1) / e2);
+    q.lo = lo * (1.f - 1e-5f);                       // margins: the softmax is rounded arithmetic
+    const float range = fmaxf(hi * (1.f + 1e-5f) - q.lo, hi * 1e-6f);
+    float C = (float)PK_QMAX * (1.f - 1e-4f) / range;
+    // K0 <= 2^17, so S + K0 < 2^18: the fp32 summation error of an exact score (31 roundings,
+    // each at most 2^-24 of the sum) stays below half a table unit, inside the bracket's slack
+    const float cap = (float)(1 << 17) / ((float)L * fmaxf(q.lo, 1e-30f));
+    q.C = fminf(C, cap);
+    q.K0 = (float)L * q.lo * q.C;
+    return q;
+}
+__device__ __forceinline__ uint32_t packed_entry(float p, const PackedQuant& q) {
+    const int e = __float2int_rd((p - q.lo) * q.C);
+    return (uint32_t)min(max(e, 0), PK_QMAX);
 }
 
 // One CTA: head tile `g` (= (b*Hkv + kvh)*tiles + tile) and tables [l0, l0 + SH_WARPS/ht).
@@ -31,7 +63,8 @@ template <typename QT, typename PT>
 __device__ __forceinline__ void soft_hash_body(
     const QT* __restrict__ q, const PT* __restrict__ planes, const float* __restrict__ protos_T,
     float inv_temperature, int H, int Hkv, int D, int L, int P, int R, int ht, int g, int l0,
-    float* __restrict__ q_probs, float* __restrict__ lut, float* smem) {
+    float* __restrict__ q_probs, float* __restrict__ lut, float* smem,
+    uint2* __restrict__ lutq = nullptr, float* __restrict__ qpar = nullptr) {
     const int rep = H / Hkv;
     const int tiles = rep / ht;
     const int tile = g % tiles;
@@ -46,7 +79,8 @@ __device__ __forceinline__ void soft_hash_body(
 
     float* pr_s = smem;                           // [P][R]
     float* t_s = pr_s + (size_t)P * R;            // [SH_WARPS][16]
-    float* stage = t_s + SH_WARPS * 16;           // [tpc][R][ht]
+    float* red_s = t_s + SH_WARPS * 16;           // [SH_WARPS]
+    float* stage = red_s + SH_WARPS;              // [tpc][R][ht]
 
     // every global load of the CTA is issued before the first one is consumed: the protos (kept in
     // registers until the dot products are done) together with the plane / query rows
@@ -102,6 +136,17 @@ __device__ __forceinline__ void soft_hash_body(
     }
     if (lane < P) t_s[warp * 16 + lane] = tanhf(mine) * inv_sqrt_d;
     __syncthreads();
+    if (lutq != nullptr) {
+        // largest column sum of |protos_T|: one partial maximum per warp, combined after the next barrier
+        float cs = 0.f;
+        for (int r = threadIdx.x; r < R; r += SH_THREADS) {
+            float a = 0.f;
+            for (int p = 0; p < P; ++p) a += fabsf(pr_s[p * R + r]);
+            cs = fmaxf(cs, a);
+        }
+        cs = warp_max_f(cs);
+        if (lane == 0) red_s[warp] = cs;
+    }
 
     if (active) {
         const float* t = t_s + warp * 16;
@@ -174,13 +219,30 @@ __device__ __forceinline__ void soft_hash_body(
     __syncthreads();
     // scorer table rows: lut[g][r][l][0..ht)
     float* lut_g = lut + (size_t)g * R * L * ht;
+    const bool packed = lutq != nullptr && ht == 4;
+    PackedQuant pq = {0.f, 0.f, 0.f};
+    uint2* lutq_g = nullptr;
+    if (packed) {
+        float lam = 0.f;
+#pragma unroll
+        for (int w = 0; w < SH_WARPS; ++w) lam = fmaxf(lam, red_s[w]);
+        pq = packed_quant(lam * inv_sqrt_d * inv_temperature, R, L);
+        lutq_g = lutq + (size_t)g * 256 * L;          // 256 bucket slots whatever R is
+        if (l0 == 0 && threadIdx.x == 0) qpar[g] = pq.K0;
+    }
     for (int i = threadIdx.x; i < tpc * R; i += SH_THREADS) {
         const int lt2 = i / R, r = i - lt2 * R;
         if (l0 + lt2 >= L) continue;
         const float* src = stage + (size_t)i * ht;
         float* dst = lut_g + ((size_t)r * L + l0 + lt2) * ht;
-        if (ht == 4) *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
-        else if (ht == 2) *reinterpret_cast<float2*>(dst) = *reinterpret_cast<const float2*>(src);
+        if (ht == 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src);
+            *reinterpret_cast<float4*>(dst) = v;
+            if (packed)
+                lutq_g[(size_t)r * L + l0 + lt2] =
+                    make_uint2(packed_entry(v.x, pq) | (packed_entry(v.y, pq) << 16),
+                               packed_entry(v.z, pq) | (packed_entry(v.w, pq) << 16));
+        } else if (ht == 2) *reinterpret_cast<float2*>(dst) = *reinterpret_cast<const float2*>(src);
         else *dst = *src;
     }
 }

@@ -252,6 +252,58 @@ def score_select_list(lut: torch.Tensor, codes: torch.Tensor, v_norm: torch.Tens
     return lst, ln, workspace
 
 
+def packed_applicable(B: int, H: int, Hkv: int, L: int, R: int, T: int, M: int) -> bool:
+    return bool(lib().sk_packed_applicable(B, H, Hkv, L, R, T, M))
+
+
+def soft_hash_packed(q_bhd: torch.Tensor, planes: torch.Tensor, protos_T: torch.Tensor,
+                     temperature: float = 1.0, n_kv_heads: Optional[int] = None):
+    """q [B,H,D] -> (fp32 scorer table, packed 12-bit copy of it) for `score_select_packed`
+    (`sk_soft_hash_packed`)."""
+    _require_cuda(q_bhd, planes, protos_T)
+    B, H, D = q_bhd.shape
+    L, P, _ = planes.shape
+    R = protos_T.shape[1]
+    Hkv = n_kv_heads if n_kv_heads is not None else H
+    q = q_bhd.contiguous()
+    planes = planes.contiguous()
+    protos = protos_T.to(torch.float32).contiguous()
+    lut = torch.empty(B * H * L * R, dtype=torch.float32, device=q.device)
+    nbytes = int(lib().sk_packed_table_bytes(B, H, Hkv))
+    if nbytes == 0:
+        raise RuntimeError("soft_hash_packed: needs a multiple of 4 query heads per KV head")
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    check(lib().sk_soft_hash_packed(ptr(q), dtype_code(q), ptr(planes), dtype_code(planes), ptr(protos),
+                                    float(temperature), B, H, Hkv, D, L, P, R, ptr(lut), ptr(packed),
+                                    stream_ptr(q.device)), "sk_soft_hash_packed")
+    return lut, packed
+
+
+def score_select_packed(lut: torch.Tensor, packed: torch.Tensor, codes: torch.Tensor, v_norm: torch.Tensor,
+                        n_heads: int, T: int, M: int, sink: int, window: int, R: int = 256,
+                        T_dev: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                        stages: int = 3, out=None):
+    """The fused scorer + select on the packed table (`sk_score_select_packed`); same result as
+    `score_select_list`.  Returns (sparse_list, sparse_len, workspace)."""
+    _require_cuda(lut, packed, codes, v_norm)
+    B, Hkv, Tcap, L = codes.shape
+    M = min(M, T)
+    Ktot = list_len(T, sink, window, M)
+    if out is None:
+        lst = torch.empty(B, n_heads, Ktot, dtype=torch.int32, device=codes.device)
+        ln = torch.empty(B, n_heads, dtype=torch.int32, device=codes.device)
+    else:
+        lst, ln = out
+    need = int(lib().sk_score_select_workspace_bytes(B, n_heads, Hkv, L, T, M))
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.zeros(need, dtype=torch.uint8, device=codes.device)
+    check(lib().sk_score_select_packed(ptr(lut), ptr(packed), ptr(codes), ptr(v_norm), B, n_heads, Hkv, L, R, T,
+                                       ptr(T_dev), Tcap, M, sink, window, ptr(lst), Ktot, ptr(ln),
+                                       ptr(workspace), workspace.numel(), None, stages, stream_ptr(codes.device)),
+          "sk_score_select_packed")
+    return lst, ln, workspace
+
+
 def score_select_cluster_size(B: int, H: int, Hkv: int, L: int, R: int, T: int, M: int) -> int:
     """Cluster size (2..16) of the one-launch scorer + select for this shape on the current
     device, 0 when the shape is outside it."""
@@ -309,7 +361,7 @@ def sparse_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 
 
 # sk_select_path: how the decode step builds its list (all paths give the same list)
-SELECT_PATHS = {"auto": 0, "two_launch": 1, "filter": 2, "cluster": 3}
+SELECT_PATHS = {"auto": 0, "two_launch": 1, "filter": 2, "cluster": 3, "filter_f32": 4}
 
 
 class DecodeStep:

@@ -571,6 +571,20 @@ def test_run_to_run_determinism():
 
 
 # ---------------------------------------------------------------------------- fused scorer + select
+def _fused_lists(q, planes, codes_d, vn_d, H, Hkv, T, M, sink, window, T_dev=None):
+    """The fused scorer + select through every table form the shape allows: the fp32 table, and the
+    packed 12-bit table where there is one.  Yields (name, lut, list, list_len, rescored rows)."""
+    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv,
+                           want_probs=False, want_lut=True)
+    got, got_len, ws = ops.score_select_list(lut, codes_d, vn_d, H, T, M, sink, window, T_dev=T_dev)
+    yield "fp32", lut, got, got_len, int(ws[:4].view(torch.int32).item())
+    if ops.packed_applicable(q.shape[0], H, Hkv, 32, 256, T, M):
+        lut2, packed = ops.soft_hash_packed(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv)
+        assert torch.equal(lut2, lut)
+        got, got_len, ws = ops.score_select_packed(lut2, packed, codes_d, vn_d, H, T, M, sink, window, T_dev=T_dev)
+        yield "packed", lut, got, got_len, int(ws[:4].view(torch.int32).item())
+
+
 def _fused_vs_two_step(B, H, Hkv, T, M, sink, window, v_norm=None, seed=0, Tcap=None):
     g = torch.Generator().manual_seed(seed)
     Tcap = Tcap or T
@@ -579,20 +593,21 @@ def _fused_vs_two_step(B, H, Hkv, T, M, sink, window, v_norm=None, seed=0, Tcap=
     codes = torch.randint(0, 256, (B, Hkv, Tcap, 32), generator=g, dtype=torch.uint8)
     if v_norm is None:
         v_norm = (torch.rand(B, Hkv, Tcap, generator=g) + 10.5).to(torch.float16)
-    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv,
-                           want_probs=False, want_lut=True)
     codes_d, vn_d = cu(codes), cu(v_norm.contiguous())
-    scores = ops.score(lut, codes_d, vn_d, H, T)
-    want, want_len = ops.select_list(scores, T, M, sink, window)
-    got, got_len, ws = ops.score_select_list(lut, codes_d, vn_d, H, T, M, sink, window)
-    assert torch.equal(got_len, want_len)
-    nb = got.shape[-1] - min(M, T)
-    assert torch.equal(got[:, :, :nb], want[:, :, :nb])
-    assert torch.equal(torch.sort(got[:, :, nb:], dim=-1).values, torch.sort(want[:, :, nb:], dim=-1).values)
-    # and the selection is a true top-k of the scores
-    vals = torch.sort(torch.gather(scores, 2, got[:, :, nb:].long()), dim=-1, descending=True).values
-    assert torch.equal(vals, torch.topk(scores[:, :, :T], min(M, T), dim=-1).values)
-    return int(ws[:4].view(torch.int32).item())
+    n_resc = 0
+    for name, lut, got, got_len, resc in _fused_lists(q, planes, codes_d, vn_d, H, Hkv, T, M, sink, window):
+        scores = ops.score(lut, codes_d, vn_d, H, T)
+        want, want_len = ops.select_list(scores, T, M, sink, window)
+        assert torch.equal(got_len, want_len), name
+        nb = got.shape[-1] - min(M, T)
+        assert torch.equal(got[:, :, :nb], want[:, :, :nb]), name
+        # element for element: both emit the top-k in ascending index order
+        assert torch.equal(got[:, :, nb:], torch.sort(want[:, :, nb:], dim=-1).values), name
+        # and the selection is a true top-k of the scores
+        vals = torch.sort(torch.gather(scores, 2, got[:, :, nb:].long()), dim=-1, descending=True).values
+        assert torch.equal(vals, torch.topk(scores[:, :, :T], min(M, T), dim=-1).values), name
+        n_resc = max(n_resc, resc)
+    return n_resc
 
 
 @pytest.mark.parametrize("B,H,Hkv,T,M", [(1, 32, 8, 32768, 1024), (2, 8, 2, 20000, 512), (1, 4, 1, 4096, 64),
@@ -636,16 +651,14 @@ def test_fused_score_select_live_length_just_past_a_cta_boundary(extra):
     planes = torch.randn(32, 8, 128, generator=g)
     codes = cu(torch.randint(0, 256, (B, Hkv, Tcap, 32), generator=g, dtype=torch.uint8))
     vn = cu((torch.rand(B, Hkv, Tcap, generator=g) + 10.5).to(torch.float16))
-    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv, want_probs=False,
-                           want_lut=True)
     T_dev = torch.tensor(T_live, dtype=torch.int32, device=DEV)
-    got, got_len, ws = ops.score_select_list(lut, codes, vn, H, Tcap, M, 64, 256, T_dev=T_dev)
-    assert int(ws[:4].view(torch.int32).item()) == 0          # no row went through the rescoring path
-    scores = ops.score(lut, codes, vn, H, T_live)
-    want, want_len = ops.select_list(scores, T_live, M, 64, 256)
-    k = want.shape[-1]
-    assert (got_len == k).all()
-    assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values)
+    for name, lut, got, got_len, resc in _fused_lists(q, planes, codes, vn, H, Hkv, Tcap, M, 64, 256, T_dev=T_dev):
+        assert resc == 0, name                                 # no row went through the rescoring path
+        scores = ops.score(lut, codes, vn, H, T_live)
+        want, want_len = ops.select_list(scores, T_live, M, 64, 256)
+        k = want.shape[-1]
+        assert (got_len == k).all(), name
+        assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values), name
 
 
 @pytest.mark.parametrize("B,H,Hkv,Tcap,T_live,M", [(1, 32, 8, 65536, 32768, 1024), (1, 2, 1, 50001, 25592, 512),
@@ -658,16 +671,14 @@ def test_fused_score_select_capacity_well_above_the_live_length(B, H, Hkv, Tcap,
     planes = torch.randn(32, 8, 128, generator=g)
     codes = cu(torch.randint(0, 256, (B, Hkv, Tcap, 32), generator=g, dtype=torch.uint8))
     vn = cu((torch.rand(B, Hkv, Tcap, generator=g) + 10.5).to(torch.float16))
-    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv, want_probs=False,
-                           want_lut=True)
     T_dev = torch.tensor(T_live, dtype=torch.int32, device=DEV)
-    got, got_len, ws = ops.score_select_list(lut, codes, vn, H, Tcap, M, 8, 24, T_dev=T_dev)
-    assert int(ws[:4].view(torch.int32).item()) == 0
-    scores = ops.score(lut, codes, vn, H, T_live)
-    want, want_len = ops.select_list(scores, T_live, M, 8, 24)
-    k = want.shape[-1]
-    assert (got_len == k).all()
-    assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values)
+    for name, lut, got, got_len, resc in _fused_lists(q, planes, codes, vn, H, Hkv, Tcap, M, 8, 24, T_dev=T_dev):
+        assert resc == 0, name
+        scores = ops.score(lut, codes, vn, H, T_live)
+        want, want_len = ops.select_list(scores, T_live, M, 8, 24)
+        k = want.shape[-1]
+        assert (got_len == k).all(), name
+        assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values), name
 
 
 def test_fused_score_select_long_runs():
@@ -697,15 +708,65 @@ def test_fused_score_select_device_length_and_capacity():
     planes = torch.randn(32, 8, 128, generator=g)
     codes = cu(torch.randint(0, 256, (B, Hkv, Tcap, 32), generator=g, dtype=torch.uint8))
     vn = cu((torch.rand(B, Hkv, Tcap, generator=g) + 1).to(torch.float16))
-    _, lut = ops.soft_hash(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv, want_probs=False,
-                           want_lut=True)
     T_dev = torch.tensor(T_live, dtype=torch.int32, device=DEV)
-    got, got_len, _ = ops.score_select_list(lut, codes, vn, H, Tcap, M, 4, 16, T_dev=T_dev)
-    scores = ops.score(lut, codes, vn, H, T_live)
-    want, want_len = ops.select_list(scores, T_live, M, 4, 16)
-    k = want.shape[-1]
-    assert (got_len == k).all()
-    assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values)
+    for name, lut, got, got_len, _ in _fused_lists(q, planes, codes, vn, H, Hkv, Tcap, M, 4, 16, T_dev=T_dev):
+        scores = ops.score(lut, codes, vn, H, T_live)
+        want, want_len = ops.select_list(scores, T_live, M, 4, 16)
+        k = want.shape[-1]
+        assert (got_len == k).all(), name
+        assert torch.equal(torch.sort(got[:, :, :k], dim=-1).values, torch.sort(want, dim=-1).values), name
+
+
+@pytest.mark.parametrize("proto_kind,temperature,q_scale", [("corners", 0.3, 1.0), ("corners", 3.0, 0.05),
+                                                             ("gauss", 1.0, 1.0), ("tiny", 1.0, 1.0),
+                                                             ("gauss", 0.3, 0.2), ("wide", 1.0, 1.0)])
+def test_packed_score_select_other_tables(proto_kind, temperature, q_scale):
+    """The packed table's range comes from protos_T and the temperature alone: sharply peaked
+    tables (low temperature, wide prototypes), nearly flat ones (the reference's 0.02-scaled
+    initialisation) and unsaturated tanh (small queries) must all give the two-step list."""
+    B, H, Hkv, T, M, sink, window = 2, 8, 2, 24000, 384, 8, 24
+    g = torch.Generator().manual_seed(7 * len(proto_kind) + int(10 * temperature))
+    q = torch.randn(B, H, 128, generator=g) * q_scale
+    planes = torch.randn(32, 8, 128, generator=g)
+    protos = {"corners": hypercube_protos(8), "gauss": torch.randn(8, 256, generator=g) * 0.5,
+              "tiny": torch.randn(8, 256, generator=g) * 0.02,
+              "wide": torch.randn(8, 256, generator=g) * 6.0}[proto_kind]
+    codes = cu(torch.randint(0, 256, (B, Hkv, T, 32), generator=g, dtype=torch.uint8))
+    vn = cu((torch.rand(B, Hkv, T, generator=g) + 10.5).to(torch.float16))
+    lut, packed = ops.soft_hash_packed(cu(q), cu(planes), cu(protos), temperature, n_kv_heads=Hkv)
+    _, lut_ref = ops.soft_hash(cu(q), cu(planes), cu(protos), temperature, n_kv_heads=Hkv, want_probs=False,
+                               want_lut=True)
+    assert torch.equal(lut, lut_ref)
+    got, got_len, ws = ops.score_select_packed(lut, packed, codes, vn, H, T, M, sink, window)
+    scores = ops.score(lut, codes, vn, H, T)
+    want, want_len = ops.select_list(scores, T, M, sink, window)
+    nb = want.shape[-1] - M
+    assert torch.equal(got_len, want_len)
+    assert torch.equal(got[:, :, :nb], want[:, :, :nb])
+    assert torch.equal(got[:, :, nb:], torch.sort(want[:, :, nb:], dim=-1).values)
+
+
+def test_packed_table_entries_bound_the_fp32_table():
+    """Every 12-bit entry e of the packed table satisfies e <= (p - lo) * C < e + 1 for one (lo, C)
+    per call: recovered here from the entries themselves, the relation must hold with a slack far
+    below one unit, and no entry may sit at the clamps."""
+    B, H, Hkv = 1, 8, 2
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B, H, 128, generator=g)
+    planes = torch.randn(32, 8, 128, generator=g)
+    lut, packed = ops.soft_hash_packed(cu(q), cu(planes), cu(hypercube_protos(8)), 1.0, n_kv_heads=Hkv)
+    groups = B * Hkv
+    ent = packed[:groups * 65536].view(torch.int16).view(groups, 256, 32, 4).cpu().long()     # [g][r][l][head]
+    p = lut.view(groups, 256, 32, 4).cpu().double()
+    assert ent.min() > 0 and ent.max() < 4095
+    # least squares for entry + 0.5 ~ (p - lo) * C, then the residual must stay inside half a unit
+    x, y = p.flatten(), ent.flatten().double() + 0.5
+    C = ((x - x.mean()) * (y - y.mean())).sum() / ((x - x.mean()) ** 2).sum()
+    lo = x.mean() - y.mean() / C
+    resid = (p - lo) * C - ent.double()
+    assert resid.min() > -0.05 and resid.max() < 1.05
+    K0 = packed[groups * 65536:groups * 65536 + 4 * groups].view(torch.float32).cpu().double()
+    assert torch.allclose(K0, 32 * lo * C * torch.ones_like(K0), rtol=1e-3)
 
 
 # ---------------------------------------------------------------------------- one-launch scorer + select (clusters)
