@@ -74,7 +74,7 @@ def parse_args():
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--skip-stages", action="store_true", help="skip the per-kernel timing loops")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end loop")
-    ap.add_argument("--select-path", default="auto", choices=["auto", "two_launch", "filter", "cluster"],
+    ap.add_argument("--select-path", default="auto", choices=["auto", "two_launch", "filter", "filter_f32", "cluster"],
                     help="pin how the step builds its list (default: the library's own choice)")
     ap.add_argument("--seed", type=int, default=1234)
     return ap.parse_args()
@@ -385,6 +385,7 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
     us = {}
     if args.skip_stages:
         res["rescored_rows"] = step.rescored_rows()
+        res["select_stats"] = step.select_stats()
         return res
     from socket_b200._lib import lib, ptr, stream_ptr
     probs, lut = ops.soft_hash(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv, want_probs=False,
@@ -396,6 +397,7 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
     cluster = ops.score_select_cluster_size(B, H, Hkv, cfg.L, cfg.R, Tcap, cfg.topk)
     use_cluster = step.n_launches == 3
     extra = {}
+    extra_notes = {}
     if cluster and not use_cluster and full:
         # not the step's path for this shape, timed for comparison only
         lst_c, ln_c = ops.score_select_cluster(lut, cache.k_hard, cache.v_norm, H, T_now, cfg.topk, cfg.sink,
@@ -412,6 +414,25 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
             ptr(lut), ptr(cache.k_hard), ptr(cache.v_norm), B, H, Hkv, cfg.L, cfg.R, T_now, None, Tcap, cfg.topk,
             cfg.sink, cfg.window, ptr(lst), ktot, ptr(ln), None, stream_ptr(dev)))
         score_name = select_name = "score_select_cluster"
+    elif fused and ops.packed_applicable(B, H, Hkv, cfg.L, cfg.R, T_now, cfg.topk) and args.select_path in ("auto", "filter"):
+        # the step's middle launches: packed-table scan, then the bracketed exact select
+        lut, packed = ops.soft_hash_packed(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv)
+        us["soft_hash"] = time_kernel(lambda: ops.soft_hash_packed(q_s, attn.planes, attn.protos_T, 1.0,
+                                                                   n_kv_heads=Hkv))
+        lst, ln, fws = ops.score_select_packed(lut, packed, cache.k_hard, cache.v_norm, H, T_now, cfg.topk,
+                                               cfg.sink, cfg.window)
+        ktot = lst.shape[-1]
+
+        def packed_stage(stages):
+            return lambda: lib().sk_score_select_packed(
+                ptr(lut), ptr(packed), ptr(cache.k_hard), ptr(cache.v_norm), B, H, Hkv, cfg.L, cfg.R, T_now, None,
+                Tcap, cfg.topk, cfg.sink, cfg.window, ptr(lst), ktot, ptr(ln), ptr(fws), fws.numel(), None, stages,
+                stream_ptr(dev))
+        us["score_filter"] = time_kernel(packed_stage(1))
+        us["select_candidates"] = time_kernel(packed_stage(2))
+        score_name, select_name = "score_filter", "select_candidates"
+        extra_notes = {"score_filter": "packed 12-bit table scan (score_packed_kernel)",
+                       "select_candidates": "bracketed exact select on packed candidates"}
     elif fused:
         lst, ln, fws = ops.score_select_list(lut, cache.k_hard, cache.v_norm, H, T_now, cfg.topk, cfg.sink,
                                              cfg.window)
@@ -437,6 +458,8 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
         stages[name] = {"us": round(t_us, 2), "algorithmic_bytes": alg[name],
                         "achieved_gbs": None if gbs is None else round(gbs, 1),
                         "frac_of_hbm_peak": None if gbs is None else round(gbs / peak, 4)}
+        if name in extra_notes:
+            stages[name]["note"] = extra_notes[name]
     # prefill hashing of the whole context on the tensor cores (not part of the decode step)
     if full and dt == torch.bfloat16 and D == 128 and cfg.L == 32 and cfg.P == 8:
         n_rows = B * Hkv * T0
@@ -600,6 +623,7 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
                   "h2d_bytes_per_step": hd.h2d_bytes, "d2h_bytes_per_step": hd.d2h_bytes,
                   "ms_per_step": e2e_ms_step, "steps": len(e2e_ms)}
     res["rescored_rows"] = step.rescored_rows()
+    res["select_stats"] = step.select_stats()
     return res
 
 
@@ -656,11 +680,12 @@ def main():
             # (batch, head) rows that took the select kernel's exact-but-slow rescoring path, over
             # every step this process ran on the timed workspace (warm-up, timed loop, whole-step stage)
             "rescored_rows": res.get("rescored_rows"),
+            "select_stats": res.get("select_stats"),
         }
         if second is not None:
             line[args.secondary] = {k: second[k] for k in ("value", "ms_per_step", "us_per_layer", "config",
                                                             "roofline", "stages", "e2e", "clocks", "gpu_launches",
-                                                            "rescored_rows") if k in second}
+                                                            "rescored_rows", "select_stats") if k in second}
             line[args.secondary]["unit"] = UNIT
         print(json.dumps(line))
     if world > 1:

@@ -693,32 +693,54 @@ __device__ __forceinline__ float packed_lower_sel(uint32_t S, float K0m, float v
     return fmaxf(v, 0.f);
 }
 
-// Exact fp32 score of key t for head column j of the group's table, the tables added in the very
-// order score_kernel adds them for this key (groups of 8 tables ascending, inside a group table
-// u ^ (t & 7) at step u), so that the value equals sk_score's bit for bit.
-__device__ __forceinline__ float exact_score_like_scorer(const float* __restrict__ lut_g, int ht, int j,
-                                                         const uint8_t* __restrict__ cg, const __half* __restrict__ vg,
-                                                         int t, int L, int R_unused) {
-    (void)R_unused;
-    const uint4* cp = reinterpret_cast<const uint4*>(cg + (size_t)t * L);
-    const int m = t & 7;
-    float sum = 0.f;
-    for (int v = 0; v < L / 16; ++v) {
-        const uint4 w4 = __ldcg(cp + v);
-        const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
-        float term[16];
+// Exact fp32 scores of the keys band_t[0..n) for head column j of the group's table (L = 32), the
+// tables added in the very order score_kernel adds them for a key (groups of 8 tables ascending,
+// inside a group table u ^ (t & 7) at step u), so that the values equal sk_score's bit for bit.
+// A warp takes 8 keys at a time: lane q fetches the q-th term of the sum of each of them (code
+// byte, then table word - two round trips for the whole batch), the terms go through a padded
+// tile in shared memory, and lanes 0..7 add one key's 32 terms each, in order.
+constexpr int XS_KEYS = 8;                        // keys per warp and batch
+constexpr int XS_TILE = XS_KEYS * 33;             // floats per warp
+static_assert((2 * BAND_MAX + SEL_WARPS * XS_TILE) * 4 <= SEL_CAP * 4, "band arrays and tiles share cand_aux");
+__device__ __forceinline__ void exact_scores_like_scorer(const float* __restrict__ lut_g, int ht, int j,
+                                                         const uint8_t* __restrict__ cg,
+                                                         const __half* __restrict__ vg, const int32_t* band_t,
+                                                         int n, float* tile_all, uint32_t* band_e) {
+    constexpr int L = 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* tile = tile_all + warp * XS_TILE;
+    const int v16 = lane & 16, u = lane & 15;
+    for (int k0 = warp * XS_KEYS; k0 < n; k0 += SEL_WARPS * XS_KEYS) {
+        int t[XS_KEYS], tb[XS_KEYS];
+        uint32_t code[XS_KEYS];
 #pragma unroll
-        for (int q = 0; q < 16; ++q) {
-            const int tb = (q & 8) | ((q & 7) ^ m);                       // table inside this group of 16
-            const uint32_t code = (w[tb >> 2] >> (8 * (tb & 3))) & 0xffu;
-            term[q] = __ldcg(lut_g + ((size_t)code * L + v * 16 + tb) * ht + j);
+        for (int kk = 0; kk < XS_KEYS; ++kk) {
+            t[kk] = k0 + kk < n ? band_t[k0 + kk] : -1;
+            tb[kk] = v16 | (u & 8) | ((u & 7) ^ (t[kk] & 7));          // table of this lane's term
+            code[kk] = t[kk] >= 0 ? (uint32_t)__ldcg(cg + (size_t)t[kk] * L + tb[kk]) : 0u;
         }
+        // all table words of the batch are requested before any of them is stored (a load is not
+        // moved across the shared-memory stores below)
+        float term[XS_KEYS];
 #pragma unroll
-        for (int q = 0; q < 16; ++q) sum += term[q];
+        for (int kk = 0; kk < XS_KEYS; ++kk)
+            term[kk] = t[kk] >= 0 ? __ldcg(lut_g + ((size_t)code[kk] * L + tb[kk]) * ht + j) : 0.f;
+        const int mine = k0 + lane;
+        const int tm = (lane < XS_KEYS && mine < n) ? band_t[mine] : -1;
+        float vn = 0.f;
+        if (tm >= 0) vn = __half2float(__ldcg(vg + tm));
+#pragma unroll
+        for (int kk = 0; kk < XS_KEYS; ++kk) tile[kk * 33 + lane] = term[kk];
+        __syncwarp();
+        if (tm >= 0) {
+            float sum = 0.f;
+#pragma unroll
+            for (int q = 0; q < 32; ++q) sum += tile[lane * 33 + q];
+            band_e[mine] = order_key(sum * vn);
+        }
+        __syncwarp();
     }
-    return sum * __half2float(__ldcg(vg + t));
 }
-
 
 // Exact top-Me of a row from its packed candidates (keys = order keys of up_i in cand_key, the
 // packed words in cand_aux, both in index order; hist zero on entry).  Returns false, with nothing
@@ -736,7 +758,7 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
                                                        const float* __restrict__ lut_g, int ht, int hj,
                                                        const uint8_t* __restrict__ cg,
                                                        const __half* __restrict__ vg, int L,
-                                                       int32_t* __restrict__ heavy) {
+                                                       int32_t* __restrict__ heavy, int32_t* stats) {
     const int tid = threadIdx.x;
     const uint32_t range = kmax - kmin;
     const int bits = range == 0 ? 0 : 32 - __clz(range);
@@ -760,7 +782,10 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
     };
     uint32_t lbk = 0x7f800000u, dummy = 0u;          // +inf; non-negative floats order like their bit patterns
     for (int i = i0; i < i1; ++i) {
-        if (((s.cand_key[i] - kmin) >> shift) >= thr) lbk = min(lbk, __float_as_uint(lower_of(s.cand_aux[i])));
+        // the packed word is not needed again: its place takes the lower bound (float bits)
+        const uint32_t lob = __float_as_uint(lower_of(s.cand_aux[i]));
+        s.cand_aux[i] = lob;
+        if (((s.cand_key[i] - kmin) >> shift) >= thr) lbk = min(lbk, lob);
     }
     block_minmax(s, lbk, dummy);
     const float LB = __uint_as_float(lbk);
@@ -770,7 +795,7 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
     int n_sure = 0, n_band = 0;
     for (int i = i0; i < i1; ++i) {
         const float up = order_key_inverse(s.cand_key[i]);
-        const float lo = lower_of(s.cand_aux[i]);
+        const float lo = __uint_as_float(s.cand_aux[i]);
         const uint32_t cls = lo > UB ? 1u : (up >= LB ? 2u : 0u);
         s.cand_key[i] = cls;
         n_sure += cls == 1u;
@@ -780,6 +805,10 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
     const int off = scan.excl(n_sure | (n_band << 16), total, s);
     const int tot_sure = total & 0xffff, tot_band = total >> 16;
     const int want = Me - tot_sure;
+    if (tid == 0) {                                   // statistics: keys rescored, rows ranked by the radix path
+        atomicAdd(stats + 1, tot_band);
+        if (tot_band > BAND_DIRECT) atomicAdd(stats + 2, 1);
+    }
     if (tot_band > BAND_MAX || want < 1 || want > tot_band) return false;
     // every read of cand_aux happened before the scan's barriers: its space now holds the band
     uint32_t* band_e = s.cand_aux;                                     // [BAND_MAX] exact order keys
@@ -795,8 +824,8 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
         }
     }
     __syncthreads();
-    for (int jb = tid; jb < tot_band; jb += SEL_THREADS)
-        band_e[jb] = order_key(exact_score_like_scorer(lut_g, ht, hj, cg, vg, band_t[jb], L, 0));
+    exact_scores_like_scorer(lut_g, ht, hj, cg, vg, band_t, tot_band,
+                             reinterpret_cast<float*>(s.cand_aux + 2 * BAND_MAX), band_e);
     __syncthreads();
 
     if (tot_band <= BAND_DIRECT) {
@@ -805,6 +834,7 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
         int cnt = 0;
         if (kb < tot_band) {
             const uint32_t mine = band_e[kb];
+#pragma unroll 8
             for (int jj = part; jj < tot_band; jj += 4) {
                 const uint32_t kj = band_e[jj];
                 cnt += (kj > mine) || (kj == mine && jj < kb);
@@ -975,7 +1005,7 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                 exact = emit_packed_candidates(s, scan, total, Me, kmin, kmax, chi, K0 - 1.0f,
                                                a.lut + (size_t)g * a.R * a.L * a.ht, a.ht, j,
                                                a.codes + (size_t)(b * a.Hkv + kvh) * a.Tcap * a.L,
-                                               a.v_norm + (size_t)(b * a.Hkv + kvh) * a.Tcap, a.L, heavy);
+                                               a.v_norm + (size_t)(b * a.Hkv + kvh) * a.Tcap, a.L, heavy, a.n_fallback);
             } else {
                 uint32_t kth = 0;
                 if (!emit_candidates_binned(s, scan, total, Me, Me, kmin, kmax, heavy, kth)) {

@@ -440,3 +440,12 @@ class DecodeStep:
         if self._rescored_off < 0:
             return None
         return int(self.workspace[self._rescored_off:self._rescored_off + 4].view(torch.int32).item())
+
+    def select_stats(self) -> Optional[dict]:
+        """Counters of the candidate select over the steps run so far: rows rescored in full, keys
+        scored exactly inside the k-th score's bracket (packed table only), rows whose bracket was
+        large enough to be ranked by the radix pass.  Synchronises."""
+        if self._rescored_off < 0:
+            return None
+        c = self.workspace[self._rescored_off:self._rescored_off + 12].view(torch.int32).tolist()
+        return {"rescored_rows": c[0], "bracket_keys": c[1], "bracket_rows_radix": c[2]}

@@ -66,3 +66,50 @@ def all_reduce_sum(y: torch.Tensor, group=None) -> torch.Tensor:
     (the reference's hook reduces only `output[0]`, GPT-FAST/tp.py:140)."""
     dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
     return y
+
+
+# ------------------------------------------------------------------------------------------
+# Weight sharding of a whole model, the split GPT-FAST/tp.py:110-156 applies in place
+# ------------------------------------------------------------------------------------------
+def _rows(w: torch.Tensor, world_size: int, rank: int) -> torch.Tensor:
+    assert w.size(0) % world_size == 0
+    return torch.tensor_split(w, world_size, dim=0)[rank]
+
+
+def _cols(w: torch.Tensor, world_size: int, rank: int) -> torch.Tensor:
+    assert w.size(1) % world_size == 0
+    return torch.tensor_split(w, world_size, dim=1)[rank]
+
+
+def shard_qkv(wqkv: torch.Tensor, splits, world_size: int, rank: int) -> torch.Tensor:
+    """Column-parallel shard of the fused projection: q, k and v blocks are each split over the
+    ranks and re-concatenated, so a rank keeps whole heads (GPT-FAST/tp.py:73-77,124-129)."""
+    q, k, v = wqkv.split(list(splits), dim=0)
+    return torch.cat([_rows(q, world_size, rank), _rows(k, world_size, rank), _rows(v, world_size, rank)], dim=0)
+
+
+@torch.no_grad()
+def shard_transformer(full, world_size: int, rank: int):
+    """Rank `rank`'s shard of a single-device `socket_b200.model.Transformer`: `wqkv`, `w1`, `w3`
+    column-parallel, `wo`, `w2` row-parallel (GPT-FAST/tp.py:110-137), embeddings, norms, the
+    vocabulary projection and the hash parameters replicated.  The sharded model sums the partial
+    results of `wo` and `w2` over the ranks itself (`all_reduce_sum`)."""
+    from .model import Transformer
+    cfg = full.config
+    dev, dt = full.tok_embeddings.weight.device, full.tok_embeddings.weight.dtype
+    part = Transformer(cfg, world=world_size, rank=rank).to(device=dev, dtype=dt)
+    part.tok_embeddings.weight.copy_(full.tok_embeddings.weight)
+    part.norm.weight.copy_(full.norm.weight)
+    part.output.weight.copy_(full.output.weight)
+    for src, dst in zip(full.layers, part.layers):
+        a, b = src.attention, dst.attention
+        b.wqkv.weight.copy_(shard_qkv(a.wqkv.weight, [a.local_dim, a.kv_size, a.kv_size], world_size, rank))
+        b.wo.weight.copy_(_cols(a.wo.weight, world_size, rank))
+        b.planes.copy_(a.planes)
+        b.protos_T.copy_(a.protos_T)
+        dst.feed_forward.w1.weight.copy_(_rows(src.feed_forward.w1.weight, world_size, rank))
+        dst.feed_forward.w3.weight.copy_(_rows(src.feed_forward.w3.weight, world_size, rank))
+        dst.feed_forward.w2.weight.copy_(_cols(src.feed_forward.w2.weight, world_size, rank))
+        dst.attention_norm.weight.copy_(src.attention_norm.weight)
+        dst.ffn_norm.weight.copy_(src.ffn_norm.weight)
+    return part
