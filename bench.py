@@ -74,7 +74,7 @@ def parse_args():
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--skip-stages", action="store_true", help="skip the per-kernel timing loops")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer end-to-end loop")
-    ap.add_argument("--select-path", default="auto", choices=["auto", "two_launch", "filter", "filter_f32", "cluster"],
+    ap.add_argument("--select-path", default="auto", choices=["auto", "two_launch", "filter", "filter_f32", "filter_packed", "cluster"],
                     help="pin how the step builds its list (default: the library's own choice)")
     ap.add_argument("--seed", type=int, default=1234)
     return ap.parse_args()
@@ -414,7 +414,8 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
             ptr(lut), ptr(cache.k_hard), ptr(cache.v_norm), B, H, Hkv, cfg.L, cfg.R, T_now, None, Tcap, cfg.topk,
             cfg.sink, cfg.window, ptr(lst), ktot, ptr(ln), None, stream_ptr(dev)))
         score_name = select_name = "score_select_cluster"
-    elif fused and ops.packed_applicable(B, H, Hkv, cfg.L, cfg.R, T_now, cfg.topk) and args.select_path in ("auto", "filter"):
+    elif fused and (args.select_path == "filter_packed" or (
+            args.select_path in ("auto", "filter") and ops.packed_preferred(B, H, Hkv, cfg.L, cfg.R, Tcap, cfg.topk))):
         # the step's middle launches: packed-table scan, then the bracketed exact select
         lut, packed = ops.soft_hash_packed(q_s, attn.planes, attn.protos_T, 1.0, n_kv_heads=Hkv)
         us["soft_hash"] = time_kernel(lambda: ops.soft_hash_packed(q_s, attn.planes, attn.protos_T, 1.0,

@@ -240,7 +240,7 @@ SK_API int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, con
                      size_t workspace_bytes, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------
- * Packed form of the fused scorer + select (L = 32, R <= 256, query heads per KV head a multiple
+ * Packed form of the fused scorer + select (L = 32, R = 256, query heads per KV head a multiple
  * of 4): the scan reads a 12-bit fixed-point copy of the scorer table (8 bytes per bucket and table
  * for the four heads, summed as exact integers), which halves the shared-memory traffic of the scan;
  * the select brackets the k-th score with rigorous bounds and scores the few keys inside the
@@ -249,7 +249,8 @@ SK_API int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, con
  * (GPT-FAST/kernels/sparse.py:39-95 with soft_hash_collision.cu:25-54); the fixed-point table has no
  * counterpart in the reference.
  *
- *   sk_packed_table_bytes      size of the packed-table buffer [B*Hkv*(H/Hkv/4) x 64 KiB | constants]
+ *   sk_packed_table_bytes      size of the packed-table buffer [B*Hkv*(H/Hkv/4) x 64 KiB | constants |
+ *                              q_probs fp32, 32 KiB per (batch, head) row - read by the select]
  *   sk_soft_hash_packed        sk_soft_hash that writes the fp32 table AND its packed copy; the
  *                              quantisation range follows from protos_T and the temperature alone
  *                              (|tanh| <= 1), so it needs the soft hash, not just q_probs
@@ -258,6 +259,9 @@ SK_API int sk_sparse_decode(const void* q, int q_dtype, const void* k_cache, con
  * ---------------------------------------------------------------------------------- */
 SK_API size_t sk_packed_table_bytes(int B, int H, int Hkv);
 SK_API int sk_packed_applicable(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M);
+/* 1 where sk_decode_step's SK_SELECT_AUTO / SK_SELECT_FILTER take the packed form: shapes in which a
+ * CTA scans tens of thousands of keys; below that the fp32 scan is as fast and its select cheaper. */
+SK_API int sk_packed_preferred(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M);
 SK_API int sk_soft_hash_packed(const void* q, int q_dtype, const void* planes, int plane_dtype,
                         const float* protos_T, float temperature, int B, int H, int Hkv, int D, int L,
                         int P, int R, float* lut, void* packed, void* stream);
@@ -312,7 +316,8 @@ enum sk_select_path {
     SK_SELECT_TWO_LAUNCH = 1,   /* sk_score + sk_select_list (score matrix in the workspace) */
     SK_SELECT_FILTER = 2,       /* filtering scorer + candidate select, packed table where it applies */
     SK_SELECT_CLUSTER = 3,      /* sk_score_select_cluster                                   */
-    SK_SELECT_FILTER_F32 = 4    /* sk_score_filter + sk_select_candidates on the fp32 table  */
+    SK_SELECT_FILTER_F32 = 4,   /* sk_score_filter + sk_select_candidates on the fp32 table  */
+    SK_SELECT_FILTER_PACKED = 5 /* sk_score_select_packed, whatever the size                 */
 };
 
 typedef struct sk_decode_params {

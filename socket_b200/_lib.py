@@ -72,6 +72,7 @@ SIGNATURES = {
                                   _p, _sz, _p, _p]),
     "sk_packed_table_bytes": (_sz, [_i, _i, _i]),
     "sk_packed_applicable": (_i, [_i, _i, _i, _i, _i, _i64, _i64]),
+    "sk_packed_preferred": (_i, [_i, _i, _i, _i, _i, _i64, _i64]),
     "sk_soft_hash_packed": (_i, [_p, _i, _p, _i, _p, _f, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p]),
     "sk_score_select_packed": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _p, _i64, _i64, _i, _i, _p, _i64,
                                     _p, _p, _sz, _p, _i, _p]),

@@ -361,13 +361,25 @@ int sk_select_candidates(const float* lut, const uint8_t* codes, const uint16_t*
 static inline int packed_groups(int B, int H, int Hkv) { return B * Hkv * ((H / Hkv) / 4); }
 static inline size_t packed_param_offset(int B, int H, int Hkv) { return (size_t)packed_groups(B, H, Hkv) * 65536; }
 
+// [12-bit tables, 64 KiB per group | K0 per group | q_probs fp32, 32 KiB per (batch, head) row]
+static inline size_t packed_probs_offset(int B, int H, int Hkv) {
+    return packed_param_offset(B, H, Hkv) + up256((size_t)packed_groups(B, H, Hkv) * sizeof(float));
+}
 size_t sk_packed_table_bytes(int B, int H, int Hkv) {
     if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || (H / Hkv) % 4) return 0;
-    return packed_param_offset(B, H, Hkv) + up256((size_t)packed_groups(B, H, Hkv) * sizeof(float));
+    return packed_probs_offset(B, H, Hkv) + (size_t)B * H * 32 * 256 * sizeof(float);
 }
 
 int sk_packed_applicable(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M) {
     return sk_score_select_applicable(B, H, Hkv, L, R, T, M) && packed_filter_applicable(H, Hkv, L, R) ? 1 : 0;
+}
+
+// The packed scan pays for its extra table and the bracketed select once a CTA scans tens of
+// thousands of keys (measured: 128K context x batch 4 gains 12 %, 32K x batch 1 loses 8 %); the
+// boundary is the scorer plan's own switch to the flat split.
+int sk_packed_preferred(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M) {
+    if (!sk_packed_applicable(B, H, Hkv, L, R, T, M)) return 0;
+    return (int64_t)packed_groups(B, H, Hkv) * T / sm_count() >= 16384 ? 1 : 0;
 }
 
 int sk_soft_hash_packed(const void* q, int q_dtype, const void* planes, int plane_dtype,
@@ -381,13 +393,15 @@ int sk_soft_hash_packed(const void* q, int q_dtype, const void* planes, int plan
     SK_REQUIRE(valid_dtype(q_dtype) && valid_dtype(plane_dtype), "sk_soft_hash_packed: bad dtype");
     SK_REQUIRE(temperature > 0.f, "sk_soft_hash_packed: temperature must be positive");
     if (!packed_filter_applicable(H, Hkv, L, R))
-        return fail(SK_ERR_UNSUPPORTED, "sk_soft_hash_packed: needs L=32, R<=256 and a multiple of 4 query heads per KV head");
+        return fail(SK_ERR_UNSUPPORTED, "sk_soft_hash_packed: needs L=32, R=256 and a multiple of 4 query heads per KV head");
     SK_ALIGNED(lut, 16, "sk_soft_hash_packed: lut");
     SK_ALIGNED(packed, 256, "sk_soft_hash_packed: packed");
     char* pk = static_cast<char*>(packed);
+    if (R != 256)
+        return fail(SK_ERR_UNSUPPORTED, "sk_soft_hash_packed: R=%d (the packed path keeps 256 buckets per table)", R);
     return launch_soft_hash(q, q_dtype, planes, plane_dtype, protos_T, temperature, B, H, Hkv, D, L, P, R,
-                            nullptr, lut, (cudaStream_t)stream, pk,
-                            reinterpret_cast<float*>(pk + packed_param_offset(B, H, Hkv)));
+                            reinterpret_cast<float*>(pk + packed_probs_offset(B, H, Hkv)), lut,
+                            (cudaStream_t)stream, pk, reinterpret_cast<float*>(pk + packed_param_offset(B, H, Hkv)));
 }
 
 int sk_score_select_packed(const float* lut, const void* packed, const uint8_t* codes,
@@ -411,7 +425,7 @@ int sk_score_select_packed(const float* lut, const void* packed, const uint8_t* 
     SK_ALIGNED(workspace, 256, "sk_score_select_packed: workspace");
     if (!sk_packed_applicable(B, H, Hkv, L, R, T, M))
         return fail(SK_ERR_UNSUPPORTED,
-                    "sk_score_select_packed: shape outside the packed path (needs L=32, R<=256, 4 | H/Hkv, T>=4096, "
+                    "sk_score_select_packed: shape outside the packed path (needs L=32, R=256, 4 | H/Hkv, T>=4096, "
                     "12*M<=T, M<=4096); use sk_score_select_list or sk_score + sk_select_list");
     if (workspace_bytes < score_select_workspace_bytes(B, H, Hkv, L, T, M))
         return fail(SK_ERR_WORKSPACE, "sk_score_select_packed: workspace %zu < %zu bytes", workspace_bytes,
@@ -426,7 +440,8 @@ int sk_score_select_packed(const float* lut, const void* packed, const uint8_t* 
     }
     if (stages & 2)
         return launch_select_candidates(lut, codes, v_norm, B, H, Hkv, L, R, T, T_dev, Tcap, M, sink, window, 0,
-                                        list, list_row_stride, list_len, workspace, status, st, qpar);
+                                        list, list_row_stride, list_len, workspace, status, st, qpar,
+                                        reinterpret_cast<const float*>(pk + packed_probs_offset(B, H, Hkv)));
     return SK_OK;
 }
 
@@ -556,14 +571,17 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
         return fail(SK_ERR_WORKSPACE, "sk_decode_step: workspace %zu < %zu bytes", p->workspace_bytes, lay.total);
     SK_REQUIRE(p->list == nullptr || p->list_row_stride >= lay.list_stride,
                "sk_decode_step: list_row_stride smaller than the list length %lld", (long long)lay.list_stride);
-    SK_REQUIRE(p->select_path >= SK_SELECT_AUTO && p->select_path <= SK_SELECT_FILTER_F32,
+    SK_REQUIRE(p->select_path >= SK_SELECT_AUTO && p->select_path <= SK_SELECT_FILTER_PACKED,
                "sk_decode_step: select_path %d is not an sk_select_path", p->select_path);
     const bool can_cluster = score_select_cluster_size(p->B, p->H, p->Hkv, p->L, p->R, p->T_max, p->M) != 0;
     int path = p->select_path;
     if (path == SK_SELECT_AUTO) path = lay.fused ? SK_SELECT_FILTER : (can_cluster ? SK_SELECT_CLUSTER : SK_SELECT_TWO_LAUNCH);
     if (path == SK_SELECT_CLUSTER && !can_cluster)
         return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the one-launch scorer + select");
-    if ((path == SK_SELECT_FILTER || path == SK_SELECT_FILTER_F32) && !lay.fused)
+    if (path == SK_SELECT_FILTER_PACKED && !(lay.has_packed && aligned(p->codes, 32)))
+        return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the packed scorer (L=32, R=256, 4 | H/Hkv, "
+                                        "32-byte aligned codes)");
+    if ((path == SK_SELECT_FILTER || path == SK_SELECT_FILTER_F32 || path == SK_SELECT_FILTER_PACKED) && !lay.fused)
         return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: shape outside the filtering scorer + candidate select");
     if (path == SK_SELECT_TWO_LAUNCH && lay.fused)
         return fail(SK_ERR_UNSUPPORTED, "sk_decode_step: the workspace of this shape holds no score matrix; "
@@ -576,9 +594,12 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
     int32_t* list_len = p->list ? p->list_len : reinterpret_cast<int32_t*>(ws + lay.len);
     const int64_t list_stride = p->list ? p->list_row_stride : lay.list_stride;
     // the packed scan needs 32-byte aligned code rows (one 256-bit load per key)
-    const bool use_packed = path == SK_SELECT_FILTER && lay.has_packed && aligned(p->codes, 32);
+    const bool use_packed = path == SK_SELECT_FILTER_PACKED ||
+                            (path == SK_SELECT_FILTER && lay.has_packed && aligned(p->codes, 32) &&
+                             sk_packed_preferred(p->B, p->H, p->Hkv, p->L, p->R, p->T_max, p->M));
     char* pk = use_packed ? ws + lay.packed : nullptr;
     float* qpar = use_packed ? reinterpret_cast<float*>(pk + packed_param_offset(p->B, p->H, p->Hkv)) : nullptr;
+    float* probs = use_packed ? reinterpret_cast<float*>(pk + packed_probs_offset(p->B, p->H, p->Hkv)) : nullptr;
     int rc;
     bool fused = false;
     if (p->k_new != nullptr && p->q_dtype == p->kv_dtype) {
@@ -586,7 +607,7 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
         rc = launch_decode_prologue(p->q, p->k_new, p->v_new, p->kv_dtype, p->input_pos, p->planes,
                                     p->plane_dtype, p->protos_T, p->temperature, p->k_cache, p->v_cache,
                                     p->codes, p->v_norm, p->prefill_len, p->status, lut, p->B, p->H, p->Hkv,
-                                    p->D, p->Tcap, p->L, p->P, p->R, st, &fused, pk, qpar);
+                                    p->D, p->Tcap, p->L, p->P, p->R, st, &fused, pk, qpar, probs);
         if (rc != SK_OK) return rc;
     }
     if (!fused) {
@@ -597,7 +618,7 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
             if (rc != SK_OK) return rc;
         }
         rc = launch_soft_hash(p->q, p->q_dtype, p->planes, p->plane_dtype, p->protos_T, p->temperature, p->B,
-                              p->H, p->Hkv, p->D, p->L, p->P, p->R, nullptr, lut, st, pk, qpar);
+                              p->H, p->Hkv, p->D, p->L, p->P, p->R, probs, lut, st, pk, qpar);
         if (rc != SK_OK) return rc;
     }
     // from here on every launch may start while its predecessor drains (see pdl_wait in the kernels)
@@ -608,14 +629,14 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
                                          p->prefill_len, p->Tcap, p->M, p->sink, p->window, list, list_stride,
                                          list_len, p->status, st);
         if (rc != SK_OK) return rc;
-    } else if (path == SK_SELECT_FILTER || path == SK_SELECT_FILTER_F32) {
+    } else if (path == SK_SELECT_FILTER || path == SK_SELECT_FILTER_F32 || path == SK_SELECT_FILTER_PACKED) {
         // filtering scorer + candidate select: no score array is written or re-read
         rc = launch_score_filter(lut, p->codes, p->v_norm, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
                                  p->prefill_len, p->Tcap, p->M, ws + lay.scores, p->status, st, pk, qpar);
         if (rc != SK_OK) return rc;
         rc = launch_select_candidates(lut, p->codes, p->v_norm, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,
                                       p->prefill_len, p->Tcap, p->M, p->sink, p->window, 0, list, list_stride,
-                                      list_len, ws + lay.scores, p->status, st, qpar);
+                                      list_len, ws + lay.scores, p->status, st, qpar, probs);
         if (rc != SK_OK) return rc;
     } else {
         rc = sk_score(lut, p->codes, p->v_norm, nullptr, p->B, p->H, p->Hkv, p->L, p->R, p->T_max,

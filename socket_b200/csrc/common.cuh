@@ -247,7 +247,7 @@ int launch_select_candidates(const float* lut, const uint8_t* codes, const uint1
                              int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
                              int sink, int window, int sorted, int32_t* list, int64_t list_row_stride,
                              int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st,
-                             const float* qpar = nullptr);
+                             const float* qpar = nullptr, const float* probs = nullptr);
 
 // One-launch scorer + exact select on thread-block clusters (score_cluster.cu)
 int score_select_cluster_size(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M);
@@ -273,6 +273,7 @@ int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, 
                            const float* protos_T, float temperature, void* k_cache, void* v_cache,
                            uint8_t* codes, uint16_t* v_norm, int32_t* prefill_len, int32_t* status,
                            float* lut, int B, int H, int Hkv, int D, int64_t Tcap, int L, int P, int R,
-                           cudaStream_t st, bool* launched, void* lutq = nullptr, float* qpar = nullptr);
+                           cudaStream_t st, bool* launched, void* lutq = nullptr, float* qpar = nullptr,
+                           float* q_probs = nullptr);
 
 }  // namespace sk

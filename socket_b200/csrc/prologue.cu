@@ -17,7 +17,8 @@ decode_prologue_kernel(const T* __restrict__ q, const T* __restrict__ k_new, con
                        T* __restrict__ v_cache, uint8_t* __restrict__ codes, __half* __restrict__ v_norm,
                        int32_t* prefill_len, int32_t* status, float* __restrict__ lut, int B, int H,
                        int Hkv, int64_t Tcap, int L, int P, int R, int ht, int append_gx, int append_gy,
-                       int sh_gx, uint2* __restrict__ lutq, float* __restrict__ qpar) {
+                       int sh_gx, uint2* __restrict__ lutq, float* __restrict__ qpar,
+                       float* __restrict__ q_probs) {
     extern __shared__ __align__(16) float pro_smem[];
     pdl_launch_dependents();
     const int n_append = append_gx * append_gy;
@@ -30,7 +31,7 @@ decode_prologue_kernel(const T* __restrict__ q, const T* __restrict__ k_new, con
         const int i = blockIdx.x - n_append;
         const int bx = i % sh_gx, g = i / sh_gx;
         soft_hash_body<T, PT>(q, planes, protos_T, inv_temperature, H, Hkv, 128, L, P, R, ht, g,
-                              bx * (SH_WARPS / ht), nullptr, lut, pro_smem, lutq, qpar);
+                              bx * (SH_WARPS / ht), q_probs, lut, pro_smem, lutq, qpar);
     }
 }
 
@@ -43,7 +44,7 @@ int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, 
                            const float* protos_T, float temperature, void* k_cache, void* v_cache,
                            uint8_t* codes, uint16_t* v_norm, int32_t* prefill_len, int32_t* status,
                            float* lut, int B, int H, int Hkv, int D, int64_t Tcap, int L, int P, int R,
-                           cudaStream_t st, bool* launched, void* lutq, float* qpar) {
+                           cudaStream_t st, bool* launched, void* lutq, float* qpar, float* q_probs) {
     *launched = false;
     if (D != 128 || P > 16) return SK_OK;
     const int rep = H / Hkv;
@@ -69,7 +70,7 @@ int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, 
                                              (const PT*)planes, protos_T, inv_t, (T*)k_cache,        \
                                              (T*)v_cache, codes, (__half*)v_norm, prefill_len, status, \
                                              lut, B, H, Hkv, Tcap, L, P, R, ht, append_gx, append_gy, \
-                                             sh_gx, (uint2*)lutq, qpar);                             \
+                                             sh_gx, (uint2*)lutq, qpar, q_probs);                    \
         *launched = true;                                                                            \
     } while (0)
     if (dtype == SK_F32 && plane_dtype == SK_F32) SK_PRO_LAUNCH(float, float);

@@ -434,75 +434,7 @@ __device__ __forceinline__ float packed_upper(uint32_t S, float K0p, float vn) {
     return __fmul_rn(__fadd_rn(__uint2float_rn(S), K0p), vn);
 }
 
-// The two halves of filter_cuts for a CTA whose warps own several runs each: run_sample_stat() is
-// the per-run part (one warp, the run's 32 sample scores), cuts_from_run_stats() the mean over the
-// SC_WARPS runs of the chunk after a barrier.  Same arithmetic as filter_cuts.
-template <int HT>
-__device__ __forceinline__ void run_sample_stat(FilterShared& fs, int run, const float (&sv)[HT], bool valid, float frac) {
-    const int lane = threadIdx.x & 31;
-    const float t = frac * 33.0f + 0.5f;
-    const int r_lo = max(1, min(31, (int)t));
-    const float w = fminf(fmaxf(t - (float)r_lo, 0.f), 1.f);
-    uint32_t key[HT], s_lo[HT], s_hi[HT];
-#pragma unroll
-    for (int j = 0; j < HT; ++j) {
-        const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
-        key[j] = fin ? order_key(sv[j]) : 0u;
-        s_lo[j] = s_hi[j] = 0u;
-    }
-    for (int r = 1; r <= r_lo + 1; ++r) {
-#pragma unroll
-        for (int j = 0; j < HT; ++j) {
-            const uint32_t mx = __reduce_max_sync(FULL, key[j]);
-            if (r == r_lo) s_lo[j] = mx;
-            if (r == r_lo + 1) s_hi[j] = mx;
-            const unsigned who = __ballot_sync(FULL, key[j] == mx);
-            if (lane == __ffs(who) - 1) key[j] = 0u;
-        }
-    }
-    const bool full = __all_sync(FULL, valid);
-    if (lane == 0) {
-        fs.warp_full[run] = full ? 1 : 0;
-#pragma unroll
-        for (int j = 0; j < HT; ++j)
-            fs.warp_stat[j][run] = (s_hi[j] != 0u)
-                                       ? (1.f - w) * order_key_inverse(s_lo[j]) + w * order_key_inverse(s_hi[j])
-                                       : NAN;
-    }
-}
-template <int HT>
-__device__ __forceinline__ void cuts_from_run_stats(FilterShared& fs, float* __restrict__ cut_out, size_t cut_stride,
-                                                    float (&cut)[HT]) {
-    const int lane = threadIdx.x & 31;
-    const bool any_full = __any_sync(FULL, fs.warp_full[lane] != 0);
-#pragma unroll
-    for (int j = 0; j < HT; ++j) {
-        const float v = fs.warp_stat[j][lane];
-        const bool have = v == v && (!any_full || fs.warp_full[lane] != 0);
-        const int n = __popc(__ballot_sync(FULL, have));
-        float sum = have ? v : 0.f;
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(FULL, sum, o);
-        cut[j] = n > 0 ? sum / (float)n : -INFINITY;
-    }
-    if (threadIdx.x < HT) {
-        float mine = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < HT; ++j)
-            if (j == (int)threadIdx.x) mine = cut[j];
-        cut_out[(size_t)threadIdx.x * cut_stride] = mine;
-    }
-}
-
-// 512 threads with up to 128 registers each (the table walk wants ~40 values in flight); a warp owns
-// two of the chunk's SC_WARPS runs and walks them one after the other, so the run layout the select
-// kernel reads is the one score_kernel writes.
-constexpr int PK_THREADS = 512;
-constexpr int PK_WARPS = PK_THREADS / 32;
-constexpr int PK_RUNS = SC_WARPS / PK_WARPS;      // runs per warp
-static_assert(PK_RUNS == 2, "two runs per warp");
-
-__global__ void __launch_bounds__(PK_THREADS, 1)
+__global__ void __launch_bounds__(SC_THREADS, 1)
 score_packed_kernel(const uint8_t* __restrict__ lutq, const float* __restrict__ qpar,
                     const uint8_t* __restrict__ codes, const __half* __restrict__ v_norm, int H, int Hkv, int R,
                     int64_t T, const int32_t* __restrict__ T_dev, int64_t Tcap, int64_t Tslots,
@@ -517,7 +449,6 @@ score_packed_kernel(const uint8_t* __restrict__ lutq, const float* __restrict__ 
     uint64_t* bar = &fs.bar;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t lane_lt = (1u << lane) - 1u;
     const int rep = H / Hkv;
     const int tiles = rep / HT;
     const uint32_t lut_bytes = (uint32_t)R * 256u;
@@ -584,13 +515,12 @@ score_packed_kernel(const uint8_t* __restrict__ lutq, const float* __restrict__ 
         in_flight = false;
         const float K0p = __ldcg(qpar + g) + 33.0f;
 
-        // each of the SC_WARPS runs is a contiguous share of the segment's live keys (a multiple of 32 long)
-        const int per_run = (int)(((t1 - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32);
-        const uint8_t* cg = codes + (size_t)bk * Tcap * L;
-        const uint16_t* vg = reinterpret_cast<const uint16_t*>(v_norm) + (size_t)bk * Tcap;
-        // (run starts are multiples of 32, so a lane's visiting order - key index & 15 - is the same in
-        // every run of the segment)
-        const uint32_t m = (uint32_t)((int)t0 + lane) & 15u;
+        // each warp owns a contiguous run of the segment's live keys (a multiple of 32 long)
+        const int per_warp = (int)(((t1 - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32);
+        const int ws = (int)t0 + warp * per_warp;
+        const int we = min((int)t1, ws + per_warp);
+        // the lane's keys are 32 apart, so its visiting order (key index & 15) is fixed per segment
+        const uint32_t m = (uint32_t)(ws + lane) & 15u;
         const uint32_t sel_lo = 0x3210u ^ (0x1111u * (m & 7u));
         const uint32_t sel_hi = 0x7654u ^ (0x1111u * (m & 7u));
         const bool swap = (m & 8u) != 0u;
@@ -605,141 +535,111 @@ score_packed_kernel(const uint8_t* __restrict__ lutq, const float* __restrict__ 
             }
             X[i] = v;
         }
+        const uint8_t* cg = codes + (size_t)bk * Tcap * L;
+        const __half* vg = v_norm + (size_t)bk * Tcap;
 
-        // integer sums of the key in c[0..8) and the upper bounds they give
-        auto score_of = [&](const uint32_t (&c)[8], uint32_t vb, uint32_t (&S)[HT], float (&sv)[HT]) {
-            uint32_t a0, b0, a1, b1;
-            packed_half<0>(c, swap, sel_lo, sel_hi, X, a0, b0);
-            packed_half<128>(c + 4, swap, sel_lo, sel_hi, X, a1, b1);
-            S[0] = (a0 & 0xffffu) + (a1 & 0xffffu);
-            S[1] = (a0 >> 16) + (a1 >> 16);
-            S[2] = (b0 & 0xffffu) + (b1 & 0xffffu);
-            S[3] = (b0 >> 16) + (b1 >> 16);
-            const float vn = __half2float(__ushort_as_half((unsigned short)vb));
+        uint32_t cur[8], nxt[8];
 #pragma unroll
-            for (int j = 0; j < HT; ++j) sv[j] = packed_upper(S[j], K0p, vn);
-        };
-
-        // ---- the samples: first key of every lane of both runs, their per-run statistics
-        uint32_t sS[PK_RUNS][HT], svb[PK_RUNS];
-        float ssv[PK_RUNS][HT];
-        bool sok[PK_RUNS];
-        {
-            uint32_t c[PK_RUNS][8];
-#pragma unroll
-            for (int r = 0; r < PK_RUNS; ++r) {
-                const int ws = (int)t0 + (warp * PK_RUNS + r) * per_run;
-                const int ts = ws + lane;
-                sok[r] = ts < min((int)t1, ws + per_run);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) c[r][i] = 0u;
-                svb[r] = 0u;
-                if (sok[r]) {
-                    ldg256(cg + (size_t)ts * L, c[r]);
-                    svb[r] = (uint32_t)__ldcg(vg + ts) & 0x7fffu;
-                }
-            }
-            const bool ok = mbar_wait(bar, phase);
-            phase ^= 1u;
-            if (!__syncthreads_and(ok)) {
-                if (threadIdx.x == 0 && status != nullptr) atomicOr(status, SK_DEV_WAIT_TIMEOUT);
-                return;
-            }
-#pragma unroll
-            for (int r = 0; r < PK_RUNS; ++r) {
-                score_of(c[r], svb[r], sS[r], ssv[r]);
-                if (!sok[r]) {
-#pragma unroll
-                    for (int j = 0; j < HT; ++j) ssv[r][j] = 0.f;
-                }
-            }
+        for (int i = 0; i < 8; ++i) cur[i] = nxt[i] = 0u;
+        uint16_t vcur = 0, vnxt = 0;                                 // ||v|| (fp16 bits) travels with the codes
+        int t = ws + lane;
+        if (t < we) {
+            ldg256(cg + (size_t)t * L, cur);
+            vcur = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t);
         }
+        if (t + 32 < we) {
+            ldg256(cg + (size_t)(t + 32) * L, nxt);
+            vnxt = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t + 32);
+        }
+
+        const bool ok = mbar_wait(bar, phase);
+        phase ^= 1u;
+        if (!__syncthreads_and(ok)) {
+            if (threadIdx.x == 0 && status != nullptr) atomicOr(status, SK_DEV_WAIT_TIMEOUT);
+            return;
+        }
+
+        uint32_t cnt4 = 0;            // four 8-bit run lengths, saturating at 255 (cap_w <= 250)
         float cutv[HT];
 #pragma unroll
         for (int j = 0; j < HT; ++j) cutv[j] = -INFINITY;
-        // a short segment keeps everything when its runs have the room (see score_kernel)
-        if (t1 - t0 <= 1024 && 2 * (t1 - t0) <= slots_per_cta && per_run <= fa.cap_w) {   // uniform across the CTA
-            if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
-        } else {
-            const float frac = fminf(__fdividef(fa.keep, (float)Teff), 1.0f);
-#pragma unroll
-            for (int r = 0; r < PK_RUNS; ++r) run_sample_stat<HT>(fs, warp * PK_RUNS + r, ssv[r], sok[r], frac);
-            __syncthreads();
-            cuts_from_run_stats<HT>(fs, fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
-        }
-
         const int run_stride = fa.chunks_max * SC_WARPS * fa.cap_w;
-#pragma unroll 1
-        for (int r = 0; r < PK_RUNS; ++r) {
-            const int run = warp * PK_RUNS + r;
-            const int ws = (int)t0 + run * per_run;
-            const int we = min((int)t1, ws + per_run);
-            // entry 0 of this run for head 0; head j's run lies j * run_stride entries further on
-            uint2* const run0 = fa.cand + (((size_t)row0 * fa.chunks_max + chunk) * SC_WARPS + run) * fa.cap_w;
-            int cnt[HT];
-#pragma unroll
-            for (int j = 0; j < HT; ++j) cnt[j] = 0;
-            auto keep = [&](const uint32_t (&S)[HT], const float (&sv)[HT], uint32_t vb, bool valid, int tk) {
-#pragma unroll
-                for (int j = 0; j < HT; ++j) {
-                    const bool hit = valid && sv[j] >= cutv[j];
-                    const unsigned bal = __ballot_sync(FULL, hit);
-                    if (bal != 0u) {                              // warp-uniform
-                        const int pos = cnt[j] + __popc(bal & lane_lt);
-                        if (hit && pos < fa.cap_w)
-                            run0[(size_t)j * run_stride + pos] = make_uint2((S[j] << 15) | vb, (uint32_t)tk);
-                        cnt[j] += __popc(bal);
-                    }
-                }
-            };
-            int t = ws + lane;
-            // the sample key of this run, scored above
-            if (r == 0) keep(sS[0], ssv[0], svb[0], sok[0], t);
-            else keep(sS[1], ssv[1], svb[1], sok[1], t);
+        const int run_index0 = (((int)row0 * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w;
 
-            // ---- main loop: keys 32 apart, two buffers in turn, the next key's codes always in flight
-            uint32_t ca[8], cb[8];
-            uint32_t va = 0u, vb2 = 0u;
+        // scores of the key held in cur/vcur: the packed entries and the upper bounds
+        auto score_cur = [&](uint32_t (&pk)[HT], float (&sv)[HT]) {
+            uint32_t a0, b0, a1, b1;
+            packed_half<0>(cur, swap, sel_lo, sel_hi, X, a0, b0);
+            packed_half<128>(cur + 4, swap, sel_lo, sel_hi, X, a1, b1);
+            const uint32_t S[HT] = {(a0 & 0xffffu) + (a1 & 0xffffu), (a0 >> 16) + (a1 >> 16),
+                                    (b0 & 0xffffu) + (b1 & 0xffffu), (b0 >> 16) + (b1 >> 16)};
+            const uint32_t vb = (uint32_t)vcur & 0x7fffu;
+            const float vn = __half2float(__ushort_as_half((unsigned short)vb));
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ca[i] = cb[i] = 0u;
-            t += 32;
-            if (t < we) {
-                ldg256(cg + (size_t)t * L, ca);
-                va = (uint32_t)__ldcg(vg + t) & 0x7fffu;
+            for (int j = 0; j < HT; ++j) {
+                sv[j] = packed_upper(S[j], K0p, vn);
+                pk[j] = (S[j] << 15) | vb;
             }
-            if (t + 32 < we) {
-                ldg256(cg + (size_t)(t + 32) * L, cb);
-                vb2 = (uint32_t)__ldcg(vg + t + 32) & 0x7fffu;
-            }
-            for (; t - lane < we; t += 64) {
-                uint32_t S[HT];
-                float sv[HT];
-                {
-                    score_of(ca, va, S, sv);
-                    const uint32_t vcur = va;
-                    const bool valid = t < we;
-                    if (t + 64 < we) {
-                        ldg256(cg + (size_t)(t + 64) * L, ca);
-                        va = (uint32_t)__ldcg(vg + t + 64) & 0x7fffu;
-                    }
-                    keep(S, sv, vcur, valid, t);
-                }
-                if (t + 32 - lane < we) {
-                    score_of(cb, vb2, S, sv);
-                    const uint32_t vcur = vb2;
-                    const bool valid = t + 32 < we;
-                    if (t + 96 < we) {
-                        ldg256(cg + (size_t)(t + 96) * L, cb);
-                        vb2 = (uint32_t)__ldcg(vg + t + 96) & 0x7fffu;
-                    }
-                    keep(S, sv, vcur, valid, t + 32);
+        };
+        auto keep = [&](const uint32_t (&pk)[HT], const float (&sv)[HT], bool valid, int tk) {
+#pragma unroll
+            for (int j = 0; j < HT; ++j) {
+                const bool hit = valid && sv[j] >= cutv[j];
+                const unsigned bal = __ballot_sync(FULL, hit);
+                if (bal != 0u) {                              // warp-uniform
+                    const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
+                    const int pos = have + __popc(bal & ((1u << lane) - 1u));
+                    if (hit && pos < fa.cap_w)
+                        fa.cand[(size_t)(run_index0 + j * run_stride + pos)] = make_uint2(pk[j], (uint32_t)tk);
+                    cnt4 += (uint32_t)min(__popc(bal), 255 - have) << (8 * j);
                 }
             }
-            if (lane == 0) {
+        };
+
+        {
+            // ---- sample = first key of every lane: scores, cut
+            float sv[HT];
+            uint32_t pk[HT];
+            const bool valid = t < we;
+            score_cur(pk, sv);
+            if (!valid) {
 #pragma unroll
-                for (int j = 0; j < HT; ++j)
-                    fa.cnt[((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + run] = min(cnt[j], 255);
+                for (int j = 0; j < HT; ++j) sv[j] = 0.f;
             }
+            if (t1 - t0 <= 1024 && 2 * (t1 - t0) <= slots_per_cta && per_warp <= fa.cap_w) {   // uniform across the CTA
+                if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
+            } else {
+                filter_cuts<HT>(fs, sv, valid, fminf(__fdividef(fa.keep, (float)Teff), 1.0f),
+                                fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
+            }
+            keep(pk, sv, valid, t);
+        }
+        t += 32;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+        vcur = vnxt;
+        if (t + 32 < we) {
+            ldg256(cg + (size_t)(t + 32) * L, nxt);
+            vnxt = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t + 32);
+        }
+        for (; t - lane < we; t += 32) {
+            const bool valid = t < we;
+            float sv[HT];
+            uint32_t pk[HT];
+            score_cur(pk, sv);
+            keep(pk, sv, valid, t);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+            vcur = vnxt;
+            if (t + 64 < we) {
+                ldg256(cg + (size_t)(t + 64) * L, nxt);
+                vnxt = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t + 64);
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < HT; ++j)
+                fa.cnt[((row0 + j) * fa.chunks_max + chunk) * SC_WARPS + warp] = (int32_t)((cnt4 >> (8 * j)) & 0xffu);
         }
     }
 }
@@ -835,7 +735,7 @@ size_t score_select_workspace_bytes(int B, int H, int Hkv, int L, int64_t T, int
 }
 
 bool packed_filter_applicable(int H, int Hkv, int L, int R) {
-    return Hkv > 0 && H % Hkv == 0 && L == 32 && R >= 1 && R <= 256 && lut_head_tile(H / Hkv) == 4;
+    return Hkv > 0 && H % Hkv == 0 && L == 32 && R == 256 && lut_head_tile(H / Hkv) == 4;
 }
 
 int launch_score_filter(const float* lut, const uint8_t* codes, const uint16_t* v_norm, int B, int H,
@@ -854,13 +754,13 @@ int launch_score_filter(const float* lut, const uint8_t* codes, const uint16_t* 
     fa.keep = plan.frac * (float)T;
     if (lutq != nullptr) {
         if (!packed_filter_applicable(H, Hkv, L, R) || qpar == nullptr)
-            return fail(SK_ERR_UNSUPPORTED, "packed scorer: needs L=32, R<=256 and a multiple of 4 query heads per KV head");
+            return fail(SK_ERR_UNSUPPORTED, "packed scorer: needs L=32, R=256 and a multiple of 4 query heads per KV head");
         if (reinterpret_cast<uintptr_t>(codes) % 32 != 0 || reinterpret_cast<uintptr_t>(lutq) % 16 != 0)
             return fail(SK_ERR_MISALIGNED, "packed scorer: codes must be 32-byte aligned, the table 16-byte aligned");
         cudaError_t e = cudaFuncSetAttribute(score_packed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PK_SMEM);
         if (e != cudaSuccess) return fail(SK_ERR_CUDA, "score_packed_kernel smem attribute: %s", cudaGetErrorString(e));
         const int n_groups = B * Hkv * ((H / Hkv) / 4);
-        e = launch_chained(score_packed_kernel, dim3((unsigned)plan.grid), dim3(PK_THREADS), (size_t)PK_SMEM, st,
+        e = launch_chained(score_packed_kernel, dim3((unsigned)plan.grid), dim3(SC_THREADS), (size_t)PK_SMEM, st,
                            (const uint8_t*)lutq, qpar, codes, (const __half*)v_norm, H, Hkv, R, T, T_dev, Tcap,
                            plan.Tslots, plan.per_cta, n_groups, status, fa);
         if (e != cudaSuccess) return fail(SK_ERR_CUDA, "score_packed_kernel: %s", cudaGetErrorString(e));

@@ -39,7 +39,7 @@ struct SelShared {
     int32_t cand_idx[SEL_CAP];
     uint32_t cand_aux[SEL_CAP];                   // packed candidates: the (S, ||v||) word of every candidate
     int scan_buf[2][40];
-    uint32_t red_lo[SEL_WARPS], red_hi[SEL_WARPS];
+    uint32_t red_lo[SEL_WARPS], red_hi[SEL_WARPS], red_x[SEL_WARPS];
     int thr_bin, thr_above, thr_inbin;
 };
 
@@ -110,6 +110,33 @@ __device__ __forceinline__ void block_minmax(SelShared& s, uint32_t& lo, uint32_
         hi = max(hi, __shfl_xor_sync(FULL, hi, o));
     }
     __syncthreads();                                   // red_lo / red_hi may be reused
+}
+
+// Same with a second minimum riding along.
+__device__ __forceinline__ void block_minmax3(SelShared& s, uint32_t& lo, uint32_t& hi, uint32_t& lo2) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(FULL, lo, o));
+        hi = max(hi, __shfl_xor_sync(FULL, hi, o));
+        lo2 = min(lo2, __shfl_xor_sync(FULL, lo2, o));
+    }
+    if (lane == 0) {
+        s.red_lo[warp] = lo;
+        s.red_hi[warp] = hi;
+        s.red_x[warp] = lo2;
+    }
+    __syncthreads();
+    lo = s.red_lo[lane];
+    hi = s.red_hi[lane];
+    lo2 = s.red_x[lane];
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(FULL, lo, o));
+        hi = max(hi, __shfl_xor_sync(FULL, hi, o));
+        lo2 = min(lo2, __shfl_xor_sync(FULL, lo2, o));
+    }
+    __syncthreads();
 }
 
 // Over hist[0..SEL_BINS): the bin b with  #(bins > b) < target <= #(bins >= b)  (target >= 1,
@@ -671,6 +698,7 @@ struct CandArgs {
     int H, Hkv, L, R, ht;
     int64_t Tcap;
     const float* qpar;      // packed candidates: K0 of every KV-head group
+    const float* probs;     // packed candidates: q_probs [rows][32][256] fp32 (rows 32 KiB apart)
 };
 
 // ------------------------------------------------------------------------------------------
@@ -682,7 +710,7 @@ struct CandArgs {
 // (fp32 summation and the two roundings of the bound itself are far inside the slack of 0.9).
 // Call the two sides lo_i and up_i.  The candidates are all keys with up_i >= their chunk's cut.
 // ------------------------------------------------------------------------------------------
-constexpr int BAND_MAX = 2048;                    // keys between the brackets that can be rescored on chip
+constexpr int BAND_MAX = 1024;                    // keys between the brackets that can be rescored on chip
 constexpr int BAND_DIRECT = 256;                  // up to here the band is ranked pair by pair
 
 __device__ __forceinline__ float packed_upper_sel(uint32_t S, float K0p, float vn) {
@@ -693,71 +721,70 @@ __device__ __forceinline__ float packed_lower_sel(uint32_t S, float K0m, float v
     return fmaxf(v, 0.f);
 }
 
-// Exact fp32 scores of the keys band_t[0..n) for head column j of the group's table (L = 32), the
-// tables added in the very order score_kernel adds them for a key (groups of 8 tables ascending,
-// inside a group table u ^ (t & 7) at step u), so that the values equal sk_score's bit for bit.
-// A warp takes 8 keys at a time: lane q fetches the q-th term of the sum of each of them (code
-// byte, then table word - two round trips for the whole batch), the terms go through a padded
-// tile in shared memory, and lanes 0..7 add one key's 32 terms each, in order.
+// Exact fp32 scores of the keys band_t[0..n) of one row (L = 32), the tables added in the very order
+// score_kernel adds them for a key (groups of 8 tables ascending, inside a group table u ^ (t & 7)
+// at step u), so that the values equal sk_score's bit for bit.  The row's probabilities
+// tab_s[l * 256 + bucket] are in shared memory.  A warp takes 8 keys at a time: lane l fetches
+// code byte l of each (one 32-byte sector per key) and looks its term up, the terms go through a
+// padded tile, four keys at a time, and lanes 0..3 add one key's 32 terms each, in order.
 constexpr int XS_KEYS = 8;                        // keys per warp and batch
-constexpr int XS_TILE = XS_KEYS * 33;             // floats per warp
-static_assert((2 * BAND_MAX + SEL_WARPS * XS_TILE) * 4 <= SEL_CAP * 4, "band arrays and tiles share cand_aux");
-__device__ __forceinline__ void exact_scores_like_scorer(const float* __restrict__ lut_g, int ht, int j,
-                                                         const uint8_t* __restrict__ cg,
+constexpr int XS_TILE = 4 * 33;                   // floats per warp
+constexpr int XS_TAB = 32 * 256;                  // floats of one row's table
+static_assert((2 * BAND_MAX + XS_TAB + SEL_WARPS * XS_TILE) * 4 <= SEL_CAP * 4, "band arrays, table and tiles share cand_aux");
+__device__ __forceinline__ void exact_scores_like_scorer(const float* tab_s, const uint8_t* __restrict__ cg,
                                                          const __half* __restrict__ vg, const int32_t* band_t,
                                                          int n, float* tile_all, uint32_t* band_e) {
     constexpr int L = 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* tile = tile_all + warp * XS_TILE;
-    const int v16 = lane & 16, u = lane & 15;
     for (int k0 = warp * XS_KEYS; k0 < n; k0 += SEL_WARPS * XS_KEYS) {
-        int t[XS_KEYS], tb[XS_KEYS];
+        int t[XS_KEYS];
         uint32_t code[XS_KEYS];
 #pragma unroll
         for (int kk = 0; kk < XS_KEYS; ++kk) {
             t[kk] = k0 + kk < n ? band_t[k0 + kk] : -1;
-            tb[kk] = v16 | (u & 8) | ((u & 7) ^ (t[kk] & 7));          // table of this lane's term
-            code[kk] = t[kk] >= 0 ? (uint32_t)__ldcg(cg + (size_t)t[kk] * L + tb[kk]) : 0u;
+            code[kk] = t[kk] >= 0 ? (uint32_t)__ldcg(cg + (size_t)t[kk] * L + lane) : 0u;
         }
-        // all table words of the batch are requested before any of them is stored (a load is not
-        // moved across the shared-memory stores below)
-        float term[XS_KEYS];
-#pragma unroll
-        for (int kk = 0; kk < XS_KEYS; ++kk)
-            term[kk] = t[kk] >= 0 ? __ldcg(lut_g + ((size_t)code[kk] * L + tb[kk]) * ht + j) : 0.f;
         const int mine = k0 + lane;
         const int tm = (lane < XS_KEYS && mine < n) ? band_t[mine] : -1;
         float vn = 0.f;
         if (tm >= 0) vn = __half2float(__ldcg(vg + tm));
 #pragma unroll
-        for (int kk = 0; kk < XS_KEYS; ++kk) tile[kk * 33 + lane] = term[kk];
-        __syncwarp();
-        if (tm >= 0) {
-            float sum = 0.f;
+        for (int half = 0; half < 2; ++half) {
 #pragma unroll
-            for (int q = 0; q < 32; ++q) sum += tile[lane * 33 + q];
-            band_e[mine] = order_key(sum * vn);
+            for (int kk = 0; kk < 4; ++kk) tile[kk * 33 + lane] = tab_s[lane * 256 + code[half * 4 + kk]];
+            __syncwarp();
+            const int who = lane - 4 * half;               // lanes 0..3 sum the first four keys, 4..7 the others
+            if (who >= 0 && who < 4 && tm >= 0) {
+                const int m = tm & 7;
+                float sum = 0.f;
+#pragma unroll
+                for (int q = 0; q < 32; ++q) sum += tile[who * 33 + ((q & 24) | ((q & 7) ^ m))];
+                band_e[mine] = order_key(sum * vn);
+            }
+            __syncwarp();
         }
-        __syncwarp();
     }
 }
 
 // Exact top-Me of a row from its packed candidates (keys = order keys of up_i in cand_key, the
-// packed words in cand_aux, both in index order; hist zero on entry).  Returns false, with nothing
-// usable written, when the result cannot be proved or held on chip; the caller then rescans the row.
+// packed words in cand_aux, both in index order; hist zero on entry; s_min = smallest S of the row's
+// candidates).  Returns false, with nothing usable written, when the result cannot be proved or
+// held on chip; the caller then rescans the row.
 //
 // One histogram of the up_i finds the bin that holds the Me-th largest; its upper edge UB bounds
-// C * (k-th exact score) from above, and LB = min lo_i over the candidates in that bin or higher
-// (at least Me keys) bounds it from below.  A key outside the candidate set has
+// C * (k-th exact score) from above.  Every candidate has lo_i >= up_i * (1 - 34 / (s_min + K0 + 33)),
+// so LB = (lower edge of that bin) * that factor is below lo_i of the >= Me candidates in the bin
+// or above it, hence below C * (k-th exact score).  A key outside the candidate set has
 // up < its chunk's cut <= chi, so with chi <= LB it lies strictly below the k-th exact score.
-// Candidates with lo_i > UB are in the top Me, those with up_i < LB are not, and the few in
-// between are scored exactly (fp32 table, sk_score's summation order) and ranked by (score
-// descending, index ascending).  Output in ascending index order.
+// Candidates with lo_i > UB are in the top Me and are written at once (ascending index); those
+// with up_i < LB are out; the few in between are scored exactly (fp32 table, sk_score's summation
+// order), ranked by (score descending, index ascending) and the best fill the remaining places.
 __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan, int n, int Me, uint32_t kmin,
-                                                       uint32_t kmax, uint32_t chi_key, float K0m,
-                                                       const float* __restrict__ lut_g, int ht, int hj,
+                                                       uint32_t kmax, uint32_t s_min, uint32_t chi_key, float K0,
+                                                       const float* __restrict__ probs_row,
                                                        const uint8_t* __restrict__ cg,
-                                                       const __half* __restrict__ vg, int L,
+                                                       const __half* __restrict__ vg,
                                                        int32_t* __restrict__ heavy, int32_t* stats) {
     const int tid = threadIdx.x;
     const uint32_t range = kmax - kmin;
@@ -768,36 +795,34 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
         const uint32_t k = i < n ? s.cand_key[i] : kmin;
         warp_hist_add(s.hist, (k - kmin) >> shift, i < n);
     }
+    // the row's probabilities [L][R] (32 KiB), requested now, stored to shared memory once the
+    // classification below has freed cand_aux
+    float4 tab_r[XS_TAB / 4 / SEL_THREADS];
+#pragma unroll
+    for (int u = 0; u < XS_TAB / 4 / SEL_THREADS; ++u)
+        tab_r[u] = __ldcg(reinterpret_cast<const float4*>(probs_row) + u * SEL_THREADS + tid);
     __syncthreads();
     find_bin_desc(s, scan, Me);
     const uint32_t thr = (uint32_t)s.thr_bin;
     uint64_t ub64 = (uint64_t)kmin + (((uint64_t)thr + 1u) << shift) - 1u;
     if (ub64 > (uint64_t)kmax) ub64 = kmax;
     const float UB = order_key_inverse((uint32_t)ub64);
+    const float edge = order_key_inverse(kmin + (thr << shift));
+    const float gap = 34.0f / (__uint2float_rz(s_min) + K0 + 33.0f);
+    const float LB = fmaxf(edge * (1.0f - gap * 1.0001f) * (1.0f - 1e-5f), 0.f);
+    if (!(gap < 0.5f) || order_key(LB) < chi_key) return false;   // some chunk may have dropped a key of the top Me
 
-    const int ept = (n + SEL_THREADS - 1) / SEL_THREADS;
+    // ---- classes: 1 = in, 2 = between the brackets, 0 = out; two bits per candidate of this thread
+    const int ept = (n + SEL_THREADS - 1) / SEL_THREADS;          // <= 16
     const int i0 = tid * ept, i1 = min(n, i0 + ept);
-    auto lower_of = [&](uint32_t x) {
-        return packed_lower_sel(x >> 15, K0m, __half2float(__ushort_as_half((unsigned short)(x & 0x7fffu))));
-    };
-    uint32_t lbk = 0x7f800000u, dummy = 0u;          // +inf; non-negative floats order like their bit patterns
-    for (int i = i0; i < i1; ++i) {
-        // the packed word is not needed again: its place takes the lower bound (float bits)
-        const uint32_t lob = __float_as_uint(lower_of(s.cand_aux[i]));
-        s.cand_aux[i] = lob;
-        if (((s.cand_key[i] - kmin) >> shift) >= thr) lbk = min(lbk, lob);
-    }
-    block_minmax(s, lbk, dummy);
-    const float LB = __uint_as_float(lbk);
-    if (order_key(LB) < chi_key) return false;        // some chunk may have dropped a key of the top Me
-
-    // ---- classes: 1 = in, 2 = between the brackets, 0 = out
+    uint32_t cls_bits = 0;
     int n_sure = 0, n_band = 0;
     for (int i = i0; i < i1; ++i) {
         const float up = order_key_inverse(s.cand_key[i]);
-        const float lo = __uint_as_float(s.cand_aux[i]);
+        const uint32_t x = s.cand_aux[i];
+        const float lo = packed_lower_sel(x >> 15, K0 - 1.0f, __half2float(__ushort_as_half((unsigned short)(x & 0x7fffu))));
         const uint32_t cls = lo > UB ? 1u : (up >= LB ? 2u : 0u);
-        s.cand_key[i] = cls;
+        cls_bits |= cls << (2 * (i - i0));
         n_sure += cls == 1u;
         n_band += cls == 2u;
     }
@@ -809,27 +834,34 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
         atomicAdd(stats + 1, tot_band);
         if (tot_band > BAND_DIRECT) atomicAdd(stats + 2, 1);
     }
-    if (tot_band > BAND_MAX || want < 1 || want > tot_band) return false;
+    if (tot_band > BAND_MAX || want < 0 || want > tot_band) return false;
     // every read of cand_aux happened before the scan's barriers: its space now holds the band
     uint32_t* band_e = s.cand_aux;                                     // [BAND_MAX] exact order keys
-    int32_t* band_t = reinterpret_cast<int32_t*>(s.cand_aux + BAND_MAX);   // [BAND_MAX] key index, then "taken" flag
+    int32_t* band_t = reinterpret_cast<int32_t*>(s.cand_aux + BAND_MAX);   // [BAND_MAX] key index
+    float* tab_s = reinterpret_cast<float*>(s.cand_aux + 2 * BAND_MAX);    // [L][256] this row's probabilities
+#pragma unroll
+    for (int u = 0; u < XS_TAB / 4 / SEL_THREADS; ++u)
+        reinterpret_cast<float4*>(tab_s)[u * SEL_THREADS + tid] = tab_r[u];
     {
-        int bpos = off >> 16;
+        int spos = off & 0xffff, bpos = off >> 16;
         for (int i = i0; i < i1; ++i) {
-            if (s.cand_key[i] == 2u) {
-                band_t[bpos] = s.cand_idx[i];
-                s.cand_key[i] = 2u + (uint32_t)bpos;
-                ++bpos;
+            const uint32_t cls = (cls_bits >> (2 * (i - i0))) & 3u;
+            if (cls == 1u) {
+                if (spos < Me) heavy[spos] = s.cand_idx[i];
+                ++spos;
+            } else if (cls == 2u) {
+                band_t[bpos++] = s.cand_idx[i];
             }
         }
     }
+    if (want == 0) return true;                        // uniform
     __syncthreads();
-    exact_scores_like_scorer(lut_g, ht, hj, cg, vg, band_t, tot_band,
-                             reinterpret_cast<float*>(s.cand_aux + 2 * BAND_MAX), band_e);
+    exact_scores_like_scorer(tab_s, cg, vg, band_t, tot_band, tab_s + XS_TAB, band_e);
     __syncthreads();
 
+    int32_t* out = heavy + tot_sure;                   // `want` places left
     if (tot_band <= BAND_DIRECT) {
-        // four threads per key count the keys that precede it
+        // four threads per key count the keys that precede it (band order = index order)
         const int kb = tid >> 2, part = tid & 3;
         int cnt = 0;
         if (kb < tot_band) {
@@ -842,42 +874,29 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
         }
         cnt += __shfl_xor_sync(FULL, cnt, 1);
         cnt += __shfl_xor_sync(FULL, cnt, 2);
-        if (kb < tot_band && part == 0) band_t[kb] = cnt < want;
-        __syncthreads();
+        if (kb < tot_band && part == 0 && cnt < want) out[cnt] = band_t[kb];
     } else {
         uint32_t quota;
         const uint32_t kth = smem_kth(s, scan, band_e, tot_band, (uint32_t)want, quota);
         const int ept2 = (tot_band + SEL_THREADS - 1) / SEL_THREADS;
         const int j0 = tid * ept2, j1 = min(tot_band, j0 + ept2);
-        int n_eq = 0;
-        for (int jb = j0; jb < j1; ++jb) n_eq += band_e[jb] == kth;
+        int n_gt = 0, n_eq = 0;
+        for (int jb = j0; jb < j1; ++jb) {
+            n_gt += band_e[jb] > kth;
+            n_eq += band_e[jb] == kth;
+        }
         int tot2;
-        int eq_before = scan.excl(n_eq, tot2, s);
+        const int off2 = scan.excl(n_gt | (n_eq << 16), tot2, s);
+        int gt_before = off2 & 0xffff, eq_before = off2 >> 16;
         for (int jb = j0; jb < j1; ++jb) {
             const uint32_t e = band_e[jb];
-            int take = e > kth;
-            if (e == kth) take = eq_before++ < (int)quota;
-            band_t[jb] = take;
-        }
-        __syncthreads();
-    }
-
-    // ---- ordered emission
-    int n_sel = 0;
-    for (int i = i0; i < i1; ++i) {
-        const uint32_t cls = s.cand_key[i];
-        n_sel += cls == 1u || (cls >= 2u && band_t[cls - 2u] != 0);
-    }
-    int tot_sel;
-    int pos = scan.excl(n_sel, tot_sel, s);
-    for (int i = i0; i < i1; ++i) {
-        const uint32_t cls = s.cand_key[i];
-        if (cls == 1u || (cls >= 2u && band_t[cls - 2u] != 0)) {
-            if (pos < Me) heavy[pos] = s.cand_idx[i];
-            ++pos;
+            const int dst = gt_before + min(eq_before, (int)quota);
+            if ((e > kth || (e == kth && eq_before < (int)quota)) && dst < want) out[dst] = band_t[jb];
+            gt_before += e > kth;
+            eq_before += e == kth;
         }
     }
-    return tot_sel == Me;
+    return true;
 }
 
 __global__ void __launch_bounds__(SEL_THREADS, 1)
@@ -904,9 +923,11 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
     pdl_wait();                               // the runs, their lengths and the cuts come from the scorer
     const float K0 = packed ? __ldcg(a.qpar + g) : 0.f;
     // one candidate into shared memory: its order key (of the score, or of the packed entry's upper bound)
+    uint32_t s_min = 0xffffffffu;                 // packed candidates: smallest integer sum S
     auto put = [&](int i, uint2 e, uint32_t& kmin, uint32_t& kmax) {
         uint32_t k;
         if (packed) {
+            s_min = min(s_min, e.x >> 15);
             const float vn = __half2float(__ushort_as_half((unsigned short)(e.x & 0x7fffu)));
             k = order_key(packed_upper_sel(e.x >> 15, K0 + 33.0f, vn));
             s.cand_aux[i] = e.x;
@@ -999,13 +1020,13 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                 __syncthreads();
                 for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
             }
-            block_minmax(s, kmin, kmax);               // also the barrier after the gather
+            if (packed) block_minmax3(s, kmin, kmax, s_min);
+            else block_minmax(s, kmin, kmax);          // also the barrier after the gather
             if (packed) {
-                const int j = hj % a.ht;
-                exact = emit_packed_candidates(s, scan, total, Me, kmin, kmax, chi, K0 - 1.0f,
-                                               a.lut + (size_t)g * a.R * a.L * a.ht, a.ht, j,
+                exact = emit_packed_candidates(s, scan, total, Me, kmin, kmax, s_min, chi, K0,
+                                               a.probs + (size_t)row * XS_TAB,
                                                a.codes + (size_t)(b * a.Hkv + kvh) * a.Tcap * a.L,
-                                               a.v_norm + (size_t)(b * a.Hkv + kvh) * a.Tcap, a.L, heavy, a.n_fallback);
+                                               a.v_norm + (size_t)(b * a.Hkv + kvh) * a.Tcap, heavy, a.n_fallback);
             } else {
                 uint32_t kth = 0;
                 if (!emit_candidates_binned(s, scan, total, Me, Me, kmin, kmax, heavy, kth)) {
@@ -1080,7 +1101,7 @@ int launch_select_candidates(const float* lut, const uint8_t* codes, const uint1
                              int Hkv, int L, int R, int64_t T, const int32_t* T_dev, int64_t Tcap, int64_t M,
                              int sink, int window, int sorted, int32_t* list, int64_t list_row_stride,
                              int32_t* list_len, void* workspace, int32_t* status, cudaStream_t st,
-                             const float* qpar) {
+                             const float* qpar, const float* probs) {
     (void)status;
     if (sorted) return fail(SK_ERR_UNSUPPORTED, "fused score+select: sorted output not supported");
     const int ht = lut_head_tile(H / Hkv);
@@ -1105,6 +1126,7 @@ int launch_select_candidates(const float* lut, const uint8_t* codes, const uint1
     a.H = H; a.Hkv = Hkv; a.L = L; a.R = R; a.ht = ht;
     a.Tcap = Tcap;
     a.qpar = qpar;
+    a.probs = probs;
     if ((size_t)L * R * 4 > sizeof(uint32_t) * SEL_CAP)
         return fail(SK_ERR_UNSUPPORTED, "fused score+select: L*R too large for the rescoring table");
     const size_t smem = sizeof(SelShared);

@@ -256,6 +256,11 @@ def packed_applicable(B: int, H: int, Hkv: int, L: int, R: int, T: int, M: int) 
     return bool(lib().sk_packed_applicable(B, H, Hkv, L, R, T, M))
 
 
+def packed_preferred(B: int, H: int, Hkv: int, L: int, R: int, T: int, M: int) -> bool:
+    """Whether `sk_decode_step` takes the packed scan for this shape on its own."""
+    return bool(lib().sk_packed_preferred(B, H, Hkv, L, R, T, M))
+
+
 def soft_hash_packed(q_bhd: torch.Tensor, planes: torch.Tensor, protos_T: torch.Tensor,
                      temperature: float = 1.0, n_kv_heads: Optional[int] = None):
     """q [B,H,D] -> (fp32 scorer table, packed 12-bit copy of it) for `score_select_packed`
@@ -361,7 +366,7 @@ def sparse_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 
 
 # sk_select_path: how the decode step builds its list (all paths give the same list)
-SELECT_PATHS = {"auto": 0, "two_launch": 1, "filter": 2, "cluster": 3, "filter_f32": 4}
+SELECT_PATHS = {"auto": 0, "two_launch": 1, "filter": 2, "cluster": 3, "filter_f32": 4, "filter_packed": 5}
 
 
 class DecodeStep:

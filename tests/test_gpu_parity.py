@@ -512,6 +512,43 @@ def test_fused_decode_step_against_chained_oracle(dtype):
     assert torch.equal(out, out1)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_decode_step_packed_and_fp32_tables_agree(dtype):
+    """The whole step with the list built from the packed 12-bit table against the step pinned to
+    the fp32 table: same index sets, outputs within rounding of the summation order, over a few
+    growing-context steps (the newest token must be scored in both)."""
+    B, H, Hkv, T, M, sink, window = 2, 8, 2, 9000, 256, 8, 32
+    inp = make_decode_inputs(B, H, Hkv, T + 4, seed=61, dtype=dtype)
+    k_bshd = cu(inp.k.permute(0, 2, 1, 3).contiguous())
+    v_bshd = cu(inp.v.permute(0, 2, 1, 3).contiguous())
+    g = torch.Generator().manual_seed(3)
+    qs = [cu(torch.randn(B, H, 128, generator=g).to(dtype)) for _ in range(4)]
+    results = {}
+    for path in ("filter_f32", "filter_packed"):
+        attn = SocketAttention(H, Hkv, 128, heavy_const=M, sink_size=sink, window_size=window,
+                               planes=inp.planes, protos_T=inp.protos_T, dtype=dtype, device=DEV)
+        cache = attn.setup_cache(B, T + 64, dtype=dtype)
+        cache.append(torch.arange(T, device=DEV), k_bshd[:, :T], v_bshd[:, :T], attn.planes)
+        q = torch.empty(B, H, 128, dtype=dtype, device=DEV)
+        kn = torch.empty(B, 1, Hkv, 128, dtype=dtype, device=DEV)
+        vn = torch.empty_like(kn)
+        pos = torch.zeros(1, dtype=torch.long, device=DEV)
+        out = torch.empty_like(q)
+        step = ops.DecodeStep(cache, q, kn, vn, pos, attn.planes, attn.protos_T, out, topk=M, sink=sink,
+                              window=window, T_max=T + 64, keep_list=True, select_path=path)
+        res = []
+        for i in range(4):
+            q.copy_(qs[i]); kn.copy_(k_bshd[:, T + i:T + i + 1]); vn.copy_(v_bshd[:, T + i:T + i + 1]); pos.fill_(T + i)
+            step.run()
+            torch.cuda.synchronize()
+            res.append((torch.sort(step.list.clone(), dim=-1).values, step.list_len.clone(), out.clone()))
+        assert int(step.status) == 0 and step.rescored_rows() == 0
+        results[path] = res
+    for (la, na, oa), (lb, nb_, ob) in zip(results["filter_f32"], results["filter_packed"]):
+        assert torch.equal(na, nb_) and torch.equal(la, lb)
+        assert (oa.float() - ob.float()).abs().max() <= (2e-3 if dtype == torch.bfloat16 else 1e-5)
+
+
 def test_sparse_decode_rereads_non_contiguous_inputs_on_every_call():
     """The reference flow hands `v` over as a view of the fused QKV projection (not contiguous for
     B > 1).  Two calls with the same buffers and different contents must each use the contents of
