@@ -63,7 +63,13 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default="c3", choices=sorted(PRESETS))
+    ap.add_argument("--workload", default="c3", choices=sorted(PRESETS) + ["c4", "c5"],
+                    help="c1-c3: one attention layer (op level); c4 / c5: whole-model greedy decode, "
+                         "Llama-3-8B / Llama-3-70B shape with random weights")
+    ap.add_argument("--model-record", default="auto", choices=["auto", "on", "off"],
+                    help="also run the whole-model decode comparison (c4) and attach it to the line; "
+                         "auto = on a single GPU only")
+    ap.add_argument("--model-tokens", type=int, default=64, help="decode tokens timed per mode by the attached c4 record")
     ap.add_argument("--secondary", default="c2", choices=sorted(PRESETS) + ["none"],
                     help="second workload measured in the same process and reported under its own key")
     ap.add_argument("--impl", default="socket_b200", choices=["socket_b200", "reference"])
@@ -628,9 +634,100 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
     return res
 
 
+MODEL_WORKLOADS = {
+    # name: (architecture, batch, prompt tokens, new tokens of the full configuration)
+    "c4": ("llama-3-8b", 1, 32768, 256),
+    "c5": ("llama-3-70b", 8, 65536, 128),
+}
+
+
+def measure_model(args, wl, K, W, world, rank, local_rank):
+    """Whole-model greedy decode (the reference's `generate.py` flow): random bf16 weights of the
+    named architecture, a prompt of uniform random token ids, prefill (causal flash attention +
+    bulk hashing), then W untimed and K timed decode tokens, one CUDA graph per token - once with
+    the SOCKET sparse step in every layer and once with dense split-KV flash decode over the whole
+    cache.  tokens/s = batch * K / decode time (generate.py:362-368).  Under N > 1 the model is
+    tensor-parallel (heads split as GPT-FAST/tp.py does, explicit all-reduce after `wo` and the
+    feed-forward)."""
+    from socket_b200.model import ModelArgs, Transformer
+    arch, B, T, _ = MODEL_WORKLOADS[wl]
+    dev = torch.device("cuda", local_rank)
+    cfg = ModelArgs.from_name(arch)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = Transformer(cfg, world=world, rank=rank)
+    finally:
+        torch.set_default_dtype(old)
+    model.init_random(seed=args.seed)
+    g = torch.Generator().manual_seed(args.seed)
+    prompt = torch.randint(0, cfg.vocab_size, (B, T), generator=g).pin_memory()
+    n_new = W + K + 1
+    out = {"architecture": arch, "batch": B, "prompt_tokens": T, "decode_tokens_timed": K, "warmup_tokens": W,
+           "layers": cfg.n_layer, "tensor_parallel": world,
+           "sparse": {"L": cfg.L, "P": cfg.K, "topk": cfg.heavy_const, "sink": cfg.sink_size, "window": cfg.window_size}}
+    host_tok = torch.empty(B, 1, dtype=torch.long).pin_memory()
+    for mode in ("sparse", "dense"):
+        model.max_seq_length = -1                         # fresh caches per mode
+        model.setup_caches(B, T + n_new + 8)
+        model.setup_decode(B, mode)
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        logits = model.prefill(prompt.to(dev, non_blocking=True))
+        first = torch.argmax(logits, dim=-1, keepdim=True)
+        t1.record()
+        model.start_decode(first, T)
+        for _ in range(W):
+            model.decode_one_token()
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            model.decode_one_token()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+        ms = float(ms.item())
+        rec = {"tokens_per_s": B * K / (ms * 1e-3), "ms_per_token": ms / K,
+               "prefill_s": t0.elapsed_time(t1) / 1e3, "gpu_launches_per_token_path": 4 * cfg.n_layer if mode == "sparse" else 0}
+        if mode == "sparse":
+            # end to end: every token is copied to pinned host memory and waited for before the next launch
+            n_e = min(K, 32)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(n_e):
+                tok = model.decode_one_token()
+                host_tok.copy_(tok, non_blocking=True)
+                torch.cuda.current_stream(dev).synchronize()
+            e1.record()
+            torch.cuda.synchronize()
+            rec["e2e_tokens_per_s"] = B * n_e / (e0.elapsed_time(e1) * 1e-3)
+            rec["status"] = int(sum(int(l.attention.kv_cache.status) for l in model.layers))
+            rec["rescored_rows"] = sum((l.attention._step.rescored_rows() or 0) for l in model.layers)
+        out[mode] = rec
+        for l in model.layers:                            # release this mode's scratch
+            l.attention._step = None
+    out["sparse_over_dense"] = out["sparse"]["tokens_per_s"] / out["dense"]["tokens_per_s"]
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
+        if args.workload in MODEL_WORKLOADS:
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the whole-model workloads have no CPU arm: the "
+                                  "reference's CPU path is timed at the op level (c1-c3)"}))
+            return
         run_reference(args, PRESETS[args.workload])
         return
 
@@ -647,6 +744,27 @@ def main():
         tp.maybe_init_dist("nccl")
     K, W = args.steps, args.warmup
 
+    if args.workload in MODEL_WORKLOADS:
+        K = min(K, MODEL_WORKLOADS[args.workload][3] - 1)
+        m = measure_model(args, args.workload, K, W, world, rank, local_rank)
+        if rank == 0:
+            print(json.dumps({
+                "metric": "decode_tokens_per_s", "value": m["sparse"]["tokens_per_s"], "unit": "tokens/s",
+                "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": m["sparse"]["ms_per_token"],
+                "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"{args.workload}: greedy decode, {m['architecture']} shape, random bf16 weights, "
+                                       f"batch {m['batch']}, prompt {m['prompt_tokens']} uniform random token ids",
+                           "parallelism": "single GPU" if world == 1 else f"tensor parallel over {world} GPUs (heads split, "
+                                          "NCCL all-reduce after wo and the feed-forward)",
+                           "timing": "CUDA events around K graph-replayed decode tokens"},
+                "model": m, "e2e": {"value": m["sparse"].get("e2e_tokens_per_s"), "unit": "tokens/s",
+                                    "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8 * m["batch"]},
+                "gpu_launches": K * m["sparse"]["gpu_launches_per_token_path"]}))
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+
     res = measure(args, args.workload, K, W, world, rank, local_rank, full=True)
     torch.cuda.empty_cache()
     second = None
@@ -655,6 +773,14 @@ def main():
         if not (world > 1 and args.shard == "strong" and wl2.n_local_heads % world):
             second = measure(args, args.secondary, K, W, world, rank, local_rank, full=False)
             torch.cuda.empty_cache()
+
+    model_rec = None
+    if args.model_record == "on" or (args.model_record == "auto" and world == 1):
+        try:
+            model_rec = measure_model(args, "c4", min(args.model_tokens, K), min(W, 8), world, rank, local_rank)
+        except Exception as e:  # the comparison must never cost the op-level line
+            model_rec = {"failed": repr(e)[:300]}
+        torch.cuda.empty_cache()
 
     cfg_full = PRESETS[args.workload]
     cpu_baseline = None
@@ -683,6 +809,8 @@ def main():
             "rescored_rows": res.get("rescored_rows"),
             "select_stats": res.get("select_stats"),
         }
+        if model_rec is not None:
+            line["c4"] = model_rec
         if second is not None:
             line[args.secondary] = {k: second[k] for k in ("value", "ms_per_step", "us_per_layer", "config",
                                                             "roofline", "stages", "e2e", "clocks", "gpu_launches",
