@@ -63,7 +63,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default="c3", choices=sorted(PRESETS) + ["c4", "c5"],
+    ap.add_argument("--workload", default="c3", choices=sorted(PRESETS) + ["c4", "c4-128k", "c4-128k-b4", "c5"],
                     help="c1-c3: one attention layer (op level); c4 / c5: whole-model greedy decode, "
                          "Llama-3-8B / Llama-3-70B shape with random weights")
     ap.add_argument("--model-record", default="auto", choices=["auto", "on", "off"],
@@ -635,9 +635,12 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
 
 
 MODEL_WORKLOADS = {
-    # name: (architecture, batch, prompt tokens, new tokens of the full configuration)
-    "c4": ("llama-3-8b", 1, 32768, 256),
-    "c5": ("llama-3-70b", 8, 65536, 128),
+    # name: (architecture, batch, prompt tokens, new tokens of the full configuration, sparse overrides)
+    "c4": ("llama-3-8b", 1, 32768, 256, {}),
+    # the same model at the long-context point the 1.5x target is stated on (sparse parameters of c3)
+    "c4-128k": ("llama-3-8b", 1, 131072, 256, dict(heavy_const=2048, sink_size=64, window_size=256)),
+    "c4-128k-b4": ("llama-3-8b", 4, 131072, 256, dict(heavy_const=2048, sink_size=64, window_size=256)),
+    "c5": ("llama-3-70b", 8, 65536, 128, {}),
 }
 
 
@@ -650,9 +653,9 @@ def measure_model(args, wl, K, W, world, rank, local_rank):
     tensor-parallel (heads split as GPT-FAST/tp.py does, explicit all-reduce after `wo` and the
     feed-forward)."""
     from socket_b200.model import ModelArgs, Transformer
-    arch, B, T, _ = MODEL_WORKLOADS[wl]
+    arch, B, T, _, over = MODEL_WORKLOADS[wl]
     dev = torch.device("cuda", local_rank)
-    cfg = ModelArgs.from_name(arch)
+    cfg = ModelArgs.from_name(arch, **over)
     old = torch.get_default_dtype()
     torch.set_default_dtype(torch.bfloat16)
     try:
@@ -663,7 +666,7 @@ def measure_model(args, wl, K, W, world, rank, local_rank):
     model.init_random(seed=args.seed)
     g = torch.Generator().manual_seed(args.seed)
     prompt = torch.randint(0, cfg.vocab_size, (B, T), generator=g).pin_memory()
-    n_new = W + K + 1
+    n_new = W + K + 32 + 8                               # warm-up, timed and end-to-end tokens, spare
     out = {"architecture": arch, "batch": B, "prompt_tokens": T, "decode_tokens_timed": K, "warmup_tokens": W,
            "layers": cfg.n_layer, "tensor_parallel": world,
            "sparse": {"L": cfg.L, "P": cfg.K, "topk": cfg.heavy_const, "sink": cfg.sink_size, "window": cfg.window_size}}

@@ -106,6 +106,18 @@ SK_API int sk_kv_append_tc(const void* k_new, const void* v_new, int kv_dtype, c
                     int64_t Tcap, int L, int P, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Front end of a decode step: split one token's fused QKV projection [B, (H + 2 Hkv) * D] into
+ * q [B,H,D], k [B,1,Hkv,D], v [B,1,Hkv,D] and apply the rotary embedding of position
+ * input_pos[0] (device) to q and k.  Replaces the split + two apply_rotary_emb calls of
+ * Attention.sparse_forward (GPT-FAST/model.py:436-445, 626-637): same fp32 arithmetic, one launch.
+ * freqs_cis: [n_pos, D/2, 2] (cos, sin), bf16 as the reference stores it or fp32.  A position
+ * outside [0, n_pos) writes nothing and sets SK_DEV_POS_OUT_OF_RANGE.
+ * ---------------------------------------------------------------------------------- */
+SK_API int sk_rope_split(const void* qkv, int dtype, const void* freqs_cis, int freq_dtype,
+                  const int64_t* input_pos, int B, int H, int Hkv, int D, int64_t n_pos, void* q_out,
+                  void* k_out, void* v_out, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Query soft hash.  Replaces Attention.soft_hash (GPT-FAST/model.py:392-401):
  * q_probs[b,h,l,:] = softmax_r( (tanh(<q, planes[l,p]>) / sqrt(D)) . protos_T[p,r] / temperature )
  * (temperature 1.0 = the GPT-FAST formula; the HuggingFace variant divides by 0.3,

@@ -185,6 +185,19 @@ int sk_kv_append_tc(const void* k_new, const void* v_new, int kv_dtype, const in
     return launch_hash_keys_tc(k_new, D, planes, N, codes, L, dst_row, ws + off, workspace_bytes - off, status, st);
 }
 
+int sk_rope_split(const void* qkv, int dtype, const void* freqs_cis, int freq_dtype, const int64_t* input_pos,
+                  int B, int H, int Hkv, int D, int64_t n_pos, void* q_out, void* k_out, void* v_out,
+                  int32_t* status, void* stream) {
+    SK_REQUIRE(B >= 0 && H > 0 && Hkv > 0 && D > 0 && n_pos > 0, "sk_rope_split: sizes must be positive");
+    if (B == 0) return SK_OK;
+    SK_REQUIRE(D % 2 == 0, "sk_rope_split: head_dim %d is odd", D);
+    SK_REQUIRE(qkv && freqs_cis && input_pos && q_out && k_out && v_out, "sk_rope_split: null pointer");
+    SK_REQUIRE(valid_dtype(dtype) && (freq_dtype == SK_BF16 || freq_dtype == SK_F32), "sk_rope_split: bad dtype");
+    SK_REQUIRE(B <= 65535, "sk_rope_split: B > 65535");
+    return launch_rope_split(qkv, dtype, freqs_cis, freq_dtype, input_pos, B, H, Hkv, D, n_pos, q_out, k_out, v_out,
+                             status, (cudaStream_t)stream);
+}
+
 int sk_lut_head_tile(int rep) { return rep > 0 ? lut_head_tile(rep) : 0; }
 
 int sk_soft_hash(const void* q, int q_dtype, const void* planes, int plane_dtype,

@@ -267,6 +267,10 @@ int launch_kv_copy(const void* k_new, const void* v_new, int kv_dtype, const int
                    void* v_cache, uint16_t* v_norm, int32_t* prefill_len, int32_t* status, int B, int S,
                    int Hkv, int D, int64_t Tcap, cudaStream_t st);
 
+int launch_rope_split(const void* qkv, int dtype, const void* freqs_cis, int freq_dtype, const int64_t* input_pos,
+                      int B, int H, int Hkv, int D, int64_t n_pos, void* q_out, void* k_out, void* v_out,
+                      int32_t* status, cudaStream_t st);
+
 int lut_head_tile(int rep);
 int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, int dtype,
                            const int64_t* input_pos, const void* planes, int plane_dtype,

@@ -23,8 +23,7 @@ and is the full-attention baseline of the tokens/s comparison.
 """
 from __future__ import annotations
 
-import math
-from dataclasses import dataclass, replace
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -98,6 +97,8 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
 
     def forward(self, x: Tensor) -> Tensor:
+        if x.is_cuda:                                   # one fused library kernel
+            return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
         xf = x.float()
         return (xf * torch.rsqrt(torch.mean(xf * xf, dim=-1, keepdim=True) + self.eps)).type_as(x) * self.weight
 
@@ -122,15 +123,26 @@ def apply_rotary_emb(x: Tensor, freqs_cis: Tensor, out: Optional[Tensor] = None)
 
 
 class FeedForward(nn.Module):
+    """SwiGLU feed-forward (GPT-FAST/model.py:592-600).  `w1` and `w3` are the two halves of one
+    parameter so that the gate and the up projection are one GEMM."""
+
     def __init__(self, config: ModelArgs, world: int = 1):
         super().__init__()
-        inter = config.intermediate_size // world
-        self.w1 = nn.Linear(config.dim, inter, bias=False)
-        self.w3 = nn.Linear(config.dim, inter, bias=False)
-        self.w2 = nn.Linear(inter, config.dim, bias=False)
+        self.inter = config.intermediate_size // world
+        self.w13 = nn.Linear(config.dim, 2 * self.inter, bias=False)
+        self.w2 = nn.Linear(self.inter, config.dim, bias=False)
+
+    @property
+    def w1(self) -> Tensor:
+        return self.w13.weight[:self.inter]
+
+    @property
+    def w3(self) -> Tensor:
+        return self.w13.weight[self.inter:]
 
     def forward(self, x: Tensor) -> Tensor:
-        return self.w2(F.silu(self.w1(x)) * self.w3(x))
+        a, b = self.w13(x).split(self.inter, dim=-1)
+        return self.w2(F.silu(a) * b)
 
 
 class Attention(nn.Module):
@@ -193,14 +205,21 @@ class Attention(nn.Module):
                                         window=self.window_size, T_max=cache.k_cache.shape[2],
                                         temperature=self.temperature)
 
-    def decode(self, x: Tensor, freqs_cis: Tensor, pos: Tensor, seqlens: Optional[Tensor], mode: str) -> Tensor:
+    def decode(self, x: Tensor, freqs_cis: Tensor, pos: Tensor, seqlens: Optional[Tensor], mode: str,
+               rope_table: Optional[Tensor] = None) -> Tensor:
         """x [B,1,dim]; `pos` [1] int64 (device) is the new token's position; `seqlens` [B] int32 =
-        keys already cached (dense mode)."""
+        keys already cached (dense mode); `freqs_cis` the position's rotary row (CPU flow),
+        `rope_table` the whole table (GPU flow: the row is picked on the device)."""
         B = x.shape[0]
-        q, k, v = self.wqkv(x).split([self.local_dim, self.kv_size, self.kv_size], dim=-1)
-        apply_rotary_emb(q.view(B, 1, self.n_head, self.head_dim), freqs_cis, out=self.q_s)
-        apply_rotary_emb(k.view(B, 1, self.n_local_heads, self.head_dim), freqs_cis, out=self.k_s)
-        self.v_s.copy_(v.view(self.v_s.shape))
+        qkv = self.wqkv(x)
+        if x.is_cuda:
+            # split + rotary embedding of q and k in one launch, straight into the step's inputs
+            ops.rope_split(qkv, rope_table, pos, self.n_head, self.n_local_heads, self.q_s, self.k_s, self.v_s)
+        else:
+            q, k, v = qkv.split([self.local_dim, self.kv_size, self.kv_size], dim=-1)
+            apply_rotary_emb(q.view(B, 1, self.n_head, self.head_dim), freqs_cis, out=self.q_s)
+            apply_rotary_emb(k.view(B, 1, self.n_local_heads, self.head_dim), freqs_cis, out=self.k_s)
+            self.v_s.copy_(v.view(self.v_s.shape))
         cache = self.kv_cache
         if mode == "sparse":
             self._step.run()
@@ -253,8 +272,8 @@ class TransformerBlock(nn.Module):
         h = x + self._sum(self.attention.prefill(self.attention_norm(x), freqs_cis, input_pos, start))
         return h + self._sum(self.feed_forward(self.ffn_norm(h)))
 
-    def decode(self, x, freqs_cis, pos, seqlens, mode):
-        h = x + self._sum(self.attention.decode(self.attention_norm(x), freqs_cis, pos, seqlens, mode))
+    def decode(self, x, freqs_cis, pos, seqlens, mode, rope_table=None):
+        h = x + self._sum(self.attention.decode(self.attention_norm(x), freqs_cis, pos, seqlens, mode, rope_table))
         return h + self._sum(self.feed_forward(self.ffn_norm(h)))
 
 
@@ -330,9 +349,9 @@ class Transformer(nn.Module):
     # ------------------------------------------------------------------------------- decode
     def _decode_body(self, mode: str) -> None:
         x = self.tok_embeddings(self._tok)                      # [B,1,dim]
-        fc = self.freqs_cis[self._pos]                          # [1,D/2,2]
+        fc = None if x.is_cuda else self.freqs_cis[self._pos]   # [1,D/2,2]
         for layer in self.layers:
-            x = layer.decode(x, fc, self._pos, self._seqlens, mode)
+            x = layer.decode(x, fc, self._pos, self._seqlens, mode, self.freqs_cis)
         logits = self.output(self.norm(x))[:, -1]
         self._tok.copy_(torch.argmax(logits, dim=-1, keepdim=True))
         self._pos.add_(1)
@@ -350,6 +369,7 @@ class Transformer(nn.Module):
         for layer in self.layers:
             layer.attention.setup_decode(batch, self._pos, mode)
         self._graph = None
+        self._host_pos = 0
         if use_graph and dev.type == "cuda":
             saved = (self._tok.clone(), self._pos.clone(), self._seqlens.clone())
             side = torch.cuda.Stream(dev)
@@ -369,6 +389,10 @@ class Transformer(nn.Module):
     @torch.no_grad()
     def start_decode(self, first_token: Tensor, position: int) -> None:
         """`first_token` [B,1] sits at `position` (= number of tokens already cached)."""
+        if position >= self.max_seq_length:
+            raise RuntimeError(f"start_decode: position {position} outside the caches (max_seq_length="
+                               f"{self.max_seq_length})")
+        self._host_pos = position                 # host mirror of the device-side position counter
         self._tok.copy_(first_token)
         self._pos.fill_(position)
         self._seqlens.fill_(position)
@@ -378,7 +402,13 @@ class Transformer(nn.Module):
 
     @torch.no_grad()
     def decode_one_token(self) -> Tensor:
-        """Runs one token through the model (greedy); returns the buffer holding the new token."""
+        """Runs one token through the model (greedy); returns the buffer holding the new token.
+        Raises before anything is launched when the caches are full (same situation as the
+        reference's `_check_input_pos`, GPT-FAST/model.py:279-289, without its device round trip)."""
+        if self._host_pos >= self.max_seq_length:
+            raise RuntimeError(f"decode position {self._host_pos} outside the caches (max_seq_length="
+                               f"{self.max_seq_length}); call setup_caches with a larger length")
+        self._host_pos += 1
         if self._graph is not None:
             self._graph.replay()
         else:

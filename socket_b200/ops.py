@@ -111,6 +111,23 @@ def kv_append(k_cache, v_cache, codes, v_norm, prefill_len, input_pos, k_new, v_
                              stream_ptr(k_cache.device)), "sk_kv_append")
 
 
+def rope_split(qkv: torch.Tensor, freqs_cis: torch.Tensor, input_pos: torch.Tensor, n_head: int,
+               n_kv_heads: int, q_out: torch.Tensor, k_out: torch.Tensor, v_out: torch.Tensor,
+               status: Optional[torch.Tensor] = None) -> None:
+    """qkv [B,1,(H+2Hkv)*D] of one new token -> q_out [B,H,D], k_out / v_out [B,1,Hkv,D], q and k
+    rotated by the angles of position `input_pos[0]` (device int64); freqs_cis [n_pos, D/2, 2]."""
+    _require_cuda(qkv, freqs_cis, input_pos, q_out, k_out, v_out)
+    B, H, D = q_out.shape
+    assert H == n_head and k_out.shape == (B, 1, n_kv_heads, D) and v_out.shape == k_out.shape
+    assert qkv.is_contiguous() and qkv.numel() == B * (H + 2 * n_kv_heads) * D
+    assert q_out.is_contiguous() and k_out.is_contiguous() and v_out.is_contiguous()
+    assert freqs_cis.is_contiguous() and freqs_cis.shape[1:] == (D // 2, 2)
+    assert input_pos.dtype == torch.int64
+    check(lib().sk_rope_split(ptr(qkv), dtype_code(qkv), ptr(freqs_cis), dtype_code(freqs_cis), ptr(input_pos), B, H,
+                              n_kv_heads, D, freqs_cis.shape[0], ptr(q_out), ptr(k_out), ptr(v_out), ptr(status),
+                              stream_ptr(qkv.device)), "sk_rope_split")
+
+
 def soft_hash(q_bhd: torch.Tensor, planes: torch.Tensor, protos_T: torch.Tensor,
               temperature: float = 1.0, n_kv_heads: Optional[int] = None,
               want_probs: bool = True, want_lut: bool = False):

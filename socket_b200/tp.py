@@ -107,8 +107,8 @@ def shard_transformer(full, world_size: int, rank: int):
         b.wo.weight.copy_(_cols(a.wo.weight, world_size, rank))
         b.planes.copy_(a.planes)
         b.protos_T.copy_(a.protos_T)
-        dst.feed_forward.w1.weight.copy_(_rows(src.feed_forward.w1.weight, world_size, rank))
-        dst.feed_forward.w3.weight.copy_(_rows(src.feed_forward.w3.weight, world_size, rank))
+        dst.feed_forward.w1.copy_(_rows(src.feed_forward.w1, world_size, rank))
+        dst.feed_forward.w3.copy_(_rows(src.feed_forward.w3, world_size, rank))
         dst.feed_forward.w2.weight.copy_(_cols(src.feed_forward.w2.weight, world_size, rank))
         dst.attention_norm.weight.copy_(src.attention_norm.weight)
         dst.ffn_norm.weight.copy_(src.ffn_norm.weight)

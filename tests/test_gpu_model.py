@@ -4,7 +4,8 @@ import pytest
 import torch
 
 from oracle import socket_oracle as orc
-from socket_b200.model import ModelArgs, Transformer, generate
+from socket_b200 import ops
+from socket_b200.model import ModelArgs, Transformer, apply_rotary_emb, generate, precompute_freqs_cis
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -67,3 +68,27 @@ def test_sparse_decode_tracks_dense_decode_when_the_budget_covers_the_context():
     model.max_seq_length = -1
     b, _ = generate(model, prompt, 8, mode="dense", use_graph=False)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fused_rope_split_equals_the_tensor_formulation(dtype):
+    B, H, Hkv, D, n_pos = 3, 8, 2, 128, 500
+    g = torch.Generator().manual_seed(0)
+    qkv = torch.randn(B, 1, (H + 2 * Hkv) * D, generator=g).to(dtype).to(DEV)
+    table = precompute_freqs_cis(n_pos, D, 500000.0, device=DEV)
+    pos = torch.tensor([317], device=DEV)
+    q = torch.empty(B, H, D, dtype=dtype, device=DEV)
+    k = torch.empty(B, 1, Hkv, D, dtype=dtype, device=DEV)
+    v = torch.empty_like(k)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.rope_split(qkv, table, pos, H, Hkv, q, k, v, status=status)
+    qq, kk, vv = qkv.split([H * D, Hkv * D, Hkv * D], dim=-1)
+    want_q = apply_rotary_emb(qq.view(B, 1, H, D), table[pos])
+    want_k = apply_rotary_emb(kk.view(B, 1, Hkv, D), table[pos])
+    assert torch.equal(q, want_q.view(B, H, D)) and torch.equal(k, want_k) and torch.equal(v, vv.view(B, 1, Hkv, D))
+    assert int(status) == 0
+    # a position outside the table is reported, not read
+    q.zero_()
+    ops.rope_split(qkv, table, torch.tensor([n_pos], device=DEV), H, Hkv, q, k, v, status=status)
+    torch.cuda.synchronize()
+    assert int(status) == 1 and (q == 0).all()
