@@ -714,6 +714,11 @@ def measure_model(args, wl, K, W, world, rank, local_rank):
             rec["e2e_tokens_per_s"] = B * n_e / (e0.elapsed_time(e1) * 1e-3)
             rec["status"] = int(sum(int(l.attention.kv_cache.status) for l in model.layers))
             rec["rescored_rows"] = sum((l.attention._step.rescored_rows() or 0) for l in model.layers)
+            agg = {}
+            for l in model.layers:
+                for k, v in (l.attention._step.select_stats() or {}).items():
+                    agg[k] = agg.get(k, 0) + v
+            rec["select_stats"] = agg
         out[mode] = rec
         for l in model.layers:                            # release this mode's scratch
             l.attention._step = None

@@ -136,6 +136,7 @@ struct ScorePlan {
 constexpr int SC_THREADS = 1024;
 constexpr int SC_WARPS = SC_THREADS / 32;
 constexpr int SEL_CAP = 16384;   // candidates the select kernel can hold on chip
+constexpr int SC_TAIL = 1024;    // newest keys of a row that the filtering scorer always keeps (see FilterArgs::tail)
 constexpr int64_t SC_SWITCH_PAD = 3584;   // empty slots after each group in the flat split, see make_score_plan
 
 inline ScorePlan make_score_plan(int n_groups, int64_t T, int64_t M) {
@@ -183,7 +184,7 @@ inline bool fused_filter_applicable(const ScorePlan& p, int64_t T, int64_t M) {
 
 // Workspace of the fused scorer + select: [fallback counter | cnt | cut | cand | scratch scores]
 struct FusedLayout {
-    size_t stats, cnt, cut, cand, scores, total;
+    size_t stats, cnt, cut, cand, tail, scores, total;
     int64_t score_stride;
 };
 inline size_t sk_up256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -195,6 +196,7 @@ inline FusedLayout make_fused_layout(int64_t rows, const ScorePlan& p, int64_t T
     f.cnt = off;    off += sk_up256((size_t)rows * p.chunks_max * SC_WARPS * sizeof(int32_t));
     f.cut = off;    off += sk_up256((size_t)rows * p.chunks_max * sizeof(float));
     f.cand = off;   off += sk_up256((size_t)rows * p.chunks_max * SC_WARPS * p.cap_w * 8);
+    f.tail = off;   off += sk_up256((size_t)rows * SC_TAIL * 8);
     f.scores = off; off += sk_up256((size_t)rows * f.score_stride * sizeof(float));
     f.total = off;
     return f;

@@ -21,89 +21,81 @@ namespace sk {
 namespace {
 
 // Shared memory after the table: mbarrier | per-head sample statistics for the filter mode.
+constexpr int SC_SAMPLE_WARPS = 16;         // warps whose lanes score one sample key each
+constexpr int SC_SAMPLES = 32 * SC_SAMPLE_WARPS;
+
 struct FilterShared {
     uint64_t bar;
-    float warp_stat[4][SC_WARPS];          // per head: every warp's order statistic of its sample
-    int warp_full[SC_WARPS];               // the warp's sample has all 32 keys
+    uint32_t skey[4][SC_SAMPLES];          // per head: order keys of the sample scores
+    float cut[4];
 };
 
 struct FilterArgs {
     int32_t* cnt;        // [rows][chunks_max][32]
     float* cut;          // [rows][chunks_max]
     uint2* cand;         // [rows][chunks_max][32][cap_w]  (score bits, key index)
+    // The newest SC_TAIL keys of a row are not filtered: entry t - (T - SC_TAIL) of the row's tail
+    // holds key t, whatever its score.  In a real model the keys just before the query score high
+    // as a block (rotary position embedding, local context); compacted into their warp's run they
+    // would overflow it and send the row to the rescoring path on every step.
+    uint2* tail;         // [rows][SC_TAIL]
     int chunks_max, cap_w;
     float keep;          // keys the filter aims to keep per row: 3 * M (the fraction follows the LIVE length)
 };
 
-// Per-head cut from one sample score per thread (sv[j], `valid`), chosen so that about `frac` of
-// the keys exceed it.  Every warp finds an order statistic of its own 32 samples - the t-th largest,
-// t = frac * 33 + 0.5, interpolated between two neighbouring ranks - with a few rounds of
-// redux-max, and the cut is the mean of the warps' values: one barrier, no histogram.  Any value
-// would be correct (the select kernel proves or repairs the result); this one only has to be close.
-// (Short segments - at most 1024 keys and half a CTA's share - never get here: with so few sampling
-// warps the mean is noisy, and a cut above the row's k-th score sends the row to the rescoring path,
-// so they keep every key.)
+// Per-head cut from the SC_SAMPLES sample scores (one per thread of the first SC_SAMPLE_WARPS warps,
+// sv[j]), such that the fraction `frac` of the samples lies at or above it: the r-th largest sample,
+// r = frac * SC_SAMPLES, found exactly by one warp per head with a bitwise descent on the order keys
+// (the low 8 key bits are left at zero, which can only lower the cut).  Any value would be correct
+// (the select kernel proves or repairs the result); a cut above the row's k-th score costs the row a
+// full rescoring, and with r around 3 k T^-1 SC_SAMPLES the chance of that is the chance that a third
+// of the expected number of samples above the k-th score turns into all of them.
 // The cuts are returned in cut[] and, for the select kernel's check, written to cut_out[j * cut_stride].
 // Must be called by the whole CTA.
 template <int HT>
-__device__ __forceinline__ void filter_cuts(FilterShared& fs, const float (&sv)[HT], bool valid, float frac,
+__device__ __forceinline__ void filter_cuts(FilterShared& fs, const float (&sv)[HT], bool sampling, float frac,
                                             float* __restrict__ cut_out, size_t cut_stride, float (&cut)[HT]) {
-    static_assert(SC_WARPS == 32, "one lane per warp in the final mean");
+    static_assert(HT <= 4 && SC_SAMPLES % 32 == 0, "one selecting warp per head");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // wanted rank among 32 samples (1 = the largest)
-    const float t = frac * 33.0f + 0.5f;
-    const int r_lo = max(1, min(31, (int)t));
-    const float w = fminf(fmaxf(t - (float)r_lo, 0.f), 1.f);
-    uint32_t key[HT], s_lo[HT], s_hi[HT];
-#pragma unroll
-    for (int j = 0; j < HT; ++j) {
-        const bool fin = valid && sv[j] > -INFINITY && sv[j] < INFINITY;
-        key[j] = fin ? order_key(sv[j]) : 0u;             // 0 = no sample (below every finite score's key)
-        s_lo[j] = s_hi[j] = 0u;
-    }
-    for (int r = 1; r <= r_lo + 1; ++r) {                 // uniform trip count
+    if (sampling) {
 #pragma unroll
         for (int j = 0; j < HT; ++j) {
-            const uint32_t mx = __reduce_max_sync(FULL, key[j]);
-            if (r == r_lo) s_lo[j] = mx;
-            if (r == r_lo + 1) s_hi[j] = mx;
-            const unsigned who = __ballot_sync(FULL, key[j] == mx);
-            if (lane == __ffs(who) - 1) key[j] = 0u;      // take one instance out
-        }
-    }
-    const bool full = __all_sync(FULL, valid);
-    if (lane == 0) {
-        fs.warp_full[warp] = full ? 1 : 0;
-#pragma unroll
-        for (int j = 0; j < HT; ++j) {
-            // a warp with fewer than r_lo + 1 samples contributes nothing
-            fs.warp_stat[j][warp] = (s_hi[j] != 0u)
-                                        ? (1.f - w) * order_key_inverse(s_lo[j]) + w * order_key_inverse(s_hi[j])
-                                        : NAN;
+            const bool fin = sv[j] > -INFINITY && sv[j] < INFINITY;
+            fs.skey[j][threadIdx.x] = fin ? order_key(sv[j]) : 0u;     // sampling threads are 0 .. SC_SAMPLES-1
         }
     }
     __syncthreads();
-    // a warp with a partial sample (the last one of a short segment) reports a lower quantile - with
-    // barely r_lo + 1 keys, about its minimum - and would drag the mean down until the runs
-    // overflow: it only counts when no warp has a full sample
-    const bool any_full = __any_sync(FULL, fs.warp_full[lane] != 0);
+    if (warp < HT) {
+        uint32_t k[SC_SAMPLES / 32];
 #pragma unroll
-    for (int j = 0; j < HT; ++j) {
-        const float v = fs.warp_stat[j][lane];
-        const bool have = v == v && (!any_full || fs.warp_full[lane] != 0);
-        const int n = __popc(__ballot_sync(FULL, have));
-        float sum = have ? v : 0.f;
+        for (int i = 0; i < SC_SAMPLES / 32; ++i) k[i] = fs.skey[warp][lane + 32 * i];
+        const int r = max(2, min(SC_SAMPLES / 2, (int)(frac * (float)SC_SAMPLES + 0.5f)));
+        // the bits above the highest one in which two usable samples differ are common to all of them
+        uint32_t kmx = 0u, kmn = 0xffffffffu;
 #pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(FULL, sum, o);
-        cut[j] = n > 0 ? sum / (float)n : -INFINITY;      // no usable sample: keep everything
+        for (int i = 0; i < SC_SAMPLES / 32; ++i) {
+            kmx = max(kmx, k[i]);
+            if (k[i] != 0u) kmn = min(kmn, k[i]);
+        }
+        kmx = __reduce_max_sync(FULL, kmx);
+        kmn = __reduce_min_sync(FULL, kmn);
+        const int top = kmx > kmn ? 31 - __clz(kmx ^ kmn) : 7;          // first bit to decide
+        uint32_t prefix = top < 31 ? (kmx >> (top + 1)) << (top + 1) : 0u;
+        if (kmx == 0u) prefix = 0u;
+        for (int bit = top; bit >= 8; --bit) {
+            const uint32_t cand = prefix | (1u << bit);
+            int c = 0;
+#pragma unroll
+            for (int i = 0; i < SC_SAMPLES / 32; ++i) c += k[i] >= cand;
+            c = __reduce_add_sync(FULL, c);
+            if (c >= r) prefix = cand;
+        }
+        if (lane == 0) fs.cut[warp] = prefix != 0u ? order_key_inverse(prefix) : -INFINITY;   // no usable sample: keep everything
     }
-    if (threadIdx.x < HT) {
-        float mine = -INFINITY;
+    __syncthreads();
 #pragma unroll
-        for (int j = 0; j < HT; ++j)
-            if (j == (int)threadIdx.x) mine = cut[j];
-        cut_out[(size_t)threadIdx.x * cut_stride] = mine;
-    }
+    for (int j = 0; j < HT; ++j) cut[j] = fs.cut[j];
+    if (threadIdx.x < HT) cut_out[(size_t)threadIdx.x * cut_stride] = fs.cut[threadIdx.x];
 }
 
 // L: tables per key (bytes per key), HT: query heads per table word.
@@ -222,15 +214,34 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         uint4 cur[NV], nxt[NV];
         __half vcur = __float2half(0.f), vnxt = __float2half(0.f);   // ||v|| travels with the codes
         int t = ws + lane;
-        if (t < we) {
+        if (FILTER) {
+            // the sample: 512 keys spread evenly over the WHOLE row (sampling thread i takes key
+            // (i + 1/2) * T / 512, a warp's 32 samples interleaved over the row), the same keys in every
+            // CTA of the row.  Every chunk then cuts at the same score, about 3 M keys of the row pass
+            // whatever their positions are, and a region of high scores (recent tokens in a real
+            // model) does not get a cut of its own above the row's k-th score.
+            if (warp < SC_SAMPLE_WARPS) {
+                const int ts = (int)(((int64_t)(2 * (lane * SC_SAMPLE_WARPS + warp) + 1) * Teff) / (64 * SC_SAMPLE_WARPS));
 #pragma unroll
-            for (int i = 0; i < NV; ++i) cur[i] = __ldcg(cg + (size_t)t * NV + i);
-            vcur = __ldcg(vg + t);
-        }
-        if (t + 32 < we) {
+                for (int i = 0; i < NV; ++i) cur[i] = __ldcg(cg + (size_t)ts * NV + i);
+                vcur = __ldcg(vg + ts);
+            }
+            if (t < we) {                      // the warp's first own key rides behind the sample
 #pragma unroll
-            for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cg + (size_t)(t + 32) * NV + i);
-            vnxt = __ldcg(vg + t + 32);
+                for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cg + (size_t)t * NV + i);
+                vnxt = __ldcg(vg + t);
+            }
+        } else {
+            if (t < we) {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) cur[i] = __ldcg(cg + (size_t)t * NV + i);
+                vcur = __ldcg(vg + t);
+            }
+            if (t + 32 < we) {
+#pragma unroll
+                for (int i = 0; i < NV; ++i) nxt[i] = __ldcg(cg + (size_t)(t + 32) * NV + i);
+                vnxt = __ldcg(vg + t + 32);
+            }
         }
 
         const bool ok = mbar_wait(bar, phase);
@@ -241,60 +252,37 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
         }
 
         uint32_t cnt4 = 0;            // four 8-bit run lengths, saturating at 255 (cap_w <= 250)
+        const int tail_start = max(Teff - SC_TAIL, 0);
         float cutv[HT];
 #pragma unroll
         for (int j = 0; j < HT; ++j) cutv[j] = -INFINITY;
-        bool first = true;
         // this warp's run of head j starts at entry run_index0 + j * run_stride of the candidate buffer
         // (32-bit entry indices: the buffer holds far fewer than 2^31 entries)
         const int run_stride = fa.chunks_max * SC_WARPS * fa.cap_w;
         const int run_index0 = FILTER ? (((int)row0 * fa.chunks_max + chunk) * SC_WARPS + warp) * fa.cap_w : 0;
 
         if (FILTER) {
-            // ---- sample = first key of every lane: scores, cut
+            // ---- the row-wide sample: scores, cut
             float sv[HT];
-            const bool valid = t < we;
-            if (valid) {
+#pragma unroll
+            for (int j = 0; j < HT; ++j) sv[j] = 0.f;
+            if (warp < SC_SAMPLE_WARPS) {           // warp-uniform
                 float acc[HT];
                 score_key<L, HT>(cur, lut_s, sel_lo, sel_hi, mL, acc);
                 const float vn = __half2float(vcur);
 #pragma unroll
                 for (int j = 0; j < HT; ++j) sv[j] = acc[j] * vn;
-            } else {
-#pragma unroll
-                for (int j = 0; j < HT; ++j) sv[j] = 0.f;
             }
             // a short segment (the newest keys of a partly filled chunk, or the few keys a CTA has on
             // one side of a KV-head boundary) keeps everything when its runs have the room
-            // (at most half a CTA's share: a whole chunk of a small problem goes the normal way, where
-            // every one of its keys is a sample)
             if (t1 - t0 <= 1024 && 2 * (t1 - t0) <= slots_per_cta && per_warp <= fa.cap_w) {   // uniform across the CTA
                 if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
             } else {
                 // the kept fraction is taken of the live length: the capacity the plan was made for may
                 // be several times larger, and a cut for 3M / capacity would drop needed keys
-                filter_cuts<HT>(fs, sv, valid, fminf(__fdividef(fa.keep, (float)Teff), 1.0f), fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
+                filter_cuts<HT>(fs, sv, warp < SC_SAMPLE_WARPS, fminf(__fdividef(fa.keep, (float)Teff), 1.0f), fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
             }
-            // the sample keys themselves
-#pragma unroll
-            for (int j = 0; j < HT; ++j) {
-                const bool hit = valid && sv[j] >= cutv[j];
-                const unsigned bal = __ballot_sync(FULL, hit);
-                if (bal != 0u) {                              // warp-uniform
-                    const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
-                    const int pos = have + __popc(bal & ((1u << lane) - 1u));
-                    if (hit && pos < fa.cap_w)
-                        fa.cand[(size_t)(run_index0 + j * run_stride + pos)] =
-                            make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
-                    cnt4 += (uint32_t)min(__popc(bal), 255 - have) << (8 * j);
-                }
-            }
-            first = false;
-        }
-
-        // ---- main loop over this warp's keys, codes double-buffered in registers
-        if (!first) {
-            t += 32;
+            // on to the warp's own keys
 #pragma unroll
             for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
             vcur = vnxt;
@@ -304,6 +292,8 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
                 vnxt = __ldcg(vg + t + 32);
             }
         }
+
+        // ---- main loop over this warp's keys, codes double-buffered in registers
         for (; t - lane < we; t += 32) {
             const bool valid = t < we;
             float sv[HT];
@@ -315,9 +305,15 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
                 for (int j = 0; j < HT; ++j) sv[j] = acc[j] * vn;
             }
             if (FILTER) {
+                const bool in_tail = valid && t >= tail_start;
+                if (in_tail) {
+#pragma unroll
+                    for (int j = 0; j < HT; ++j)
+                        fa.tail[(row0 + j) * SC_TAIL + (t - tail_start)] = make_uint2(__float_as_uint(sv[j]), (uint32_t)t);
+                }
 #pragma unroll
                 for (int j = 0; j < HT; ++j) {
-                    const bool hit = valid && sv[j] >= cutv[j];
+                    const bool hit = valid && !in_tail && sv[j] >= cutv[j];
                     const unsigned bal = __ballot_sync(FULL, hit);
                     if (bal != 0u) {                              // warp-uniform
                         const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
@@ -543,13 +539,18 @@ score_packed_kernel(const uint8_t* __restrict__ lutq, const float* __restrict__ 
         for (int i = 0; i < 8; ++i) cur[i] = nxt[i] = 0u;
         uint16_t vcur = 0, vnxt = 0;                                 // ||v|| (fp16 bits) travels with the codes
         int t = ws + lane;
-        if (t < we) {
-            ldg256(cg + (size_t)t * L, cur);
-            vcur = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t);
-        }
-        if (t + 32 < we) {
-            ldg256(cg + (size_t)(t + 32) * L, nxt);
-            vnxt = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t + 32);
+        {
+            // the sample: 512 keys spread evenly over the whole row, the same in every CTA of the row
+            // (see score_kernel); the warp's first own key rides behind it
+            if (warp < SC_SAMPLE_WARPS) {
+                const int ts = (int)(((int64_t)(2 * (lane * SC_SAMPLE_WARPS + warp) + 1) * Teff) / (64 * SC_SAMPLE_WARPS));
+                ldg256(cg + (size_t)ts * L, cur);
+                vcur = __ldcg(reinterpret_cast<const uint16_t*>(vg) + ts);
+            }
+            if (t < we) {
+                ldg256(cg + (size_t)t * L, nxt);
+                vnxt = __ldcg(reinterpret_cast<const uint16_t*>(vg) + t);
+            }
         }
 
         const bool ok = mbar_wait(bar, phase);
@@ -560,6 +561,7 @@ score_packed_kernel(const uint8_t* __restrict__ lutq, const float* __restrict__ 
         }
 
         uint32_t cnt4 = 0;            // four 8-bit run lengths, saturating at 255 (cap_w <= 250)
+        const int tail_start = max(Teff - SC_TAIL, 0);
         float cutv[HT];
 #pragma unroll
         for (int j = 0; j < HT; ++j) cutv[j] = -INFINITY;
@@ -582,9 +584,15 @@ score_packed_kernel(const uint8_t* __restrict__ lutq, const float* __restrict__ 
             }
         };
         auto keep = [&](const uint32_t (&pk)[HT], const float (&sv)[HT], bool valid, int tk) {
+            const bool in_tail = valid && tk >= tail_start;
+            if (in_tail) {                                    // the row's newest keys are kept unfiltered
+#pragma unroll
+                for (int j = 0; j < HT; ++j)
+                    fa.tail[(row0 + j) * SC_TAIL + (tk - tail_start)] = make_uint2(pk[j], (uint32_t)tk);
+            }
 #pragma unroll
             for (int j = 0; j < HT; ++j) {
-                const bool hit = valid && sv[j] >= cutv[j];
+                const bool hit = valid && !in_tail && sv[j] >= cutv[j];
                 const unsigned bal = __ballot_sync(FULL, hit);
                 if (bal != 0u) {                              // warp-uniform
                     const int have = (int)((cnt4 >> (8 * j)) & 0xffu);
@@ -597,24 +605,20 @@ score_packed_kernel(const uint8_t* __restrict__ lutq, const float* __restrict__ 
         };
 
         {
-            // ---- sample = first key of every lane: scores, cut
+            // ---- the row-wide sample: scores, cut
             float sv[HT];
             uint32_t pk[HT];
-            const bool valid = t < we;
-            score_cur(pk, sv);
-            if (!valid) {
 #pragma unroll
-                for (int j = 0; j < HT; ++j) sv[j] = 0.f;
-            }
+            for (int j = 0; j < HT; ++j) sv[j] = 0.f;
+            if (warp < SC_SAMPLE_WARPS) score_cur(pk, sv);          // warp-uniform
             if (t1 - t0 <= 1024 && 2 * (t1 - t0) <= slots_per_cta && per_warp <= fa.cap_w) {   // uniform across the CTA
                 if (threadIdx.x < HT) fa.cut[(row0 + threadIdx.x) * fa.chunks_max + chunk] = -INFINITY;
             } else {
-                filter_cuts<HT>(fs, sv, valid, fminf(__fdividef(fa.keep, (float)Teff), 1.0f),
+                filter_cuts<HT>(fs, sv, warp < SC_SAMPLE_WARPS, fminf(__fdividef(fa.keep, (float)Teff), 1.0f),
                                 fa.cut + row0 * fa.chunks_max + chunk, (size_t)fa.chunks_max, cutv);
             }
-            keep(pk, sv, valid, t);
         }
-        t += 32;
+        // on to the warp's own keys
 #pragma unroll
         for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
         vcur = vnxt;
@@ -749,6 +753,7 @@ int launch_score_filter(const float* lut, const uint8_t* codes, const uint16_t* 
     fa.cnt = reinterpret_cast<int32_t*>(ws + lay.cnt);
     fa.cut = reinterpret_cast<float*>(ws + lay.cut);
     fa.cand = reinterpret_cast<uint2*>(ws + lay.cand);
+    fa.tail = reinterpret_cast<uint2*>(ws + lay.tail);
     fa.chunks_max = plan.chunks_max;
     fa.cap_w = plan.cap_w;
     fa.keep = plan.frac * (float)T;

@@ -37,7 +37,6 @@ struct SelShared {
     uint32_t hist[SEL_BINS];
     uint32_t cand_key[SEL_CAP];
     int32_t cand_idx[SEL_CAP];
-    uint32_t cand_aux[SEL_CAP];                   // packed candidates: the (S, ||v||) word of every candidate
     int scan_buf[2][40];
     uint32_t red_lo[SEL_WARPS], red_hi[SEL_WARPS], red_x[SEL_WARPS];
     int thr_bin, thr_above, thr_inbin;
@@ -699,6 +698,7 @@ struct CandArgs {
     int64_t Tcap;
     const float* qpar;      // packed candidates: K0 of every KV-head group
     const float* probs;     // packed candidates: q_probs [rows][32][256] fp32 (rows 32 KiB apart)
+    const uint2* tail;      // [rows][SC_TAIL]: the row's newest keys, unfiltered (see FilterArgs::tail)
 };
 
 // ------------------------------------------------------------------------------------------
@@ -730,7 +730,7 @@ __device__ __forceinline__ float packed_lower_sel(uint32_t S, float K0m, float v
 constexpr int XS_KEYS = 8;                        // keys per warp and batch
 constexpr int XS_TILE = 4 * 33;                   // floats per warp
 constexpr int XS_TAB = 32 * 256;                  // floats of one row's table
-static_assert((2 * BAND_MAX + XS_TAB + SEL_WARPS * XS_TILE) * 4 <= SEL_CAP * 4, "band arrays, table and tiles share cand_aux");
+static_assert((2 * BAND_MAX + XS_TAB + SEL_WARPS * XS_TILE) * 4 <= SEL_CAP * 4, "band arrays, table and tiles share cand_key");
 __device__ __forceinline__ void exact_scores_like_scorer(const float* tab_s, const uint8_t* __restrict__ cg,
                                                          const __half* __restrict__ vg, const int32_t* band_t,
                                                          int n, float* tile_all, uint32_t* band_e) {
@@ -767,9 +767,9 @@ __device__ __forceinline__ void exact_scores_like_scorer(const float* tab_s, con
     }
 }
 
-// Exact top-Me of a row from its packed candidates (keys = order keys of up_i in cand_key, the
-// packed words in cand_aux, both in index order; hist zero on entry; s_min = smallest S of the row's
-// candidates).  Returns false, with nothing usable written, when the result cannot be proved or
+// Exact top-Me of a row from its packed candidates (the packed words in cand_key, in index order;
+// kmin / kmax = smallest / largest order key of their up_i; hist zero on entry; s_min = smallest S
+// of the row's candidates).  Returns false, with nothing usable written, when the result cannot be proved or
 // held on chip; the caller then rescans the row.
 //
 // One histogram of the up_i finds the bin that holds the Me-th largest; its upper edge UB bounds
@@ -790,13 +790,18 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
     const uint32_t range = kmax - kmin;
     const int bits = range == 0 ? 0 : 32 - __clz(range);
     const int shift = max(0, bits - 12);
+    auto vn_of = [](uint32_t x) { return __half2float(__ushort_as_half((unsigned short)(x & 0x7fffu))); };
     for (int base = 0; base < n; base += SEL_THREADS) {
         const int i = base + tid;
-        const uint32_t k = i < n ? s.cand_key[i] : kmin;
+        uint32_t k = kmin;
+        if (i < n) {
+            const uint32_t x = s.cand_key[i];
+            k = order_key(packed_upper_sel(x >> 15, K0 + 33.0f, vn_of(x)));
+        }
         warp_hist_add(s.hist, (k - kmin) >> shift, i < n);
     }
     // the row's probabilities [L][R] (32 KiB), requested now, stored to shared memory once the
-    // classification below has freed cand_aux
+    // classification below has freed cand_key
     float4 tab_r[XS_TAB / 4 / SEL_THREADS];
 #pragma unroll
     for (int u = 0; u < XS_TAB / 4 / SEL_THREADS; ++u)
@@ -818,9 +823,9 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
     uint32_t cls_bits = 0;
     int n_sure = 0, n_band = 0;
     for (int i = i0; i < i1; ++i) {
-        const float up = order_key_inverse(s.cand_key[i]);
-        const uint32_t x = s.cand_aux[i];
-        const float lo = packed_lower_sel(x >> 15, K0 - 1.0f, __half2float(__ushort_as_half((unsigned short)(x & 0x7fffu))));
+        const uint32_t x = s.cand_key[i];
+        const float up = packed_upper_sel(x >> 15, K0 + 33.0f, vn_of(x));
+        const float lo = packed_lower_sel(x >> 15, K0 - 1.0f, vn_of(x));
         const uint32_t cls = lo > UB ? 1u : (up >= LB ? 2u : 0u);
         cls_bits |= cls << (2 * (i - i0));
         n_sure += cls == 1u;
@@ -835,10 +840,10 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
         if (tot_band > BAND_DIRECT) atomicAdd(stats + 2, 1);
     }
     if (tot_band > BAND_MAX || want < 0 || want > tot_band) return false;
-    // every read of cand_aux happened before the scan's barriers: its space now holds the band
-    uint32_t* band_e = s.cand_aux;                                     // [BAND_MAX] exact order keys
-    int32_t* band_t = reinterpret_cast<int32_t*>(s.cand_aux + BAND_MAX);   // [BAND_MAX] key index
-    float* tab_s = reinterpret_cast<float*>(s.cand_aux + 2 * BAND_MAX);    // [L][256] this row's probabilities
+    // every read of cand_key happened before the scan's barriers: its space now holds the band
+    uint32_t* band_e = s.cand_key;                                     // [BAND_MAX] exact order keys
+    int32_t* band_t = reinterpret_cast<int32_t*>(s.cand_key + BAND_MAX);   // [BAND_MAX] key index
+    float* tab_s = reinterpret_cast<float*>(s.cand_key + 2 * BAND_MAX);    // [L][256] this row's probabilities
 #pragma unroll
     for (int u = 0; u < XS_TAB / 4 / SEL_THREADS; ++u)
         reinterpret_cast<float4*>(tab_s)[u * SEL_THREADS + tid] = tab_r[u];
@@ -899,6 +904,10 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
     return true;
 }
 
+static_assert(SC_TAIL <= SEL_THREADS, "one tail entry per thread in the gather");
+
+// PACKED: the candidates are packed (S, ||v||) words (score_packed_kernel), else fp32 scores.
+template <bool PACKED>
 __global__ void __launch_bounds__(SEL_THREADS, 1)
 select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev, int64_t M,
                    int sink_in, int window_in, int sorted, int32_t* __restrict__ list,
@@ -918,7 +927,7 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
     const int64_t last_cta = ((int64_t)(g + 1) * a.Tslots - 1) / a.per_cta;
     const int n_runs = (int)(last_cta - first_cta + 1) * SC_WARPS;      // <= 1024
     const int32_t* cnt = a.cnt + row * a.chunks_max * SC_WARPS;
-    const bool packed = a.qpar != nullptr;
+    constexpr bool packed = PACKED;
     pdl_launch_dependents();
     pdl_wait();                               // the runs, their lengths and the cuts come from the scorer
     const float K0 = packed ? __ldcg(a.qpar + g) : 0.f;
@@ -930,11 +939,10 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
             s_min = min(s_min, e.x >> 15);
             const float vn = __half2float(__ushort_as_half((unsigned short)(e.x & 0x7fffu)));
             k = order_key(packed_upper_sel(e.x >> 15, K0 + 33.0f, vn));
-            s.cand_aux[i] = e.x;
         } else {
             k = order_key(__uint_as_float(e.x));
         }
-        s.cand_key[i] = k;
+        s.cand_key[i] = packed ? e.x : k;
         s.cand_idx[i] = (int32_t)e.y;
         kmin = min(kmin, k);
         kmax = max(kmax, k);
@@ -971,6 +979,11 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
         const int off = scan.excl(c, total, s);        // two barriers: the flags above are visible after it
         const bool any_over = s.thr_bin != 0;
         const uint32_t chi = s.red_hi[0];
+        // the row's newest keys follow the runs: all of them, in index order (they have the largest indices)
+        const int n_tail = min(SC_TAIL, T);
+        const int total_runs = total;
+        const uint2* tail = a.tail + row * SC_TAIL;
+        total += n_tail;
         if (!any_over && total >= Me && total <= SEL_CAP) {
             // ---- gather: run offsets to shared memory, then one candidate per thread and step
             // (its run found by binary search), all loads independent
@@ -983,7 +996,8 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                 const uint2* cand = a.cand + row * a.chunks_max * SC_WARPS * a.cap_w;
                 // four candidates per thread and pass: the searches first, then the four loads in
                 // flight together
-                for (int base = 0; base < total; base += 4 * SEL_THREADS) {
+                const uint2 e_tail = tid < n_tail ? __ldcg(tail + tid) : make_uint2(0u, 0u);   // SC_TAIL <= SEL_THREADS
+                for (int base = 0; base < total_runs; base += 4 * SEL_THREADS) {
                     uint2 e[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -994,14 +1008,15 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                             if (run_off[mid] <= i) lo = mid; else hi = mid - 1;
                         }
                         e[u] = make_uint2(0u, 0u);
-                        if (i < total) e[u] = __ldcg(cand + (size_t)lo * a.cap_w + (i - run_off[lo]));
+                        if (i < total_runs) e[u] = __ldcg(cand + (size_t)lo * a.cap_w + (i - run_off[lo]));
                     }
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const int i = base + u * SEL_THREADS + tid;
-                        if (i < total) put(i, e[u], kmin, kmax);
+                        if (i < total_runs) put(i, e[u], kmin, kmax);
                     }
                 }
+                if (tid < n_tail) put(total_runs + tid, e_tail, kmin, kmax);
             } else {
                 // nearly full buffer: one warp per run
                 if (tid < n_runs) {
@@ -1017,6 +1032,7 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                         put(o + i, __ldcg(src + i), kmin, kmax);
                     }
                 }
+                if (tid < n_tail) put(total_runs + tid, __ldcg(tail + tid), kmin, kmax);
                 __syncthreads();
                 for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
             }
@@ -1038,7 +1054,11 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
         }
         if (!exact) {
             // ---- rescore this row (tables added in the scorer's order), then the full-row select
-            if (tid == 0) atomicAdd(a.n_fallback, 1);
+            if (tid == 0) {
+                atomicAdd(a.n_fallback, 1);
+                // why: a run overflowed / too few or too many candidates / result not provable on the candidates
+                atomicAdd(a.n_fallback + (any_over ? 3 : ((total < Me || total > SEL_CAP) ? 4 : 5)), 1);
+            }
             __syncthreads();
             float* tab = reinterpret_cast<float*>(s.cand_key);           // [L][R] of this head
             const float* lut_g = a.lut + (size_t)g * a.R * a.L * a.ht;
@@ -1127,13 +1147,14 @@ int launch_select_candidates(const float* lut, const uint8_t* codes, const uint1
     a.Tcap = Tcap;
     a.qpar = qpar;
     a.probs = probs;
+    a.tail = reinterpret_cast<const uint2*>(ws + lay.tail);
     if ((size_t)L * R * 4 > sizeof(uint32_t) * SEL_CAP)
         return fail(SK_ERR_UNSUPPORTED, "fused score+select: L*R too large for the rescoring table");
     const size_t smem = sizeof(SelShared);
-    cudaError_t e = cudaFuncSetAttribute(select_cand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    auto kern = qpar != nullptr ? select_cand_kernel<true> : select_cand_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "select_cand_kernel smem attribute: %s", cudaGetErrorString(e));
-    e = launch_chained(select_cand_kernel, dim3((unsigned)rows), dim3(SEL_THREADS), smem, st, a, T, T_dev, M, sink,
+    e = launch_chained(kern, dim3((unsigned)rows), dim3(SEL_THREADS), smem, st, a, T, T_dev, M, sink,
                        window, sorted, list, list_row_stride, list_len);
     if (e != cudaSuccess) return fail(SK_ERR_CUDA, "select_cand_kernel: %s", cudaGetErrorString(e));
     return check_launch("select_cand_kernel");

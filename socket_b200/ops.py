@@ -469,5 +469,6 @@ class DecodeStep:
         large enough to be ranked by the radix pass.  Synchronises."""
         if self._rescored_off < 0:
             return None
-        c = self.workspace[self._rescored_off:self._rescored_off + 12].view(torch.int32).tolist()
-        return {"rescored_rows": c[0], "bracket_keys": c[1], "bracket_rows_radix": c[2]}
+        c = self.workspace[self._rescored_off:self._rescored_off + 24].view(torch.int32).tolist()
+        return {"rescored_rows": c[0], "bracket_keys": c[1], "bracket_rows_radix": c[2],
+                "rescored_run_overflow": c[3], "rescored_candidate_count": c[4], "rescored_unproved": c[5]}

@@ -663,8 +663,23 @@ def test_fused_score_select_falls_back_exactly_on_hostile_rows():
     n2 = _fused_vs_two_step(1, 8, 2, T, 1024, 4, 4, v_norm=block.to(torch.float16).expand(1, 2, T), seed=2)
     flat = torch.ones(1, 2, T, dtype=torch.float16)
     codes_equal = _fused_vs_two_step(1, 8, 2, T, 256, 0, 0, v_norm=flat, seed=3)
-    assert n1 + n2 > 0               # at least the hostile layouts went through the rescoring path
-    assert codes_equal >= 0
+    # a ramp and a block of winners no longer defeat the cut (it comes from a sample of the whole
+    # row); whichever rows still take the rescoring path, the lists above were exact
+    assert n1 >= 0 and n2 >= 0 and codes_equal >= 0
+
+
+@pytest.mark.parametrize("B,H,Hkv,T,M", [(1, 32, 8, 131072, 2048), (4, 32, 8, 131072, 2048), (1, 32, 8, 32768, 1024)])
+def test_fused_score_select_recent_keys_scoring_high_stay_on_the_candidate_path(B, H, Hkv, T, M):
+    # the few hundred keys just before the query score far above the rest, as they do in a real model
+    # (rotary embedding, local context), on top of a mild growth over the whole row.  The newest keys
+    # are kept unfiltered and the cut comes from a sample of the whole row, so no run overflows and no
+    # chunk cuts above the k-th score
+    w = torch.linspace(0.0, 1.0, T)
+    vn = 8.0 * (1.0 + 0.04 * w)                              # about one standard deviation of the scores
+    vn[-700:] *= 3.0
+    vn[:40] *= 3.0                                           # and a few "sink" keys at the start
+    vn = vn.to(torch.float16).expand(B, Hkv, T)
+    assert _fused_vs_two_step(B, H, Hkv, T, M, 64, 256, v_norm=vn, seed=T + B) == 0
 
 
 @pytest.mark.parametrize("T", [131072 + 55, 131072 + 105, 131072 - 1, 130000])
@@ -727,7 +742,7 @@ def test_fused_score_select_long_runs():
     block = torch.ones(T)
     block[60000:66000] = 50.0
     n2 = _fused_vs_two_step(1, 8, 2, T, 1024, 4, 4, v_norm=block.to(torch.float16).expand(1, 2, T), seed=13)
-    assert n1 + n2 > 0
+    assert n1 >= 0 and n2 > 0        # 6000 winners in a row overflow their runs: the rescoring path ran, exactly
     # tiny and huge weights side by side: bounds in the half-precision subnormal range and near its top
     g = torch.Generator().manual_seed(14)
     mixed = torch.where(torch.rand(1, 2, T, generator=g) < 0.5, torch.full((1, 2, T), 3e-5),
