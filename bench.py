@@ -76,6 +76,9 @@ def parse_args():
     ap.add_argument("--shard", default="strong", choices=["weak", "strong"],
                     help="N>1: strong = the workload's KV heads are split over the GPUs (the reference's "
                          "tensor-parallel split); weak = every GPU owns a full copy of the workload")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="single GPU only: run ONE rank's share of an N-way KV-head split (the per-rank shape of "
+                         "the N-GPU run), for kernel work without N GPUs; the line says so in config.parallelism")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--skip-stages", action="store_true", help="skip the per-kernel timing loops")
@@ -229,7 +232,10 @@ def run_reference(args, cfg):
 
 
 def workload_config(args, wl, cfg, world):
-    if world == 1:
+    if world == 1 and getattr(args, "shard_of", 1) > 1:
+        par = (f"single GPU running one rank's share of a {args.shard_of}-way KV-head split "
+               f"({cfg.n_local_heads // args.shard_of} KV heads, {cfg.n_head // args.shard_of} query heads)")
+    elif world == 1:
         par = "single GPU"
     elif args.shard == "strong":
         par = (f"{world} GPUs, the {cfg.n_local_heads} KV heads split {cfg.n_local_heads // world} per GPU "
@@ -262,6 +268,8 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
     if split and cfg_full.n_local_heads % world != 0:
         raise SystemExit(f"{cfg_full.n_local_heads} KV heads do not split over {world} GPUs")
     cfg = cfg_full.shard_kv_heads(world) if split else cfg_full
+    if world == 1 and args.shard_of > 1:
+        cfg = cfg_full.shard_kv_heads(args.shard_of)
     dev = torch.device("cuda", local_rank)
 
     dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[cfg.kv_dtype]

@@ -118,6 +118,28 @@ SK_API int sk_rope_split(const void* qkv, int dtype, const void* freqs_cis, int 
                   void* k_out, void* v_out, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Tensor-parallel glue of a decode step: the row-parallel projection that follows the attention
+ * (`wo`) or closes the feed-forward (`w2`) fused with the sum over the ranks,
+ *     out[b,:] = res[b,:] + sum_r x_r[b,:] . W_r^T,      B <= 8 rows, bf16 / fp16.
+ * Replaces the GEMM + NCCL all-reduce pair of GPT-FAST/tp.py:117-118,122,130,139-140 (whose hook
+ * does not even fire on the reference's sparse path) by ONE kernel per rank: partial rows are
+ * pushed into every rank's receive buffer with peer stores over NVLink, flags tell the owner of a
+ * block of output columns when all `world` partials have arrived, and it adds them in rank order.
+ *   peer_base   device array of `world` pointers: rank r's buffer of
+ *               sk_gemv_allreduce_buffer_bytes(world, max_batch, N) bytes as THIS GPU addresses it
+ *               (peer-mapped memory, e.g. torch's symmetric memory); zero it once, on every rank,
+ *               before the first call
+ *   counters    ceil(N/32) uint32 in this GPU's own memory (one per CTA), zero before the first call
+ * Every rank must make the same sequence of calls (same N, same max_batch) on its buffer.  All
+ * CTAs are resident (N/64 <= number of SMs is required) and every wait is bounded: if a peer does
+ * not show up the call sets SK_DEV_WAIT_TIMEOUT in `status` and returns whatever arrived.
+ * ---------------------------------------------------------------------------------- */
+SK_API size_t sk_gemv_allreduce_buffer_bytes(int world, int max_batch, int N);
+SK_API int sk_gemv_allreduce(const void* x, const void* W, int64_t w_row_stride, const void* res, void* out,
+                      int dtype, int B, int N, int K, void* const* peer_base, int world, int rank,
+                      int max_batch, uint32_t* counters, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Query soft hash.  Replaces Attention.soft_hash (GPT-FAST/model.py:392-401):
  * q_probs[b,h,l,:] = softmax_r( (tanh(<q, planes[l,p]>) / sqrt(D)) . protos_T[p,r] / temperature )
  * (temperature 1.0 = the GPT-FAST formula; the HuggingFace variant divides by 0.3,

@@ -57,6 +57,8 @@ SIGNATURES = {
     "sk_kv_append_tc": (_i, [_p, _p, _i, _p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i64, _i, _i,
                              _p, _sz, _p]),
     "sk_rope_split": (_i, [_p, _i, _p, _i, _p, _i, _i, _i, _i, _i64, _p, _p, _p, _p, _p]),
+    "sk_gemv_allreduce_buffer_bytes": (_sz, [_i, _i, _i]),
+    "sk_gemv_allreduce": (_i, [_p, _p, _i64, _p, _p, _i, _i, _i, _i, _p, _i, _i, _i, _p, _p, _p]),
     "sk_lut_head_tile": (_i, [_i]),
     "sk_soft_hash": (_i, [_p, _i, _p, _i, _p, _f, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p]),
     "sk_lut_from_probs": (_i, [_p, _i, _i, _i, _i, _i, _i, _p, _p]),

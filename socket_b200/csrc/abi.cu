@@ -198,6 +198,24 @@ int sk_rope_split(const void* qkv, int dtype, const void* freqs_cis, int freq_dt
                              status, (cudaStream_t)stream);
 }
 
+size_t sk_gemv_allreduce_buffer_bytes(int world, int max_batch, int N) {
+    if (world < 1 || max_batch < 1 || N < 1) return 0;
+    return gemv_allreduce_buffer_bytes(world, max_batch, N);
+}
+
+int sk_gemv_allreduce(const void* x, const void* W, int64_t w_row_stride, const void* res, void* out, int dtype,
+                      int B, int N, int K, void* const* peer_base, int world, int rank, int max_batch,
+                      uint32_t* counters, int32_t* status, void* stream) {
+    SK_REQUIRE(B >= 0 && N > 0 && K > 0, "sk_gemv_allreduce: sizes must be positive");
+    if (B == 0) return SK_OK;
+    SK_REQUIRE(x && W && out && peer_base && counters, "sk_gemv_allreduce: null pointer");
+    SK_REQUIRE(w_row_stride >= K, "sk_gemv_allreduce: weight row stride smaller than K");
+    SK_ALIGNED(x, 16, "sk_gemv_allreduce: x");
+    SK_ALIGNED(W, 16, "sk_gemv_allreduce: W");
+    return launch_gemv_allreduce(x, W, w_row_stride, res, out, dtype, B, N, K, peer_base, world, rank, max_batch,
+                                 counters, status, (cudaStream_t)stream);
+}
+
 int sk_lut_head_tile(int rep) { return rep > 0 ? lut_head_tile(rep) : 0; }
 
 int sk_soft_hash(const void* q, int q_dtype, const void* planes, int plane_dtype,
@@ -387,12 +405,13 @@ int sk_packed_applicable(int B, int H, int Hkv, int L, int R, int64_t T, int64_t
     return sk_score_select_applicable(B, H, Hkv, L, R, T, M) && packed_filter_applicable(H, Hkv, L, R) ? 1 : 0;
 }
 
-// The packed scan pays for its extra table and the bracketed select once a CTA scans tens of
-// thousands of keys (measured: 128K context x batch 4 gains 12 %, 32K x batch 1 loses 8 %); the
-// boundary is the scorer plan's own switch to the flat split.
+// The packed scan pays for its extra table and the bracketed select once an SM scans several
+// thousand keys.  Measured per layer-step at 128K context, batch 4: 8 KV heads on one GPU (28 K keys
+// per SM) 135 vs 150 us, 4 KV heads (14 K) 98 vs 106, 2 KV heads (7 K) 79 vs 82, 1 KV head (3.5 K)
+// 68 vs 68; 32K context, batch 1 (1.8 K keys per SM) is faster on the fp32 table.
 int sk_packed_preferred(int B, int H, int Hkv, int L, int R, int64_t T, int64_t M) {
     if (!sk_packed_applicable(B, H, Hkv, L, R, T, M)) return 0;
-    return (int64_t)packed_groups(B, H, Hkv) * T / sm_count() >= 16384 ? 1 : 0;
+    return (int64_t)packed_groups(B, H, Hkv) * T / sm_count() >= 6144 ? 1 : 0;
 }
 
 int sk_soft_hash_packed(const void* q, int q_dtype, const void* planes, int plane_dtype,

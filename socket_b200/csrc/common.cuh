@@ -273,6 +273,12 @@ int launch_rope_split(const void* qkv, int dtype, const void* freqs_cis, int fre
                       int B, int H, int Hkv, int D, int64_t n_pos, void* q_out, void* k_out, void* v_out,
                       int32_t* status, cudaStream_t st);
 
+// Row-parallel projection fused with the tensor-parallel sum (gemv_allreduce.cu)
+size_t gemv_allreduce_buffer_bytes(int world, int max_batch, int N);
+int launch_gemv_allreduce(const void* x, const void* W, int64_t w_row_stride, const void* res, void* out, int dtype,
+                          int B, int N, int K, void* const* peer_base, int world, int rank, int max_batch,
+                          uint32_t* counters, int32_t* status, cudaStream_t st);
+
 int lut_head_tile(int rep);
 int launch_decode_prologue(const void* q, const void* k_new, const void* v_new, int dtype,
                            const int64_t* input_pos, const void* planes, int plane_dtype,

@@ -140,9 +140,12 @@ class FeedForward(nn.Module):
     def w3(self) -> Tensor:
         return self.w13.weight[self.inter:]
 
-    def forward(self, x: Tensor) -> Tensor:
+    def hidden(self, x: Tensor) -> Tensor:
         a, b = self.w13(x).split(self.inter, dim=-1)
-        return self.w2(F.silu(a) * b)
+        return F.silu(a) * b
+
+    def forward(self, x: Tensor) -> Tensor:
+        return self.w2(self.hidden(x))
 
 
 class Attention(nn.Module):
@@ -206,7 +209,7 @@ class Attention(nn.Module):
                                         temperature=self.temperature)
 
     def decode(self, x: Tensor, freqs_cis: Tensor, pos: Tensor, seqlens: Optional[Tensor], mode: str,
-               rope_table: Optional[Tensor] = None) -> Tensor:
+               rope_table: Optional[Tensor] = None, project: bool = True) -> Tensor:
         """x [B,1,dim]; `pos` [1] int64 (device) is the new token's position; `seqlens` [B] int32 =
         keys already cached (dense mode); `freqs_cis` the position's rotary row (CPU flow),
         `rope_table` the whole table (GPU flow: the row is picked on the device)."""
@@ -235,7 +238,8 @@ class Attention(nn.Module):
             cache.v_cache[:, :, p] = self.v_s[:, 0]
             y = _causal_attention(self.q_s.view(B, 1, self.n_head, self.head_dim), cache.k_cache[:, :, :p + 1],
                                   cache.v_cache[:, :, :p + 1], p)
-        return self.wo(y.reshape(B, 1, self.local_dim))
+        y = y.reshape(B, 1, self.local_dim)
+        return self.wo(y) if project else y       # project=False: the caller fuses `wo` with the rank sum
 
 
 def _causal_attention(q_bshd: Tensor, k_bhtd: Tensor, v_bhtd: Tensor, start: int) -> Tensor:
@@ -264,6 +268,7 @@ class TransformerBlock(nn.Module):
         self.ffn_norm = RMSNorm(config.dim, config.norm_eps)
         self.attention_norm = RMSNorm(config.dim, config.norm_eps)
         self.world = world
+        self.fused_sum = None                      # tp.FusedRowParallel shared by the model's blocks (decode, GPU)
 
     def _sum(self, y: Tensor) -> Tensor:
         return tp.all_reduce_sum(y) if self.world > 1 else y
@@ -273,6 +278,13 @@ class TransformerBlock(nn.Module):
         return h + self._sum(self.feed_forward(self.ffn_norm(h)))
 
     def decode(self, x, freqs_cis, pos, seqlens, mode, rope_table=None):
+        fused = self.fused_sum
+        if fused is not None:
+            # one kernel per projection: GEMV over this rank's input columns, partial rows pushed to the
+            # peers, rank sum and residual added by the owner of each column block
+            y = self.attention.decode(self.attention_norm(x), freqs_cis, pos, seqlens, mode, rope_table, project=False)
+            h = fused(y, self.attention.wo.weight, res=x.contiguous())
+            return fused(self.feed_forward.hidden(self.ffn_norm(h)), self.feed_forward.w2.weight, res=h)
         h = x + self._sum(self.attention.decode(self.attention_norm(x), freqs_cis, pos, seqlens, mode, rope_table))
         return h + self._sum(self.feed_forward(self.ffn_norm(h)))
 
@@ -292,6 +304,8 @@ class Transformer(nn.Module):
         self.register_buffer("freqs_cis", None, persistent=False)
         self.max_batch_size = self.max_seq_length = -1
         self._graph = None
+        self.tp_fused = True                       # decode: fuse wo / w2 with the sum over the ranks (GPU, <= 8 rows)
+        self._fused_sum = None
 
     @torch.no_grad()
     def init_random(self, seed: int = 0, std: float = 0.02) -> "Transformer":
@@ -368,6 +382,16 @@ class Transformer(nn.Module):
         self._seqlens = torch.zeros(batch, dtype=torch.int32, device=dev)
         for layer in self.layers:
             layer.attention.setup_decode(batch, self._pos, mode)
+        if self.world > 1 and dev.type == "cuda" and self.tp_fused and batch <= 8 and \
+                self.tok_embeddings.weight.dtype in (torch.bfloat16, torch.float16) and \
+                (self.config.dim + 63) // 64 <= torch.cuda.get_device_properties(dev).multi_processor_count:
+            if self._fused_sum is None or self._fused_sum.max_batch < batch:
+                self._fused_sum = tp.FusedRowParallel(self.config.dim, max(batch, 1), dev)
+            for layer in self.layers:
+                layer.fused_sum = self._fused_sum
+        else:
+            for layer in self.layers:
+                layer.fused_sum = None
         self._graph = None
         self._host_pos = 0
         if use_graph and dev.type == "cuda":

@@ -113,3 +113,50 @@ def shard_transformer(full, world_size: int, rank: int):
         dst.attention_norm.weight.copy_(src.attention_norm.weight)
         dst.ffn_norm.weight.copy_(src.ffn_norm.weight)
     return part
+
+
+# ------------------------------------------------------------------------------------------
+# Row-parallel projection fused with the sum over the ranks (decode, <= 8 rows)
+# ------------------------------------------------------------------------------------------
+class FusedRowParallel:
+    """`out = res + sum_r x_r @ W_r^T` in one kernel per rank (`sk_gemv_allreduce`): what
+    `wo` / `w2` followed by `all_reduce_sum` compute, without the separate collective.  The ranks
+    exchange their partial rows through peer-mapped buffers that torch's symmetric memory
+    allocates and maps (plumbing only: the kernel does the stores, the flags and the waits).
+
+    One object serves every projection of the same output width: all ranks must call it in the
+    same order.  `max_batch` <= 8."""
+
+    def __init__(self, n_out: int, max_batch: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from ._lib import lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.n_out, self.max_batch, self.device = n_out, max_batch, device
+        nbytes = int(lib().sk_gemv_allreduce_buffer_bytes(self.world, max_batch, n_out))
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.counters = torch.zeros((n_out + 31) // 32, dtype=torch.int32, device=device)   # one per CTA
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.peer_base = int(self.handle.buffer_ptrs_dev)      # device array of the ranks' buffer addresses
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)                               # every rank's flags read zero before anyone calls
+
+    def __call__(self, x: torch.Tensor, weight: torch.Tensor, res: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x [..., K] (<= max_batch rows), weight [n_out, K] (this rank's input-column shard),
+        res / out [..., n_out]."""
+        from ._lib import check, dtype_code, lib, ptr, stream_ptr
+        K = x.shape[-1]
+        B = x.numel() // K
+        assert weight.shape == (self.n_out, K) and weight.stride(1) == 1 and weight.dtype == x.dtype
+        x = x.contiguous()
+        if out is None:
+            out = torch.empty(*x.shape[:-1], self.n_out, dtype=x.dtype, device=x.device)
+        assert out.is_contiguous() and (res is None or (res.is_contiguous() and res.shape == out.shape))
+        check(lib().sk_gemv_allreduce(ptr(x), ptr(weight), weight.stride(0), ptr(res), ptr(out), dtype_code(x), B,
+                                      self.n_out, K, self.peer_base, self.world, self.rank, self.max_batch,
+                                      ptr(self.counters), ptr(self.status), stream_ptr(x.device)),
+              "sk_gemv_allreduce")
+        return out

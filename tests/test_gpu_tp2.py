@@ -1,0 +1,120 @@
+"""Two-GPU checks of the tensor-parallel glue (needs a box with at least two GPUs; skipped
+otherwise): the fused projection + rank sum (`sk_gemv_allreduce` through `tp.FusedRowParallel`)
+against the GEMM + NCCL all-reduce it replaces, and a tensor-parallel model whose two shards
+reproduce the single-GPU model's greedy tokens with the sparse decode step in every layer."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _fused_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    from socket_b200 import tp
+    tp.maybe_init_dist("nccl")
+    dev = torch.device("cuda", rank)
+    ok = True
+    worst = 0.0
+    for (B, N, K) in [(1, 4096, 2048), (4, 4096, 7168), (8, 1024, 512), (3, 8192, 1024)]:
+        fused = tp.FusedRowParallel(N, 8, dev)
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        W = (torch.randn(N, K, generator=g, device=dev) * 0.05).bfloat16()
+        for call in range(5):                              # consecutive calls: both receive slots, growing call numbers
+            x = torch.randn(B, 1, K, generator=g, device=dev).bfloat16()
+            res = torch.randn(B, 1, N, generator=g, device=dev).bfloat16()
+            got = fused(x, W, res=res if call % 2 == 0 else None)
+            part = (x.float() @ W.float().t())
+            dist.all_reduce(part)
+            want = part + (res.float() if call % 2 == 0 else 0)
+            err = (got.float() - want).abs().max().item()
+            worst = max(worst, err / max(1.0, want.abs().max().item()))
+            # every rank must hold the same bits
+            peers = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(peers, got)
+            ok = ok and all(torch.equal(p, peers[0]) for p in peers)
+        # replayed from a CUDA graph: the call counters live on the device
+        x = torch.randn(B, 1, K, generator=g, device=dev).bfloat16()
+        out = torch.empty(B, 1, N, dtype=torch.bfloat16, device=dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            fused(x, W, out=out)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fused(x, W, out=out)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        for _ in range(3):
+            x.normal_(generator=g)
+            graph.replay()
+            torch.cuda.synchronize()
+            part = (x.float() @ W.float().t())
+            dist.all_reduce(part)
+            worst = max(worst, ((out.float() - part).abs().max() / max(1.0, part.abs().max().item())).item())
+        ok = ok and int(fused.status) == 0
+    if rank == 0:
+        ret["ok"], ret["worst"] = ok, worst
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_projection_and_rank_sum_equals_gemm_plus_all_reduce():
+    _need_two_gpus()
+    ret = mp.Manager().dict()
+    mp.spawn(_fused_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert ret["ok"]
+    assert ret["worst"] <= 8e-3            # bf16 output rounding of sums of a few units
+
+
+def _model_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    from socket_b200 import tp
+    from socket_b200.model import ModelArgs, Transformer, generate
+    tp.maybe_init_dist("nccl")
+    dev = torch.device("cuda", rank)
+    cfg = ModelArgs.from_name("tiny", n_layer=2)
+    full = Transformer(cfg).to(device=dev, dtype=torch.bfloat16).init_random(seed=9, std=0.05)
+    part = tp.shard_transformer(full, world, rank)
+    prompt = torch.randint(0, cfg.vocab_size, (2, 600), generator=torch.Generator().manual_seed(5))
+    outs = {}
+    for fused in (True, False):
+        part.tp_fused = fused
+        part.max_seq_length = -1
+        seq, _ = generate(part, prompt, 10, mode="sparse", use_graph=True)
+        outs[fused] = seq.cpu()
+    status = sum(int(l.attention.kv_cache.status) for l in part.layers)
+    if rank == 0:
+        want, _ = generate(full, prompt, 10, mode="sparse", use_graph=True)
+        ret["fused"], ret["nccl"], ret["single"], ret["status"] = outs[True], outs[False], want.cpu(), status
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_shards_decode_like_the_single_gpu_model():
+    _need_two_gpus()
+    ret = mp.Manager().dict()
+    mp.spawn(_model_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert ret["status"] == 0
+    # the rank sum rounds differently from the single-GPU GEMM (and the fused kernel sums in fp32), so
+    # greedy tokens can part ways late in a random-weight model; the prompt and the first tokens agree
+    for name in ("fused", "nccl"):
+        assert torch.equal(ret[name][:, :600], ret["single"][:, :600])
+        assert (ret[name][:, 600:603] == ret["single"][:, 600:603]).float().mean() >= 0.8, name
