@@ -122,9 +122,10 @@ SK_API int sk_rope_split(const void* qkv, int dtype, const void* freqs_cis, int 
  * (`wo`) or closes the feed-forward (`w2`) fused with the sum over the ranks,
  *     out[b,:] = res[b,:] + sum_r x_r[b,:] . W_r^T,      B <= 8 rows, bf16 / fp16.
  * Replaces the GEMM + NCCL all-reduce pair of GPT-FAST/tp.py:117-118,122,130,139-140 (whose hook
- * does not even fire on the reference's sparse path) by ONE kernel per rank: partial rows are
- * pushed into every rank's receive buffer with peer stores over NVLink, flags tell the owner of a
- * block of output columns when all `world` partials have arrived, and it adds them in rank order.
+ * does not even fire on the reference's sparse path) by ONE kernel per rank: partial sums are
+ * pushed into every rank's receive buffer with peer stores over NVLink as self-validating 8-byte
+ * words {value, call number}; the owner of a block of output columns polls its buffer until all
+ * `world` partials of this call have arrived and adds them in rank order.
  *   peer_base   device array of `world` pointers: rank r's buffer of
  *               sk_gemv_allreduce_buffer_bytes(world, max_batch, N) bytes as THIS GPU addresses it
  *               (peer-mapped memory, e.g. torch's symmetric memory); zero it once, on every rank,

@@ -10,22 +10,25 @@
 //   1. a CTA owns 32 (64 for wide models) output columns: it streams its rows of W_r once (16-byte
 //      loads, several rows in flight per warp), with x_r
 //      staged in shared memory, and reduces the products per warp;
-//   2. it PUSHES its 32 x B partial sums (fp32) straight into every rank's receive buffer over
-//      NVLink (peer stores, 128-byte rows), fences, and raises a flag in every rank's flag array;
-//   3. it waits until the CTAs with the same index on all ranks have raised theirs - those are the
-//      only producers of the 32 columns it owns - and adds the `world` partial rows, in rank order
-//      (every rank gets the same bits), plus the residual, and writes `out`.
+//   2. it PUSHES its partial sums straight into every rank's receive buffer over NVLink as 8-byte
+//      words {value (fp32), call number}: such a store arrives whole, so the word validates itself
+//      and no fence, flag or second hop is needed (the "low latency" protocol of collective
+//      libraries);
+//   3. it polls its own receive buffer until the words of all `world` ranks for the columns it
+//      owns carry this call's number - the CTAs with the same index on the other ranks are their
+//      only producers - and adds the values in rank order (every rank gets the same bits), plus
+//      the residual, and writes `out`.
 //
 // No CTA waits for a CTA of its own grid, the grid never exceeds the number of SMs (all CTAs are
 // resident), and every wait is bounded: when it runs out the kernel sets SK_DEV_WAIT_TIMEOUT and
 // carries on with whatever has arrived, so a missing peer costs a wrong value, never a hang.
 //
-// Buffers: every rank allocates the same peer-mapped block [receive slots | flags] (host side:
-// torch's symmetric memory; `peer_base[r]` is rank r's block as this GPU addresses it).  Receive
-// slots are double-buffered by call parity: a rank can be at most one call ahead of a peer (it
-// needs that peer's flag of the current call to finish it), so call n+2 never overwrites data a
-// peer still reads for call n.  Flags hold call numbers and only grow; the per-CTA call counter
-// lives in this GPU's own memory, so a CUDA graph can replay the call.
+// Buffers: every rank allocates the same peer-mapped block of receive slots (host side: torch's
+// symmetric memory; `peer_base[r]` is rank r's block as this GPU addresses it).  The slots are
+// double-buffered by call parity: a rank can be at most one call ahead of a peer (it needs that
+// peer's words of the current call to finish it), so call n+2 never overwrites words a peer still
+// reads for call n, and a word left by call n-2 never carries call n's number.  The per-CTA call
+// counter lives in this GPU's own memory, so a CUDA graph can replay the call.
 #include "common.cuh"
 
 namespace sk {
@@ -38,17 +41,13 @@ constexpr int GA_MAXB = 8;
 constexpr int GA_MAX_WORLD = 8;
 constexpr uint32_t GA_WAIT_LIMIT = 1u << 21;   // polls (with a short sleep each) before giving up: ~0.1 s
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// one 8-byte word {value, call number}: written and read whole
+__device__ __forceinline__ void st_word(uint2* p, float v, uint32_t epoch) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ float ld_volatile_f32(const float* p) {
-    float v;
-    asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
+__device__ __forceinline__ uint2 ld_word(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
 
@@ -74,11 +73,11 @@ template <typename T, int GA_COLS>
 __global__ void __launch_bounds__(GA_THREADS, 1)
 gemv_allreduce_kernel(const T* __restrict__ x, const T* __restrict__ W, int64_t w_row_stride,
                       const T* __restrict__ res, T* __restrict__ out, int B, int N, int K,
-                      void* const* __restrict__ peer_base, int world, int rank, size_t flag_off,
+                      void* const* __restrict__ peer_base, int world, int rank,
                       int max_batch, int n_pad, uint32_t* __restrict__ counters, int32_t* status) {
     extern __shared__ __align__(16) char ga_smem[];
     T* x_s = reinterpret_cast<T*>(ga_smem);                                           // [B][K]
-    float* y_s = reinterpret_cast<float*>(ga_smem + (((size_t)B * K * sizeof(T) + 15) & ~(size_t)15));   // [GA_MAXB][GA_COLS]
+    float* y_s = reinterpret_cast<float*>(ga_smem + (((size_t)B * K * sizeof(T) + 15) & ~(size_t)15));   // [GA_MAX_WORLD][GA_MAXB][GA_COLS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int blk = blockIdx.x, n0 = blk * GA_COLS;
     const uint32_t epoch = counters[blk] + 1u;            // this call's number for this CTA, the same on every rank
@@ -96,6 +95,9 @@ gemv_allreduce_kernel(const T* __restrict__ x, const T* __restrict__ W, int64_t 
         for (int rr = 0; rr < RPW; ++rr)
 #pragma unroll
             for (int b = 0; b < GA_MAXB; ++b) acc[rr][b] = 0.f;
+        // (unrolled: several iterations' loads are issued before the first is consumed - the rows are
+        // streamed once and only the bytes in flight hide the memory latency)
+#pragma unroll 4
         for (int c = lane; c < K / 8; c += 32) {
             uint4 wv[RPW];
 #pragma unroll
@@ -133,46 +135,50 @@ gemv_allreduce_kernel(const T* __restrict__ x, const T* __restrict__ W, int64_t 
     }
     __syncthreads();
 
-    // ---- 2. push the partial rows to every rank (this one included), then raise the flags
-    // receive layout of a rank: [slot][source rank][batch row][n_pad] fp32
+    // ---- 2. push the partial rows to every rank (this one included)
+    // receive layout of a rank: [slot][source rank][batch row][n_pad] words
     for (int idx = warp; idx < world * B; idx += GA_WARPS) {
         const int r = idx / B, b = idx - r * B;
-        float* dst = reinterpret_cast<float*>(peer_base[r]) +
+        uint2* dst = reinterpret_cast<uint2*>(peer_base[r]) +
                      (((size_t)slot * world + rank) * max_batch + b) * n_pad + n0;
 #pragma unroll
         for (int l = lane; l < GA_COLS; l += 32)
-            if (n0 + l < N) dst[l] = y_s[b * GA_COLS + l];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < world) {
-        uint32_t* flag = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(peer_base[tid]) + flag_off) +
-                         (size_t)blk * GA_MAX_WORLD + rank;
-        st_release_sys(flag, epoch);
+            if (n0 + l < N) st_word(dst + l, y_s[b * GA_COLS + l], epoch);
     }
 
-    // ---- 3. wait for the same CTA of every rank, add the rows in rank order
-    if (tid < world) {
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(peer_base[rank]) + flag_off) +
-                               (size_t)blk * GA_MAX_WORLD + tid;
-        uint32_t it = 0;
-        while ((int32_t)(ld_acquire_sys(flag) - epoch) < 0) {
-            if (++it >= GA_WAIT_LIMIT) {
-                if (status != nullptr) atomicOr(status, SK_DEV_WAIT_TIMEOUT);
-                break;
+    // ---- 3. collect this CTA's columns from every rank: a thread polls one word at a time
+    const uint2* mine = reinterpret_cast<const uint2*>(peer_base[rank]);
+    float* part_s = y_s;                                  // reused: [world][B][GA_COLS] partial values
+    __syncthreads();                                      // y_s has been read by the pushing warps
+    bool late = false;
+    for (int idx = tid; idx < world * B * GA_COLS; idx += GA_THREADS) {
+        const int l = idx % GA_COLS, rb = idx / GA_COLS;  // rb = r * B + b
+        const int r = rb / B, b = rb - r * B;
+        float v = 0.f;
+        if (n0 + l < N) {
+            const uint2* src = mine + (((size_t)slot * world + r) * max_batch + b) * n_pad + n0 + l;
+            uint2 w = ld_word(src);
+            uint32_t it = 0;
+            while (w.y != epoch) {
+                if (++it >= GA_WAIT_LIMIT) {
+                    late = true;
+                    break;
+                }
+                __nanosleep(20);
+                w = ld_word(src);
             }
-            __nanosleep(40);
+            v = __uint_as_float(w.x);
         }
+        part_s[idx] = v;
     }
+    if (late && status != nullptr) atomicOr(status, SK_DEV_WAIT_TIMEOUT);
     __syncthreads();
-    const float* mine = reinterpret_cast<const float*>(peer_base[rank]);
     for (int idx = tid; idx < B * GA_COLS; idx += GA_THREADS) {
         const int b = idx / GA_COLS, l = idx - b * GA_COLS;
         const int n = n0 + l;
         if (n < N) {
             float s = res != nullptr ? to_f32(res[(size_t)b * N + n]) : 0.f;
-            for (int r = 0; r < world; ++r)
-                s += ld_volatile_f32(mine + (((size_t)slot * world + r) * max_batch + b) * n_pad + n);
+            for (int r = 0; r < world; ++r) s += part_s[(r * B + b) * GA_COLS + l];
             out[(size_t)b * N + n] = from_f32<T>(s);
         }
     }
@@ -187,13 +193,9 @@ static int gemv_allreduce_cols(int N) {
         if ((N + cols - 1) / cols <= sm_count()) return cols;
     return 0;
 }
-size_t gemv_allreduce_flag_offset(int world, int max_batch, int n_pad) {
-    return sk_up256((size_t)2 * world * max_batch * n_pad * sizeof(float));
-}
 size_t gemv_allreduce_buffer_bytes(int world, int max_batch, int N) {
     const int n_pad = (N + GA_MAX_COLS - 1) / GA_MAX_COLS * GA_MAX_COLS;
-    const int grid = n_pad / 32;                                  // room for the finer split
-    return gemv_allreduce_flag_offset(world, max_batch, n_pad) + sk_up256((size_t)grid * GA_MAX_WORLD * sizeof(uint32_t));
+    return sk_up256((size_t)2 * world * max_batch * n_pad * sizeof(uint2));
 }
 
 int launch_gemv_allreduce(const void* x, const void* W, int64_t w_row_stride, const void* res, void* out, int dtype,
@@ -211,17 +213,16 @@ int launch_gemv_allreduce(const void* x, const void* W, int64_t w_row_stride, co
         return fail(SK_ERR_INVALID_ARGUMENT, "sk_gemv_allreduce: world %d / rank %d", world, rank);
     if (K % 8 != 0 || w_row_stride % 8 != 0)
         return fail(SK_ERR_MISALIGNED, "sk_gemv_allreduce: K and the weight row stride must be multiples of 8 elements");
-    const size_t smem = (((size_t)B * K * 2 + 15) & ~(size_t)15) + (size_t)GA_MAXB * GA_MAX_COLS * sizeof(float);
+    const size_t smem = (((size_t)B * K * 2 + 15) & ~(size_t)15) + (size_t)GA_MAX_WORLD * GA_MAXB * GA_MAX_COLS * sizeof(float);
     if (smem > 200 * 1024)
         return fail(SK_ERR_UNSUPPORTED, "sk_gemv_allreduce: %d x %d activations do not fit shared memory", B, K);
-    const size_t flag_off = gemv_allreduce_flag_offset(world, max_batch, n_pad);
 #define SK_GA_LAUNCH(T)                                                                                     \
     do {                                                                                                    \
         auto kern = cols == 32 ? gemv_allreduce_kernel<T, 32> : gemv_allreduce_kernel<T, 64>;               \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return fail(SK_ERR_CUDA, "gemv_allreduce_kernel smem attribute: %s", cudaGetErrorString(e)); \
         kern<<<grid, GA_THREADS, smem, st>>>((const T*)x, (const T*)W, w_row_stride, (const T*)res, (T*)out, B, N, K, \
-                                             peer_base, world, rank, flag_off, max_batch, n_pad, counters, status); \
+                                             peer_base, world, rank, max_batch, n_pad, counters, status); \
         return check_launch("gemv_allreduce_kernel");                                                       \
     } while (0)
     if (dtype == SK_BF16) SK_GA_LAUNCH(__nv_bfloat16);

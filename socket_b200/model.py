@@ -410,6 +410,17 @@ class Transformer(nn.Module):
             self._graph = g
             self._tok.copy_(saved[0]); self._pos.copy_(saved[1]); self._seqlens.copy_(saved[2])
 
+    def release_decode(self) -> None:
+        """Drop the captured graph and the per-layer steps.  Under tensor parallelism call this
+        before `torch.distributed.destroy_process_group()`: a live CUDA graph that holds NCCL
+        kernels keeps the communicator busy and the teardown waits for it."""
+        self._graph = None
+        for layer in self.layers:
+            layer.attention._step = None
+            layer.fused_sum = None
+        if self.tok_embeddings.weight.is_cuda:
+            torch.cuda.synchronize(self.tok_embeddings.weight.device)
+
     @torch.no_grad()
     def start_decode(self, first_token: Tensor, position: int) -> None:
         """`first_token` [B,1] sits at `position` (= number of tokens already cached)."""
