@@ -345,6 +345,14 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     total_ms = float(t.item())
+    if sampler is not None:
+        # a short timed region can end before nvidia-smi's first 200 ms tick: keep the same load
+        # running (untimed) until two samples exist, so the clocks are those under this load
+        t_wait = time.perf_counter()
+        while len(sampler.rows) < 2 and time.perf_counter() - t_wait < 2.0:
+            for _ in range(50):
+                graph.replay()
+            torch.cuda.synchronize()
     clocks = sampler.stop() if sampler is not None else None
     assert int(step.status) == 0, f"device status {int(step.status)}"
     # split: all ranks work on the same B tokens; replicas: every rank has its own B tokens
