@@ -985,54 +985,54 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
         const uint2* tail = a.tail + row * SC_TAIL;
         total += n_tail;
         if (!any_over && total >= Me && total <= SEL_CAP) {
-            // ---- gather: run offsets to shared memory, then one candidate per thread and step
-            // (its run found by binary search), all loads independent
-            int32_t* run_off = s.cand_idx + SEL_CAP - 1024;       // tail of cand_idx, free until total > 15360
+            // ---- gather: G lanes per run (G = the power of two at or above the mean run length, 4 to 32),
+            // four runs per lane group in flight, each with its first 2 G entries: all loads of a pass
+            // are independent and nothing searches.  Run r's (offset | length << 16) comes from shared
+            // memory: the tail of cand_idx while the candidates leave it free, else the histogram bins.
             const bool tail_free = total <= SEL_CAP - 1024;
+            int32_t* meta = tail_free ? s.cand_idx + SEL_CAP - 1024 : reinterpret_cast<int32_t*>(s.hist);
             uint32_t kmin = 0xffffffffu, kmax = 0u;
-            if (tail_free) {
-                if (tid < n_runs) run_off[tid] = off;
-                __syncthreads();
-                const uint2* cand = a.cand + row * a.chunks_max * SC_WARPS * a.cap_w;
-                // four candidates per thread and pass: the searches first, then the four loads in
-                // flight together
-                const uint2 e_tail = tid < n_tail ? __ldcg(tail + tid) : make_uint2(0u, 0u);   // SC_TAIL <= SEL_THREADS
-                for (int base = 0; base < total_runs; base += 4 * SEL_THREADS) {
-                    uint2 e[4];
+            if (tid < n_runs) meta[tid] = off | (c << 16);
+            __syncthreads();
+            const uint2* cand = a.cand + row * a.chunks_max * SC_WARPS * a.cap_w;
+            const uint2 e_tail = tid < n_tail ? __ldcg(tail + tid) : make_uint2(0u, 0u);   // SC_TAIL <= SEL_THREADS
+            int G = 4;
+            while (G < 32 && G * n_runs < total_runs) G <<= 1;
+            const int rpw = 32 / G, sub = lane / G, li = lane - sub * G;
+            const int step_runs = SEL_WARPS * rpw;
+            for (int r0 = warp * rpw + sub; r0 < n_runs; r0 += 4 * step_runs) {
+                uint2 e[4][2];
+                int o[4], n[4];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int i = base + u * SEL_THREADS + tid;
-                        int lo = 0, hi = n_runs - 1;              // last run with run_off <= i
-                        while (lo < hi) {
-                            const int mid = (lo + hi + 1) >> 1;
-                            if (run_off[mid] <= i) lo = mid; else hi = mid - 1;
-                        }
-                        e[u] = make_uint2(0u, 0u);
-                        if (i < total_runs) e[u] = __ldcg(cand + (size_t)lo * a.cap_w + (i - run_off[lo]));
-                    }
+                for (int u = 0; u < 4; ++u) {
+                    const int r = r0 + u * step_runs;
+                    const int m = r < n_runs ? meta[r] : 0;
+                    o[u] = m & 0xffff;
+                    n[u] = m >> 16;
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int i = base + u * SEL_THREADS + tid;
-                        if (i < total_runs) put(i, e[u], kmin, kmax);
+                    for (int k = 0; k < 2; ++k) {
+                        const int i = li + G * k;
+                        e[u][k] = make_uint2(0u, 0u);
+                        if (i < n[u]) e[u][k] = __ldcg(cand + (size_t)r * a.cap_w + i);
                     }
                 }
-                if (tid < n_tail) put(total_runs + tid, e_tail, kmin, kmax);
-            } else {
-                // nearly full buffer: one warp per run
-                if (tid < n_runs) {
-                    s.hist[2 * tid] = (uint32_t)off;
-                    s.hist[2 * tid + 1] = (uint32_t)c;
-                }
-                __syncthreads();
-                const uint2* cand = a.cand + row * a.chunks_max * SC_WARPS * a.cap_w;
-                for (int r = warp; r < n_runs; r += SEL_WARPS) {
-                    const int o = (int)s.hist[2 * r], n = (int)s.hist[2 * r + 1];
-                    const uint2* src = cand + (size_t)r * a.cap_w;
-                    for (int i = lane; i < n; i += 32) {
-                        put(o + i, __ldcg(src + i), kmin, kmax);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int i = li + G * k;
+                        if (i < n[u]) put(o[u] + i, e[u][k], kmin, kmax);
                     }
                 }
-                if (tid < n_tail) put(total_runs + tid, __ldcg(tail + tid), kmin, kmax);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {                      // runs longer than 2 G: rare
+                    const int r = r0 + u * step_runs;
+                    for (int i = li + 2 * G; i < n[u]; i += G)
+                        put(o[u] + i, __ldcg(cand + (size_t)r * a.cap_w + i), kmin, kmax);
+                }
+            }
+            if (tid < n_tail) put(total_runs + tid, e_tail, kmin, kmax);
+            if (!tail_free) {
                 __syncthreads();
                 for (int i = tid; i < SEL_BINS; i += SEL_THREADS) s.hist[i] = 0;
             }
