@@ -13,6 +13,7 @@
 // (max, sum, acc[D]) and takes a ticket; the CTA that draws the last ticket of a row merges
 // the row's partials and writes the output.  No CTA ever waits for another one.
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -92,6 +93,36 @@ __device__ __forceinline__ void cvt8(const __half* p, float (&d)[8]) {
     }
 }
 
+// Dot product of eight 16-bit elements with fp32 accumulation, no conversion instructions: the
+// mixed-precision fma takes both factors in their 16-bit form (the product of two bf16 or fp16
+// numbers is exact in fp32, so the result equals converting first), accumulating in the order
+// element 0..7.
+template <typename KT> struct MixedDot { static constexpr bool ok = false; };
+template <> struct MixedDot<__nv_bfloat16> {
+    static constexpr bool ok = true;
+    static __device__ __forceinline__ float word(uint32_t k, uint32_t q, float d) {
+        asm("{\n\t.reg .b16 kl, kh, ql, qh;\n\t"
+            "mov.b32 {kl, kh}, %1;\n\t"
+            "mov.b32 {ql, qh}, %2;\n\t"
+            "fma.rn.f32.bf16 %0, kl, ql, %0;\n\t"
+            "fma.rn.f32.bf16 %0, kh, qh, %0;\n\t}"
+            : "+f"(d) : "r"(k), "r"(q));
+        return d;
+    }
+};
+template <> struct MixedDot<__half> {
+    static constexpr bool ok = true;
+    static __device__ __forceinline__ float word(uint32_t k, uint32_t q, float d) {
+        asm("{\n\t.reg .b16 kl, kh, ql, qh;\n\t"
+            "mov.b32 {kl, kh}, %1;\n\t"
+            "mov.b32 {ql, qh}, %2;\n\t"
+            "fma.rn.f32.f16 %0, kl, ql, %0;\n\t"
+            "fma.rn.f32.f16 %0, kh, qh, %0;\n\t}"
+            : "+f"(d) : "r"(k), "r"(q));
+        return d;
+    }
+};
+
 template <typename KT> struct DecSmem {
     static constexpr int ROW = DEC_D * (int)sizeof(KT);                 // bytes per K or V row
     static constexpr int STAGE = DEC_G * 2 * ROW;                       // K rows then V rows
@@ -127,11 +158,19 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
     pdl_launch_dependents();
 
     // the query is an input of the whole step, so it can be fetched before the list exists
+    // 16-bit query and keys of one type: the query stays packed and the scale is applied to the
+    // finished dot product; otherwise the query is converted and scaled once
+    constexpr bool MIXED = MixedDot<KT>::ok && std::is_same<QT, KT>::value;
     float qf[8];
-    cvt8(q + (size_t)row * DEC_D + hl * 8, qf);
+    uint4 qw = make_uint4(0u, 0u, 0u, 0u);
     const float qscale = rsqrtf((float)DEC_D) * LOG2E;
+    if constexpr (MIXED) {
+        qw = *reinterpret_cast<const uint4*>(q + (size_t)row * DEC_D + hl * 8);
+    } else {
+        cvt8(q + (size_t)row * DEC_D + hl * 8, qf);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) qf[i] *= qscale;
+        for (int i = 0; i < 8; ++i) qf[i] *= qscale;
+    }
 
     pdl_wait();                               // list, list_len, the live length and the newest K/V row
     // The slice bounds come from max_len alone, so the first two index batches are requested
@@ -230,15 +269,24 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
             ok[j] = si[e] >= 0;
             float d = 0.f;
             if (ok[j]) {
-                float kf[8];
-                cvt8(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8, kf);
+                if constexpr (MIXED) {
+                    const uint4 kw = *reinterpret_cast<const uint4*>(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8);
+                    d = MixedDot<KT>::word(kw.x, qw.x, d);
+                    d = MixedDot<KT>::word(kw.y, qw.y, d);
+                    d = MixedDot<KT>::word(kw.z, qw.z, d);
+                    d = MixedDot<KT>::word(kw.w, qw.w, d);
+                } else {
+                    float kf[8];
+                    cvt8(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8, kf);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kf[i], d);
+                    for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kf[i], d);
+                }
             }
             d += __shfl_xor_sync(FULL, d, 8);
             d += __shfl_xor_sync(FULL, d, 4);
             d += __shfl_xor_sync(FULL, d, 2);
             d += __shfl_xor_sync(FULL, d, 1);
+            if constexpr (MIXED) d *= qscale;
             sc[j] = ok[j] ? d : -INFINITY;
             m_new = fmaxf(m_new, sc[j]);
         }
