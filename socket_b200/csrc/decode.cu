@@ -55,11 +55,9 @@ inline int decode_splits(int64_t rows, int64_t max_len) {
     return (int)s;
 }
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
-                     (uint32_t)__cvta_generic_to_shared(smem_dst)),
-                 "l"(gmem_src)
-                 : "memory");
+// smem_dst: 32-bit shared-window address (converted once per kernel, not per copy)
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -196,6 +194,7 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
     const KT* kb = k_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs;
     const KT* vb = v_cache + (size_t)b * kv_bs + (size_t)kvh * kv_hs;
     char* ring = smem + (size_t)warp * DEC_STAGES * S::STAGE;
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
     int32_t* sidx = sidx_all + warp * DEC_STAGES * DEC_G;
     bool bad_index = false;
 
@@ -226,7 +225,7 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
     auto issue = [&](int s) {
         if (s < n_stage) {
             const int reg = ((s >> 2) & 1) ? idx1 : idx0;
-            char* buf = ring + (s % DEC_STAGES) * S::STAGE;
+            const uint32_t buf = ring_s + (uint32_t)((s % DEC_STAGES) * S::STAGE);
 #pragma unroll
             for (int i = 0; i < COPIES; ++i) {
                 const int c = lane + 32 * i;
@@ -234,8 +233,8 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
                 const int ridx = __shfl_sync(FULL, reg, (s & 3) * DEC_G + r);
                 if (ridx >= 0) {
                     const size_t goff = (size_t)ridx * kv_rs + ch * EPC;
-                    cp_async16(buf + r * S::ROW + ch * 16, kb + goff);
-                    cp_async16(buf + (DEC_G + r) * S::ROW + ch * 16, vb + goff);
+                    cp_async16(buf + (uint32_t)(r * S::ROW + ch * 16), kb + goff);
+                    cp_async16(buf + (uint32_t)((DEC_G + r) * S::ROW + ch * 16), vb + goff);
                 }
             }
             const int mine = __shfl_sync(FULL, reg, (s & 3) * DEC_G + (lane & (DEC_G - 1)));
@@ -260,55 +259,63 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
         __syncwarp();
         const char* buf = ring + (s % DEC_STAGES) * S::STAGE;
         const int32_t* si = sidx + (s % DEC_STAGES) * DEC_G;
-        float sc[DEC_G / 2];
-        int ok[DEC_G / 2];
-        float m_new = m;
-#pragma unroll
-        for (int j = 0; j < DEC_G / 2; ++j) {
-            const int e = 2 * j + hw2;
-            ok[j] = si[e] >= 0;
-            float d = 0.f;
-            if (ok[j]) {
-                if constexpr (MIXED) {
-                    const uint4 kw = *reinterpret_cast<const uint4*>(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8);
-                    d = MixedDot<KT>::word(kw.x, qw.x, d);
-                    d = MixedDot<KT>::word(kw.y, qw.y, d);
-                    d = MixedDot<KT>::word(kw.z, qw.z, d);
-                    d = MixedDot<KT>::word(kw.w, qw.w, d);
-                } else {
-                    float kf[8];
-                    cvt8(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8, kf);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kf[i], d);
-                }
-            }
-            d += __shfl_xor_sync(FULL, d, 8);
-            d += __shfl_xor_sync(FULL, d, 4);
-            d += __shfl_xor_sync(FULL, d, 2);
-            d += __shfl_xor_sync(FULL, d, 1);
-            if constexpr (MIXED) d *= qscale;
-            sc[j] = ok[j] ? d : -INFINITY;
-            m_new = fmaxf(m_new, sc[j]);
-        }
-        if (m_new > -INFINITY) {
-            const float resc = exp2f(m - m_new);
-            l *= resc;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] *= resc;
+        // A stage whose eight entries are all real rows (every stage but a warp's last, unless the
+        // list holds an index beyond the live length) runs without per-row tests.
+        const bool all_rows = __all_sync(FULL, si[lane & (DEC_G - 1)] >= 0);
+        auto attend = [&](auto full_tag) {
+            constexpr bool FULL_STAGE = decltype(full_tag)::value;
+            float sc[DEC_G / 2];
+            bool ok[DEC_G / 2];
+            float m_new = m;
 #pragma unroll
             for (int j = 0; j < DEC_G / 2; ++j) {
+                const int e = 2 * j + hw2;
+                ok[j] = FULL_STAGE || si[e] >= 0;
+                float d = 0.f;
                 if (ok[j]) {
-                    const int e = 2 * j + hw2;
-                    const float p = exp2f(sc[j] - m_new);
-                    l += p;
-                    float vf[8];
-                    cvt8(reinterpret_cast<const KT*>(buf + (DEC_G + e) * S::ROW) + hl * 8, vf);
+                    if constexpr (MIXED) {
+                        const uint4 kw = *reinterpret_cast<const uint4*>(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8);
+                        d = MixedDot<KT>::word(kw.x, qw.x, d);
+                        d = MixedDot<KT>::word(kw.y, qw.y, d);
+                        d = MixedDot<KT>::word(kw.z, qw.z, d);
+                        d = MixedDot<KT>::word(kw.w, qw.w, d);
+                    } else {
+                        float kf[8];
+                        cvt8(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8, kf);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+                        for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kf[i], d);
+                    }
                 }
+                d += __shfl_xor_sync(FULL, d, 8);
+                d += __shfl_xor_sync(FULL, d, 4);
+                d += __shfl_xor_sync(FULL, d, 2);
+                d += __shfl_xor_sync(FULL, d, 1);
+                if constexpr (MIXED) d *= qscale;
+                sc[j] = ok[j] ? d : -INFINITY;
+                m_new = fmaxf(m_new, sc[j]);
             }
-            m = m_new;
-        }
+            if (FULL_STAGE || m_new > -INFINITY) {
+                const float resc = exp2f(m - m_new);
+                l *= resc;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] *= resc;
+#pragma unroll
+                for (int j = 0; j < DEC_G / 2; ++j) {
+                    if (ok[j]) {
+                        const int e = 2 * j + hw2;
+                        const float p = exp2f(sc[j] - m_new);
+                        l += p;
+                        float vf[8];
+                        cvt8(reinterpret_cast<const KT*>(buf + (DEC_G + e) * S::ROW) + hl * 8, vf);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
+                    }
+                }
+                m = m_new;
+            }
+        };
+        if (all_rows) attend(std::true_type{});
+        else attend(std::false_type{});
         __syncwarp();                      // the stage is free again
         issue(s + DEC_STAGES);
     }
