@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from typing import Optional
+from typing import Optional, Union
 
 import torch
 import torch.nn as nn
@@ -77,11 +77,12 @@ class SocketAttention(nn.Module):
     (GPT-FAST/model.py:377-413, 482-552) without the projections around them.
 
     planes [L,P,D] and protos_T [P,R] are buffers, as in the reference; `heavy_const` is
-    the top-k budget, `sink_size`/`window_size` the structured part of the list
-    (model.py:511-513)."""
+    the top-k budget - an int, or a float for that fraction of the cached keys (eager
+    `sparse_decode` only; see `effective_size`) - and `sink_size`/`window_size` the structured
+    part of the list (model.py:511-513)."""
 
     def __init__(self, n_head: int, n_local_heads: int, head_dim: int, L: int = 32, P: int = 8,
-                 heavy_const: int = 1024, sink_size: int = 64, window_size: int = 128,
+                 heavy_const: Union[int, float] = 1024, sink_size: int = 64, window_size: int = 128,
                  temperature: float = 1.0, planes: Optional[Tensor] = None,
                  protos_T: Optional[Tensor] = None, dtype=torch.bfloat16, device=None):
         super().__init__()
@@ -126,11 +127,21 @@ class SocketAttention(nn.Module):
 
     # -- decode branch of sparse_forward ---------------------------------------------------
     @torch.no_grad()
+    def effective_size(self, n_keys: int) -> int:
+        """The top-k budget for `n_keys` cached keys: `heavy_const` itself when it is an int, that
+        fraction of the keys when it is a float (pipeline/train_quest/modeling/modeling_llama.py:645-648,
+        806-808), clamped to [0, n_keys]."""
+        m = int(self.heavy_const * n_keys) if isinstance(self.heavy_const, float) else int(self.heavy_const)
+        return max(0, min(m, n_keys))
+
     def sparse_decode(self, q_bhd: Tensor, k_new: Tensor, v_new: Tensor, input_pos: Tensor,
-                      out: Optional[Tensor] = None) -> Tensor:
+                      out: Optional[Tensor] = None, pos: Optional[int] = None) -> Tensor:
         """One decode step: q [B,H,D]; k_new, v_new [B,1,Hkv,D]; input_pos [1] (device).
         Appends the token, builds the sparse list from the cache-native codes and attends;
-        returns out [B,H,D].  No relayout, no prefix copy, no host sync."""
+        returns out [B,H,D].  No relayout, no prefix copy, no host sync - unless `heavy_const` is a
+        fraction: the budget then follows the live length, which the caller passes as `pos` (the
+        new token's position as a host integer, as the reference's eager path has it) or which is
+        read back from `input_pos`."""
         cache = self.kv_cache
         assert cache is not None, "Call setup_cache() first so kv_cache exists"
         if input_pos.dtype != torch.long:
@@ -155,15 +166,19 @@ class SocketAttention(nn.Module):
                 s.copy_(t)
                 src.append(s)
         key = tuple(t.data_ptr() for t in src) + (input_pos.data_ptr(), out.data_ptr())
+        ratio = isinstance(self.heavy_const, float)
         if self._step is None:
             step = ops.DecodeStep(cache, src[0], src[1], src[2], input_pos, self.planes, self.protos_T, out,
-                                  topk=self.heavy_const, sink=self.sink_size, window=self.window_size,
+                                  topk=self.effective_size(Tcap), sink=self.sink_size, window=self.window_size,
                                   T_max=Tcap, temperature=self.temperature)
             self._step = (key, step)
         elif self._step[0] != key:
             # other tensors of the same shapes: new addresses, same scratch memory
             self._step[1].rebind(src[0], src[1], src[2], input_pos, out)
             self._step = (key, self._step[1])
+        if ratio:
+            n_keys = (int(pos) if pos is not None else int(input_pos.item())) + 1
+            self._step[1].set_topk(self.effective_size(n_keys))
         self._step[1].run()
         return out
 
@@ -205,6 +220,7 @@ class HostDecodeStep:
         d_pos, d_q, d_k, d_v = views(self.d_in)
         self.h_out = torch.empty(B, H, D, dtype=dt).pin_memory()
         self.h2d_bytes, self.d2h_bytes = total, self.h_out.numel() * es
+        assert not isinstance(attn.heavy_const, float), "a captured step has a fixed budget"
         self.step = ops.DecodeStep(cache, d_q, d_k, d_v, d_pos, attn.planes, attn.protos_T, self.h_out,
                                    topk=attn.heavy_const, sink=attn.sink_size, window=attn.window_size,
                                    T_max=cache.k_cache.shape[2], temperature=attn.temperature)

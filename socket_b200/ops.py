@@ -426,6 +426,7 @@ class DecodeStep:
         p.select_path = SELECT_PATHS[select_path]
         self.params = p
         self.device = dev
+        self._topk_max = topk
         # prologue (append + soft hash in one launch when q and the cache share a dtype), score,
         # select, decode
         self.n_launches = 4 if (k_new is None or q.dtype == cache.k_cache.dtype) else 5
@@ -436,6 +437,30 @@ class DecodeStep:
 
         self._rescored_off = int(lib().sk_decode_step_rescored_rows_offset(B, H, Hkv, D, L, R, T_max, topk,
                                                                            sink, window))
+
+    def set_topk(self, topk: int) -> None:
+        """Another top-k budget for the following runs (at most the budget given at construction,
+        which sized the kept list).  The scratch layout follows the budget, so the workspace grows
+        if this budget's layout needs more; the select counters restart.  For eager callers whose
+        budget is a fraction of the live length (the reference's `_effective_size`,
+        pipeline/train_quest/modeling/modeling_llama.py:645-648); a captured CUDA graph keeps the
+        budget it was captured with."""
+        p = self.params
+        assert 0 <= topk <= self._topk_max, "budget above the one the step was built for"
+        if topk == p.M:
+            return
+        nbytes = int(lib().sk_decode_step_workspace_bytes(p.B, p.H, p.Hkv, p.D, p.L, p.R, p.T_max, topk,
+                                                          p.sink, p.window))
+        if nbytes > self.workspace.numel():
+            self.workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        p.workspace, p.workspace_bytes = ptr(self.workspace), self.workspace.numel()
+        p.M = topk
+        # The decode kernel's ticket counters sit at the start of every layout and are left at zero by
+        # every call; everything else is rewritten by each step except the select counters.
+        self._rescored_off = int(lib().sk_decode_step_rescored_rows_offset(p.B, p.H, p.Hkv, p.D, p.L, p.R, p.T_max,
+                                                                           topk, p.sink, p.window))
+        if self._rescored_off >= 0:
+            self.workspace[self._rescored_off:self._rescored_off + 256].zero_()
 
     def rebind(self, q: torch.Tensor, k_new: Optional[torch.Tensor], v_new: Optional[torch.Tensor],
                input_pos: Optional[torch.Tensor], out: torch.Tensor) -> None:

@@ -151,3 +151,15 @@ def test_decode_step_refuses_unsupported_shapes_before_touching_the_cache():
     assert rc == -2 and b"scorer" in lib.sk_last_error()
     rc = lib.sk_decode_step(C.byref(_step_params(P=9, R=512)), None)
     assert rc == -1 and b"uint8" in lib.sk_last_error()
+
+
+def test_budget_given_as_an_int_or_as_a_fraction():
+    """`heavy_const`: an int is the budget, a float that fraction of the cached keys
+    (pipeline/train_quest/modeling/modeling_llama.py:645-648, 806-808), clamped to [0, keys]."""
+    from socket_b200.attention import SocketAttention
+    a = SocketAttention(8, 2, 128, heavy_const=0.1, device="cpu")
+    assert [a.effective_size(n) for n in (0, 9, 10, 1000, 4097)] == [0, 0, 1, 100, 409]
+    b = SocketAttention(8, 2, 128, heavy_const=1024, device="cpu")
+    assert [b.effective_size(n) for n in (10, 1024, 5000)] == [10, 1024, 1024]
+    c = SocketAttention(8, 2, 128, heavy_const=1.5, device="cpu")
+    assert c.effective_size(100) == 100

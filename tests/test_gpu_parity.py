@@ -593,6 +593,53 @@ def test_sparse_decode_rereads_non_contiguous_inputs_on_every_call():
     assert not torch.equal(got[0], got[1])
 
 
+@pytest.mark.parametrize("ratio,T", [(0.03, 9000), (0.1, 5000), (0.0001, 4100)])
+def test_budget_as_a_fraction_of_the_live_length(ratio, T):
+    """`heavy_const` as a float is that fraction of the cached keys (the reference's
+    `_effective_size`): each step must give what a module built with that step's integer budget
+    gives, while the budget moves with the length from one call to the next (through both select
+    paths: 3 % is inside the filtering scorer's range, 10 % is not)."""
+    B, H, Hkv, sink, window = 1, 8, 2, 4, 16
+    inp = make_decode_inputs(B, H, Hkv, T + 3, seed=77, dtype=torch.bfloat16)
+    k_bshd = cu(inp.k.permute(0, 2, 1, 3).contiguous())
+    v_bshd = cu(inp.v.permute(0, 2, 1, 3).contiguous())
+    g = torch.Generator().manual_seed(9)
+    qs = [cu(torch.randn(B, H, 128, generator=g).bfloat16()) for _ in range(3)]
+
+    def run(budget_of_step):
+        outs = []
+        for i in range(3):
+            attn = SocketAttention(H, Hkv, 128, heavy_const=budget_of_step(i), sink_size=sink, window_size=window,
+                                   planes=inp.planes, protos_T=inp.protos_T, dtype=torch.bfloat16, device=DEV)
+            cache = attn.setup_cache(B, T + 64)
+            cache.append(torch.arange(T + i, device=DEV), k_bshd[:, :T + i], v_bshd[:, :T + i], attn.planes)
+            pos = torch.tensor([T + i], dtype=torch.long, device=DEV)
+            outs.append(attn.sparse_decode(qs[i], k_bshd[:, T + i:T + i + 1].contiguous(),
+                                           v_bshd[:, T + i:T + i + 1].contiguous(), pos).clone())
+            torch.cuda.synchronize()
+            assert int(cache.status) == 0
+        return outs
+
+    want = run(lambda i: max(0, min(int(ratio * (T + i + 1)), T + i + 1)))
+    # one module, one cache, the budget following the length; `pos` given on the host for the
+    # first two calls and read back from the device for the third
+    attn = SocketAttention(H, Hkv, 128, heavy_const=ratio, sink_size=sink, window_size=window,
+                           planes=inp.planes, protos_T=inp.protos_T, dtype=torch.bfloat16, device=DEV)
+    cache = attn.setup_cache(B, T + 64)
+    cache.append(torch.arange(T, device=DEV), k_bshd[:, :T], v_bshd[:, :T], attn.planes)
+    pos = torch.zeros(1, dtype=torch.long, device=DEV)
+    budgets = []
+    for i in range(3):
+        pos.fill_(T + i)
+        o = attn.sparse_decode(qs[i], k_bshd[:, T + i:T + i + 1].contiguous(), v_bshd[:, T + i:T + i + 1].contiguous(),
+                               pos, pos=(T + i) if i < 2 else None)
+        torch.cuda.synchronize()
+        budgets.append(int(attn._step[1].params.M))
+        assert torch.equal(o, want[i]), (ratio, T, i)
+    assert budgets == [attn.effective_size(T + i + 1) for i in range(3)]
+    assert int(cache.status) == 0 and int(cache.prefill_len) == T + 3
+
+
 def test_run_to_run_determinism():
     inp = make_decode_inputs(1, 32, 8, 8192, seed=5, dtype=torch.bfloat16)
     qp = orc.soft_hash(inp.q.float(), inp.planes.float(), inp.protos_T)
