@@ -1,7 +1,8 @@
-"""Two-GPU checks of the tensor-parallel glue (needs a box with at least two GPUs; skipped
-otherwise): the fused projection + rank sum (`sk_gemv_allreduce` through `tp.FusedRowParallel`)
-against the GEMM + NCCL all-reduce it replaces, and a tensor-parallel model whose two shards
-reproduce the single-GPU model's greedy tokens with the sparse decode step in every layer."""
+"""Multi-GPU checks of the tensor-parallel glue on 2, 4 and 8 ranks (each case needs a box with
+that many GPUs; skipped otherwise): the fused projection + rank sum (`sk_gemv_allreduce` through
+`tp.FusedRowParallel`) against the GEMM + NCCL all-reduce it replaces, and a tensor-parallel model
+whose shards reproduce the single-GPU model's greedy tokens with the sparse decode step in every
+layer."""
 import os
 import socket
 
@@ -13,9 +14,9 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _need_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+def _need_gpus(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
 
 
 def _free_port():
@@ -82,10 +83,11 @@ def _fused_worker(rank, world, port, ret):
     dist.destroy_process_group()
 
 
-def test_fused_projection_and_rank_sum_equals_gemm_plus_all_reduce():
-    _need_two_gpus()
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_projection_and_rank_sum_equals_gemm_plus_all_reduce(world):
+    _need_gpus(world)
     ret = mp.Manager().dict()
-    mp.spawn(_fused_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    mp.spawn(_fused_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert ret["ok"], (ret["notes"], ret["worst"])
     assert ret["worst"] <= 8e-3            # bf16 output rounding of sums of a few units
 
@@ -97,7 +99,7 @@ def _model_worker(rank, world, port, ret):
     from socket_b200.model import ModelArgs, Transformer, generate
     tp.maybe_init_dist("nccl")
     dev = torch.device("cuda", rank)
-    cfg = ModelArgs.from_name("tiny", n_layer=2)
+    cfg = ModelArgs.from_name("tiny", n_layer=2, n_local_heads=max(2, world))       # a KV head per rank at least
     full = Transformer(cfg).to(device=dev, dtype=torch.bfloat16).init_random(seed=9, std=0.05)
     part = tp.shard_transformer(full, world, rank)
     prompt = torch.randint(0, cfg.vocab_size, (2, 600), generator=torch.Generator().manual_seed(5))
@@ -117,10 +119,11 @@ def _model_worker(rank, world, port, ret):
     dist.destroy_process_group()
 
 
-def test_two_shards_decode_like_the_single_gpu_model():
-    _need_two_gpus()
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_shards_decode_like_the_single_gpu_model(world):
+    _need_gpus(world)
     ret = mp.Manager().dict()
-    mp.spawn(_model_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    mp.spawn(_model_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert ret["status"] == 0
     # the rank sum rounds differently from the single-GPU GEMM (and the fused kernel sums in fp32), so
     # greedy tokens can part ways late in a random-weight model; the prompt and the first tokens agree
