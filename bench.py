@@ -585,6 +585,24 @@ def measure(args, wl, K, W, world, rank, local_rank, full):
                        "traffic": ncu_traffic(dominant, wl) if world == 1 else None,
                        "per": "GPU" if world > 1 else "launch",
                        "whole_step_frac": round(step_gbs / peak, 4)}
+    if dominant == "score_filter":
+        # The scan's binding unit is not HBM but the SM's shared-memory data pipe: one table lookup per
+        # (key, table) serves the 4 query heads of a KV head and moves 8 bytes per lane with the packed
+        # table (2 wavefronts of 128 B per warp), 16 bytes with the fp32 table (4 wavefronts); an SM
+        # passes one wavefront per cycle.  The floor below is that count at the SM clock sampled during
+        # the run; it explains the HBM fraction above and is reported beside it.
+        packed_scan = bool(extra_notes.get("score_filter", "").startswith("packed"))
+        ht = 4 if (H // Hkv) % 4 == 0 else (2 if (H // Hkv) % 2 == 0 else 1)
+        lookups = B * Hkv * ((H // Hkv) // ht) * T_now * cfg.L
+        wavefronts = lookups / 32 * (2 if packed_scan else ht)
+        mhz = (clocks or {}).get("sm_mhz") or (clocks or {}).get("sm_max_mhz") or 1965.0
+        n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+        floor_us = wavefronts / n_sm / mhz
+        res["roofline"]["shared_memory_pipe"] = {
+            "table": "packed 8 B per lookup" if packed_scan else f"fp32 {4 * ht} B per lookup",
+            "wavefronts_per_launch": int(wavefronts), "sm_mhz": mhz, "floor_us": round(floor_us, 2),
+            "frac": round(floor_us / us[dominant], 4),
+            "note": "lookup wavefronts / (SMs x clock) over the kernel's time: the on-chip bound of the scan"}
     if world > 1:
         # the one collective that follows the path under tensor parallelism: the sum of the
         # row-sharded output projection, [B, 1, d_model] bf16 (d_model = all query heads x head_dim)

@@ -8,8 +8,12 @@
 // collective is pure latency (about 20 us per call, twice per layer).  Here ONE kernel does both:
 //
 //   1. a CTA owns 32 (64 for wide models) output columns: it streams its rows of W_r once (16-byte
-//      loads, several rows in flight per warp), with x_r
-//      staged in shared memory, and reduces the products per warp;
+//      loads, several in flight per lane) with x_r staged in shared memory.  The products run on
+//      the tensor cores as 16 x 8 x 16 tiles - 16 weight rows against the (up to) 8 tokens of the
+//      batch, which is exactly the B operand's width - so a 16-byte piece of W costs one load and
+//      a quarter of an mma instead of 8 B fused multiply-adds and as many conversions; each warp
+//      takes a contiguous part of K and the warps' tiles are added in warp order.  (K not a
+//      multiple of 32: a scalar loop, rows side by side per warp.)
 //   2. it PUSHES its partial sums straight into every rank's receive buffer over NVLink as 8-byte
 //      words {value (fp32), call number}: such a store arrives whole, so the word validates itself
 //      and no fence, flag or second hop is needed (the "low latency" protocol of collective
@@ -69,6 +73,20 @@ __device__ __forceinline__ void unpack8(const uint4& w, const __half*, float (&f
     }
 }
 
+// D (16 x 8, fp32) += A (16 x 16, row-major) * B (16 x 8, column-major)
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1, const __nv_bfloat16*) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1, const __half*) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 template <typename T, int GA_COLS>
 __global__ void __launch_bounds__(GA_THREADS, 1)
 gemv_allreduce_kernel(const T* __restrict__ x, const T* __restrict__ W, int64_t w_row_stride,
@@ -76,19 +94,86 @@ gemv_allreduce_kernel(const T* __restrict__ x, const T* __restrict__ W, int64_t 
                       void* const* __restrict__ peer_base, int world, int rank,
                       int max_batch, int n_pad, uint32_t* __restrict__ counters, int32_t* status) {
     extern __shared__ __align__(16) char ga_smem[];
-    T* x_s = reinterpret_cast<T*>(ga_smem);                                           // [B][K]
-    float* y_s = reinterpret_cast<float*>(ga_smem + (((size_t)B * K * sizeof(T) + 15) & ~(size_t)15));   // [GA_MAX_WORLD][GA_MAXB][GA_COLS]
+    const int KS = K + 8;                                 // row stride of x_s: 16 bytes of padding spread the rows over the banks
+    T* x_s = reinterpret_cast<T*>(ga_smem);                                           // [B][KS]
+    // [GA_MAX_WORLD][GA_MAXB][GA_COLS] partial values; the warps' tiles of step 1 sit behind its first [GA_MAXB][GA_MAX_COLS]
+    float* y_s = reinterpret_cast<float*>(ga_smem + (((size_t)B * KS * sizeof(T) + 15) & ~(size_t)15));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int blk = blockIdx.x, n0 = blk * GA_COLS;
     const uint32_t epoch = counters[blk] + 1u;            // this call's number for this CTA, the same on every rank
     const int slot = (int)(epoch & 1u);
 
     // ---- 1. activations to shared memory, then this CTA's rows of W
-    for (int i = tid; i < B * K / 8; i += GA_THREADS)
-        reinterpret_cast<uint4*>(x_s)[i] = reinterpret_cast<const uint4*>(x)[i];
+    for (int i = tid; i < B * (K / 8); i += GA_THREADS) {
+        const int b = i / (K / 8), c = i - b * (K / 8);
+        reinterpret_cast<uint4*>(x_s + (size_t)b * KS)[c] = reinterpret_cast<const uint4*>(x)[i];
+    }
     __syncthreads();
     constexpr int RPW = GA_COLS / GA_WARPS;               // rows per warp, walked side by side
-    {
+    if ((K & 31) == 0) {
+        // Tensor-core tiles.  Lane (g, t) = (lane / 4, lane % 4) loads 16 bytes = elements
+        // k0 + 8 t .. k0 + 8 t + 7 of weight rows g and g + 8 of each 16-row tile and of token g's
+        // activations; the four lanes of a row cover 32 consecutive k.  A dot product does not care in
+        // which order k is walked, so the 16 k of one mma are taken to be the lanes' register pairs
+        // (elements 8 t + {0,1} and 8 t + {2,3} for the first mma of a block, + {4,5} and {6,7} for the
+        // second), the same for A and B: no shuffles, no shared-memory staging of W.
+        constexpr int TILES = GA_COLS / 16;
+        const int g = lane >> 2, t = lane & 3;
+        const int n_kb = K >> 5;                          // blocks of 32 k
+        const int kb0 = (int)(((int64_t)warp * n_kb) / GA_WARPS), kb1 = (int)(((int64_t)(warp + 1) * n_kb) / GA_WARPS);
+        float acc[TILES][4];
+#pragma unroll
+        for (int rt = 0; rt < TILES; ++rt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[rt][i] = 0.f;
+        const T* wrow[TILES][2];
+#pragma unroll
+        for (int rt = 0; rt < TILES; ++rt) {
+            // rows past the end repeat the last one; their results are never stored
+            wrow[rt][0] = W + (size_t)min(n0 + rt * 16 + g, N - 1) * w_row_stride + 8 * t;
+            wrow[rt][1] = W + (size_t)min(n0 + rt * 16 + g + 8, N - 1) * w_row_stride + 8 * t;
+        }
+        const T* xrow = x_s + (size_t)min(g, B - 1) * KS + 8 * t;
+        const bool token = g < B;
+        // (unrolled: 32 independent loads per lane, 128 KiB per CTA, are issued before the first is
+        // consumed - the rows are streamed once and only the bytes in flight hide the memory latency)
+#pragma unroll (16 / TILES)
+        for (int kb = kb0; kb < kb1; ++kb) {
+            const int k0 = kb << 5;
+            uint4 wa[TILES], wb[TILES];
+#pragma unroll
+            for (int rt = 0; rt < TILES; ++rt) {          // 2 TILES independent 16-byte loads in flight
+                wa[rt] = __ldg(reinterpret_cast<const uint4*>(wrow[rt][0] + k0));
+                wb[rt] = __ldg(reinterpret_cast<const uint4*>(wrow[rt][1] + k0));
+            }
+            uint4 xv = *reinterpret_cast<const uint4*>(xrow + k0);
+            if (!token) xv = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int rt = 0; rt < TILES; ++rt) {
+                mma16816(acc[rt], wa[rt].x, wb[rt].x, wa[rt].y, wb[rt].y, xv.x, xv.y, (const T*)nullptr);
+                mma16816(acc[rt], wa[rt].z, wb[rt].z, wa[rt].w, wb[rt].w, xv.z, xv.w, (const T*)nullptr);
+            }
+        }
+        // acc[rt] = {(row g, token 2t), (row g, token 2t+1), (row g+8, token 2t), (row g+8, token 2t+1)}
+        // of this warp's part of K: the warps' parts meet in shared memory and are added in warp order
+        float* red_s = y_s + GA_MAXB * GA_MAX_COLS;       // [GA_WARPS][GA_MAXB][GA_COLS], inside the y_s block
+#pragma unroll
+        for (int rt = 0; rt < TILES; ++rt) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int b = 2 * t + (i & 1), col = rt * 16 + g + ((i >> 1) << 3);
+                red_s[(warp * GA_MAXB + b) * GA_COLS + col] = acc[rt][i];
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < B * GA_COLS; idx += GA_THREADS) {
+            const int b = idx / GA_COLS, col = idx - b * GA_COLS;
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < GA_WARPS; ++w) v += red_s[(w * GA_MAXB + b) * GA_COLS + col];
+            y_s[b * GA_COLS + col] = v;
+        }
+    } else {
         const int nw = n0 + warp * RPW;
         float acc[RPW][GA_MAXB];
 #pragma unroll
@@ -109,7 +194,7 @@ gemv_allreduce_kernel(const T* __restrict__ x, const T* __restrict__ W, int64_t 
             for (int b = 0; b < GA_MAXB; ++b) {
                 if (b < B) {
                     float xf[8];
-                    unpack8(*reinterpret_cast<const uint4*>(x_s + (size_t)b * K + c * 8), (const T*)nullptr, xf);
+                    unpack8(*reinterpret_cast<const uint4*>(x_s + (size_t)b * KS + c * 8), (const T*)nullptr, xf);
 #pragma unroll
                     for (int rr = 0; rr < RPW; ++rr) {
                         float wf[8];
@@ -213,7 +298,8 @@ int launch_gemv_allreduce(const void* x, const void* W, int64_t w_row_stride, co
         return fail(SK_ERR_INVALID_ARGUMENT, "sk_gemv_allreduce: world %d / rank %d", world, rank);
     if (K % 8 != 0 || w_row_stride % 8 != 0)
         return fail(SK_ERR_MISALIGNED, "sk_gemv_allreduce: K and the weight row stride must be multiples of 8 elements");
-    const size_t smem = (((size_t)B * K * 2 + 15) & ~(size_t)15) + (size_t)GA_MAX_WORLD * GA_MAXB * GA_MAX_COLS * sizeof(float);
+    const size_t smem = (((size_t)B * (K + 8) * 2 + 15) & ~(size_t)15) +
+                        (size_t)(GA_MAX_WORLD + 1) * GA_MAXB * GA_MAX_COLS * sizeof(float);   // + the warps' tiles of step 1
     if (smem > 200 * 1024)
         return fail(SK_ERR_UNSUPPORTED, "sk_gemv_allreduce: %d x %d activations do not fit shared memory", B, K);
 #define SK_GA_LAUNCH(T)                                                                                     \
