@@ -133,7 +133,7 @@ struct ScorePlan {
     int cap_w;            // candidate capacity of one warp's run (filter mode)
     float frac;           // fraction of keys the filter aims to keep
 };
-constexpr int SC_THREADS = 1024;
+constexpr int SC_THREADS = 896;    // 28 warps at 72 registers: measured a little faster than 32 warps at 64 (both scans)
 constexpr int SC_WARPS = SC_THREADS / 32;
 constexpr int SEL_CAP = 16384;   // candidates the select kernel can hold on chip
 constexpr int SC_TAIL = 1024;    // newest keys of a row that the filtering scorer always keeps (see FilterArgs::tail)

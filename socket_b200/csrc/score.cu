@@ -197,7 +197,7 @@ score_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes,
 
         // each warp owns a contiguous run of keys (a multiple of 32 long)
         // (of the LIVE keys of the segment: a partly filled segment still spreads over all warps, so
-        // that its sample comes from 32 warps as soon as it has 1024 keys)
+        // that its sample comes from all warps as soon as it has a thousand keys)
         const int per_warp = (int)(((t1 - t0 + SC_WARPS - 1) / SC_WARPS + 31) / 32 * 32);
         const int ws = (int)t0 + warp * per_warp;
         const int we = min((int)t1, ws + per_warp);
