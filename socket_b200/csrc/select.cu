@@ -986,7 +986,7 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
         total += n_tail;
         if (!any_over && total >= Me && total <= SEL_CAP) {
             // ---- gather: G lanes per run (G = the power of two at or above the mean run length, 4 to 32),
-            // four runs per lane group in flight, each with its first 2 G entries: all loads of a pass
+            // four runs per lane group in flight, each with its first 3 G entries: all loads of a pass
             // are independent and nothing searches.  Run r's (offset | length << 16) comes from shared
             // memory: the tail of cand_idx while the candidates leave it free, else the histogram bins.
             const bool tail_free = total <= SEL_CAP - 1024;
@@ -1001,7 +1001,7 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
             const int rpw = 32 / G, sub = lane / G, li = lane - sub * G;
             const int step_runs = SEL_WARPS * rpw;
             for (int r0 = warp * rpw + sub; r0 < n_runs; r0 += 4 * step_runs) {
-                uint2 e[4][2];
+                uint2 e[4][3];
                 int o[4], n[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -1010,7 +1010,7 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
                     o[u] = m & 0xffff;
                     n[u] = m >> 16;
 #pragma unroll
-                    for (int k = 0; k < 2; ++k) {
+                    for (int k = 0; k < 3; ++k) {
                         const int i = li + G * k;
                         e[u][k] = make_uint2(0u, 0u);
                         if (i < n[u]) e[u][k] = __ldcg(cand + (size_t)r * a.cap_w + i);
@@ -1019,15 +1019,15 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
 #pragma unroll
-                    for (int k = 0; k < 2; ++k) {
+                    for (int k = 0; k < 3; ++k) {
                         const int i = li + G * k;
                         if (i < n[u]) put(o[u] + i, e[u][k], kmin, kmax);
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {                      // runs longer than 2 G: rare
+                for (int u = 0; u < 4; ++u) {                      // runs longer than 3 G: rare
                     const int r = r0 + u * step_runs;
-                    for (int i = li + 2 * G; i < n[u]; i += G)
+                    for (int i = li + 3 * G; i < n[u]; i += G)
                         put(o[u] + i, __ldcg(cand + (size_t)r * a.cap_w + i), kmin, kmax);
                 }
             }
