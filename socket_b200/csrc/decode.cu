@@ -264,34 +264,54 @@ sparse_decode_kernel(const QT* __restrict__ q, const KT* __restrict__ k_cache,
         const bool all_rows = __all_sync(FULL, si[lane & (DEC_G - 1)] >= 0);
         auto attend = [&](auto full_tag) {
             constexpr bool FULL_STAGE = decltype(full_tag)::value;
+            static_assert(DEC_G == 8, "the reduction below is written for four rows per half-warp");
             float sc[DEC_G / 2];
             bool ok[DEC_G / 2];
-            float m_new = m;
+            float d[DEC_G / 2];
 #pragma unroll
             for (int j = 0; j < DEC_G / 2; ++j) {
                 const int e = 2 * j + hw2;
                 ok[j] = FULL_STAGE || si[e] >= 0;
-                float d = 0.f;
+                d[j] = 0.f;
                 if (ok[j]) {
                     if constexpr (MIXED) {
                         const uint4 kw = *reinterpret_cast<const uint4*>(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8);
-                        d = MixedDot<KT>::word(kw.x, qw.x, d);
-                        d = MixedDot<KT>::word(kw.y, qw.y, d);
-                        d = MixedDot<KT>::word(kw.z, qw.z, d);
-                        d = MixedDot<KT>::word(kw.w, qw.w, d);
+                        d[j] = MixedDot<KT>::word(kw.x, qw.x, d[j]);
+                        d[j] = MixedDot<KT>::word(kw.y, qw.y, d[j]);
+                        d[j] = MixedDot<KT>::word(kw.z, qw.z, d[j]);
+                        d[j] = MixedDot<KT>::word(kw.w, qw.w, d[j]);
                     } else {
                         float kf[8];
                         cvt8(reinterpret_cast<const KT*>(buf + e * S::ROW) + hl * 8, kf);
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) d = fmaf(qf[i], kf[i], d);
+                        for (int i = 0; i < 8; ++i) d[j] = fmaf(qf[i], kf[i], d[j]);
                     }
                 }
-                d += __shfl_xor_sync(FULL, d, 8);
-                d += __shfl_xor_sync(FULL, d, 4);
-                d += __shfl_xor_sync(FULL, d, 2);
-                d += __shfl_xor_sync(FULL, d, 1);
-                if constexpr (MIXED) d *= qscale;
-                sc[j] = ok[j] ? d : -INFINITY;
+            }
+            // The four partial products of a lane are summed over the 16 lanes of the half-warp as a
+            // transposed butterfly: each exchange halves the number of values a lane carries, so the sums
+            // cost 5 shuffles instead of 16, and 4 more hand every lane all four results.
+            {
+                const bool up8 = (hl & 8) != 0, up4 = (hl & 4) != 0;
+                float a0 = up8 ? d[2] : d[0], a1 = up8 ? d[3] : d[1];
+                const float b0 = up8 ? d[0] : d[2], b1 = up8 ? d[1] : d[3];
+                a0 += __shfl_xor_sync(FULL, b0, 8);
+                a1 += __shfl_xor_sync(FULL, b1, 8);
+                float c = up4 ? a1 : a0;
+                const float t = up4 ? a0 : a1;
+                c += __shfl_xor_sync(FULL, t, 4);
+                c += __shfl_xor_sync(FULL, c, 2);
+                c += __shfl_xor_sync(FULL, c, 1);
+                if constexpr (MIXED) c *= qscale;
+                // lanes 0-3 of the half-warp now hold row 0's sum, 4-7 row 1's, 8-11 row 2's, 12-15 row 3's
+                const int base = lane & 16;
+#pragma unroll
+                for (int j = 0; j < DEC_G / 2; ++j) d[j] = __shfl_sync(FULL, c, base + 4 * j);
+            }
+            float m_new = m;
+#pragma unroll
+            for (int j = 0; j < DEC_G / 2; ++j) {
+                sc[j] = ok[j] ? d[j] : -INFINITY;
                 m_new = fmaxf(m_new, sc[j]);
             }
             if (FULL_STAGE || m_new > -INFINITY) {
