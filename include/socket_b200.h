@@ -403,7 +403,11 @@ SK_API int sk_decode_step(const sk_decode_params* p, void* stream);
  * counter: the (batch, head) rows whose candidate set could not be proven complete and that were
  * rescored in full (an exact but slow path) by the steps run on that workspace so far.  -1 if the
  * shape's select path keeps no such counter.  The counter starts from whatever the caller put
- * there (zero the workspace once). */
+ * there (zero the workspace once).  Eight more int32 counters follow it: [1] keys scored exactly
+ * inside the k-th score's bracket (packed table), [2] rows whose bracket took the radix ranking,
+ * the reason of each rescored row - [3] a run overflowed, [4] too few / too many candidates,
+ * [5] result not provable on the candidates - and, for [5] with the packed table, [6] bracket
+ * reaching below the largest cut, [7] bracket too large for the chip, [8] inconsistent counts. */
 SK_API int64_t sk_decode_step_rescored_rows_offset(int B, int H, int Hkv, int D, int L, int R, int64_t T_max,
                                             int64_t M, int sink, int window);
 

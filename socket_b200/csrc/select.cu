@@ -815,7 +815,10 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
     const float edge = order_key_inverse(kmin + (thr << shift));
     const float gap = 34.0f / (__uint2float_rz(s_min) + K0 + 33.0f);
     const float LB = fmaxf(edge * (1.0f - gap * 1.0001f) * (1.0f - 1e-5f), 0.f);
-    if (!(gap < 0.5f) || order_key(LB) < chi_key) return false;   // some chunk may have dropped a key of the top Me
+    if (!(gap < 0.5f) || order_key(LB) < chi_key) {               // some chunk may have dropped a key of the top Me
+        if (tid == 0) atomicAdd(stats + 6, 1);                    // statistics: the bracket reaches below the largest cut
+        return false;
+    }
 
     // ---- classes: 1 = in, 2 = between the brackets, 0 = out; two bits per candidate of this thread
     const int ept = (n + SEL_THREADS - 1) / SEL_THREADS;          // <= 16
@@ -839,7 +842,10 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
         atomicAdd(stats + 1, tot_band);
         if (tot_band > BAND_DIRECT) atomicAdd(stats + 2, 1);
     }
-    if (tot_band > BAND_MAX || want < 0 || want > tot_band) return false;
+    if (tot_band > BAND_MAX || want < 0 || want > tot_band) {
+        if (tid == 0) atomicAdd(stats + (tot_band > BAND_MAX ? 7 : 8), 1);   // bracket too large for the chip / inconsistent counts
+        return false;
+    }
     // every read of cand_key happened before the scan's barriers: its space now holds the band
     uint32_t* band_e = s.cand_key;                                     // [BAND_MAX] exact order keys
     int32_t* band_t = reinterpret_cast<int32_t*>(s.cand_key + BAND_MAX);   // [BAND_MAX] key index

@@ -494,6 +494,8 @@ class DecodeStep:
         large enough to be ranked by the radix pass.  Synchronises."""
         if self._rescored_off < 0:
             return None
-        c = self.workspace[self._rescored_off:self._rescored_off + 24].view(torch.int32).tolist()
+        c = self.workspace[self._rescored_off:self._rescored_off + 36].view(torch.int32).tolist()
         return {"rescored_rows": c[0], "bracket_keys": c[1], "bracket_rows_radix": c[2],
-                "rescored_run_overflow": c[3], "rescored_candidate_count": c[4], "rescored_unproved": c[5]}
+                "rescored_run_overflow": c[3], "rescored_candidate_count": c[4], "rescored_unproved": c[5],
+                # why a packed row was unproved: its bracket reached below the largest cut / held too many keys
+                "unproved_below_cut": c[6], "unproved_bracket_size": c[7], "unproved_counts": c[8]}
