@@ -632,6 +632,9 @@ int sk_decode_step(const sk_decode_params* p, void* stream) {
     char* pk = use_packed ? ws + lay.packed : nullptr;
     float* qpar = use_packed ? reinterpret_cast<float*>(pk + packed_param_offset(p->B, p->H, p->Hkv)) : nullptr;
     float* probs = use_packed ? reinterpret_cast<float*>(pk + packed_probs_offset(p->B, p->H, p->Hkv)) : nullptr;
+    // the packed scan and its select work from the packed table and the probabilities: the fp32 scorer
+    // table (4 MB of scattered 16-byte stores at 128 rows) is not written
+    if (use_packed) lut = nullptr;
     int rc;
     bool fused = false;
     if (p->k_new != nullptr && p->q_dtype == p->kv_dtype) {

@@ -1067,11 +1067,18 @@ select_cand_kernel(CandArgs a, int64_t T_host, const int32_t* __restrict__ T_dev
             }
             __syncthreads();
             float* tab = reinterpret_cast<float*>(s.cand_key);           // [L][R] of this head
-            const float* lut_g = a.lut + (size_t)g * a.R * a.L * a.ht;
-            const int j = hj % a.ht;
-            for (int i = tid; i < a.L * a.R; i += SEL_THREADS) {
-                const int l = i / a.R, r = i - l * a.R;
-                tab[i] = __ldcg(lut_g + ((size_t)r * a.L + l) * a.ht + j);
+            if (a.probs != nullptr) {
+                // packed step: the row's probabilities are the table ([L][R], the very values the fp32
+                // scorer table holds), and that table is not written
+                const float* pr = a.probs + (size_t)row * a.L * a.R;
+                for (int i = tid; i < a.L * a.R; i += SEL_THREADS) tab[i] = __ldcg(pr + i);
+            } else {
+                const float* lut_g = a.lut + (size_t)g * a.R * a.L * a.ht;
+                const int j = hj % a.ht;
+                for (int i = tid; i < a.L * a.R; i += SEL_THREADS) {
+                    const int l = i / a.R, r = i - l * a.R;
+                    tab[i] = __ldcg(lut_g + ((size_t)r * a.L + l) * a.ht + j);
+                }
             }
             __syncthreads();
             const uint8_t* cg = a.codes + (size_t)(b * a.Hkv + kvh) * a.Tcap * a.L;

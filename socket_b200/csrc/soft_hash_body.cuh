@@ -215,10 +215,11 @@ __device__ __forceinline__ void soft_hash_body(
             }
         }
     }
-    if (lut == nullptr) return;
+    if (lut == nullptr && lutq == nullptr) return;
     __syncthreads();
-    // scorer table rows: lut[g][r][l][0..ht)
-    float* lut_g = lut + (size_t)g * R * L * ht;
+    // scorer table rows: lut[g][r][l][0..ht) (fp32; not written when the caller keeps the packed table and
+    // the probabilities only) and the packed copy
+    float* lut_g = lut != nullptr ? lut + (size_t)g * R * L * ht : nullptr;
     const bool packed = lutq != nullptr && ht == 4;
     PackedQuant pq = {0.f, 0.f, 0.f};
     uint2* lutq_g = nullptr;
@@ -234,14 +235,16 @@ __device__ __forceinline__ void soft_hash_body(
         const int lt2 = i / R, r = i - lt2 * R;
         if (l0 + lt2 >= L) continue;
         const float* src = stage + (size_t)i * ht;
-        float* dst = lut_g + ((size_t)r * L + l0 + lt2) * ht;
+        float* dst = lut_g + ((size_t)r * L + l0 + lt2) * ht;      // not dereferenced when lut_g is null
         if (ht == 4) {
             const float4 v = *reinterpret_cast<const float4*>(src);
-            *reinterpret_cast<float4*>(dst) = v;
+            if (lut_g != nullptr) *reinterpret_cast<float4*>(dst) = v;
             if (packed)
                 lutq_g[(size_t)r * L + l0 + lt2] =
                     make_uint2(packed_entry(v.x, pq) | (packed_entry(v.y, pq) << 16),
                                packed_entry(v.z, pq) | (packed_entry(v.w, pq) << 16));
+        } else if (lut_g == nullptr) {
+            continue;
         } else if (ht == 2) *reinterpret_cast<float2*>(dst) = *reinterpret_cast<const float2*>(src);
         else *dst = *src;
     }
