@@ -876,12 +876,14 @@ __device__ __forceinline__ bool emit_packed_candidates(SelShared& s, Scan& scan,
         const int kb = tid >> 2, part = tid & 3;
         int cnt = 0;
         if (kb < tot_band) {
+            // keys before kb in the band (lower index) precede it when they are >=, keys after it when >
             const uint32_t mine = band_e[kb];
-#pragma unroll 8
-            for (int jj = part; jj < tot_band; jj += 4) {
-                const uint32_t kj = band_e[jj];
-                cnt += (kj > mine) || (kj == mine && jj < kb);
-            }
+            int jj = part;
+#pragma unroll 4
+            for (; jj < kb; jj += 4) cnt += band_e[jj] >= mine;
+            if (jj == kb) jj += 4;                                // kb itself (only the thread with part == kb % 4 meets it)
+#pragma unroll 4
+            for (; jj < tot_band; jj += 4) cnt += band_e[jj] > mine;
         }
         cnt += __shfl_xor_sync(FULL, cnt, 1);
         cnt += __shfl_xor_sync(FULL, cnt, 2);
