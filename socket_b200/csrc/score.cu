@@ -31,9 +31,9 @@ struct FilterShared {
 };
 
 struct FilterArgs {
-    int32_t* cnt;        // [rows][chunks_max][32]
+    int32_t* cnt;        // [rows][chunks_max][SC_WARPS]
     float* cut;          // [rows][chunks_max]
-    uint2* cand;         // [rows][chunks_max][32][cap_w]  (score bits, key index)
+    uint2* cand;         // [rows][chunks_max][SC_WARPS][cap_w]  (score bits, key index)
     // The newest SC_TAIL keys of a row are not filtered: entry t - (T - SC_TAIL) of the row's tail
     // holds key t, whatever its score.  In a real model the keys just before the query score high
     // as a block (rotary position embedding, local context); compacted into their warp's run they

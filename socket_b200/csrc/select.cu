@@ -682,9 +682,9 @@ select_list_kernel(const float* __restrict__ scores, int64_t score_row_stride,
 // full row.
 // ------------------------------------------------------------------------------------------
 struct CandArgs {
-    const int32_t* cnt;     // [rows][chunks_max][32]
+    const int32_t* cnt;     // [rows][chunks_max][SC_WARPS]
     const float* cut;       // [rows][chunks_max]
-    const uint2* cand;      // [rows][chunks_max][32][cap_w]
+    const uint2* cand;      // [rows][chunks_max][SC_WARPS][cap_w]
     float* scratch;         // [rows][score_stride]
     int32_t* n_fallback;    // statistics: rows that had to be rescored
     int64_t score_stride;
